@@ -1,0 +1,254 @@
+// C-ABI entry points of libfa_b200.so: argument validation, launch planning, dispatch.
+// Nothing here allocates, synchronises or reads device memory.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include "fa_internal.h"
+
+namespace fa {
+
+static thread_local char g_err[512] = "";
+static thread_local const char* g_kernel = "";
+static int g_policy = 0;
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+void note_kernel(const char* name) { g_kernel = name; }
+int cuda_ok(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return FA_OK;
+    return fail(FA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int sm_count() {
+    static int cached[16] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev < 16 && cached[dev]) return cached[dev];
+    int n = 148;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (dev < 16) cached[dev] = n;
+    return n;
+}
+
+static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int check_tensor(const char* name, const fa_tensor& t, bool need) {
+    if (!t.ptr) return need ? fail(FA_ERR_NULL, "%s is null", name) : FA_OK;
+    if (!aligned16(t.ptr)) return fail(FA_ERR_MISALIGNED, "%s must be 16-byte aligned", name);
+    if ((t.stride_b % 8) || (t.stride_s % 8) || (t.stride_h % 8))
+        return fail(FA_ERR_MISALIGNED, "%s strides must be multiples of 8 elements (16 bytes)", name);
+    return FA_OK;
+}
+
+static int check_common(const fa_fwd_params& p) {
+    if (p.dtype != FA_F16 && p.dtype != FA_BF16) return fail(FA_ERR_BAD_DTYPE, "only fp16 and bf16 are supported");
+    if (p.b < 0 || p.sq < 0 || p.sk < 0 || p.hq <= 0 || p.hkv <= 0) return fail(FA_ERR_BAD_SHAPE, "negative or zero size");
+    if (p.hq % p.hkv) return fail(FA_ERR_BAD_SHAPE, "number of heads in q must be divisible by the number of heads in k/v");
+    if (p.d <= 0 || p.d > 256 || p.dv <= 0 || p.dv > 256) return fail(FA_ERR_BAD_SHAPE, "head dimension must be in [1, 256]");
+    if ((p.d % 8) || (p.dv % 8)) return fail(FA_ERR_BAD_SHAPE, "head dimension must be a multiple of 8 (pad it)");
+    if (int e = check_tensor("q", p.q, true)) return e;
+    if (int e = check_tensor("k", p.k, true)) return e;
+    if (int e = check_tensor("v", p.v, true)) return e;
+    if (!p.partials_only) { if (int e = check_tensor("out", p.o, true)) return e; }
+    if (p.partials_only && (!p.o_partial || !p.lse_partial)) return fail(FA_ERR_NULL, "partials_only needs o_partial and lse_partial");
+    return FA_OK;
+}
+
+void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
+    memset(&plan, 0, sizeof(plan));
+    const int G = p.hq / p.hkv;
+    const bool cache_like = p.seqused_k || p.block_table;
+    plan.pack_gqa = (G > 1 && p.sq <= 32) ? 1 : 0;
+    const int rows = plan.pack_gqa ? p.sq * G : p.sq;
+    const int mblocks = (rows + kGenericBM - 1) / kGenericBM;
+    const int nblocks = (p.sk + kGenericBN - 1) / kGenericBN;
+    int nsplit = 1;
+    if (p.num_splits > 1) nsplit = p.num_splits;
+    else if (p.num_splits == 0 && cache_like && nblocks > 1 && p.sq <= 64) {
+        const long base = (long)mblocks * (plan.pack_gqa ? p.hkv : p.hq) * (p.b > 0 ? p.b : 1);
+        const long target = 4L * sm_count();
+        long by_occ = base >= target ? 1 : (target + base - 1) / base;
+        long by_bal = nblocks >= 64 ? (nblocks + 31) / 32 : 1;
+        nsplit = (int)(by_occ > by_bal ? by_occ : by_bal);
+    }
+    if (nsplit > nblocks) nsplit = nblocks;
+    if (nsplit > 256) nsplit = 256;
+    if (nsplit < 1) nsplit = 1;
+    plan.blocks_per_split = nblocks > 0 ? (nblocks + nsplit - 1) / nsplit : 1;
+    plan.nsplit = nblocks > 0 ? (nblocks + plan.blocks_per_split - 1) / plan.blocks_per_split : 1;
+    plan.rotate_q = (p.rotary_cos && p.rotary_sin) ? 1 : 0;
+    const size_t rows_all = (size_t)(p.cu_seqlens_q ? p.total_q : (int64_t)p.b * p.sq) * p.hq;
+    plan.q_rot_bytes = plan.rotate_q ? align256((size_t)p.b * p.sq * p.hq * p.d * 2) : 0;
+    if (plan.nsplit > 1) {
+        plan.o_part_bytes = align256((size_t)plan.nsplit * rows_all * p.dv * sizeof(float));
+        plan.lse_part_bytes = align256((size_t)plan.nsplit * rows_all * sizeof(float));
+    }
+}
+
+static int run_forward(const fa_fwd_params& pin, bool allow_fast) {
+    fa_fwd_params p = pin;
+    if (p.b == 0 || p.hq == 0) return FA_OK;
+    if ((p.cu_seqlens_q ? p.total_q : p.sq) == 0) return FA_OK;
+    FwdPlan plan;
+    plan_forward(p, plan);
+    const size_t need = plan.q_rot_bytes + plan.o_part_bytes + plan.lse_part_bytes;
+    if (need > 0 && (!p.workspace || p.workspace_bytes < need))
+        return fail(FA_ERR_WORKSPACE, "workspace of %zu bytes required, %zu given", need, p.workspace_bytes);
+    char* ws = reinterpret_cast<char*>(p.workspace);
+    void* q_rot = plan.rotate_q ? ws : nullptr;
+    float* o_part = plan.nsplit > 1 ? reinterpret_cast<float*>(ws + plan.q_rot_bytes) : nullptr;
+    float* lse_part = plan.nsplit > 1 ? reinterpret_cast<float*>(ws + plan.q_rot_bytes + plan.o_part_bytes) : nullptr;
+
+    // in-place append (and rotary) first; the attention kernels then see the updated cache
+    if (p.s_new > 0 || plan.rotate_q) {
+        int wl = p.window_left, wr = p.window_right;
+        if (p.sk > 0 && wl >= p.sk) wl = -1;
+        if (p.sk > 0 && wr >= p.sk) wr = -1;
+        const int by_pos = (p.causal || wl >= 0 || wr >= 0) ? 1 : 0;
+        if (int e = launch_append_rotary(p, q_rot, by_pos)) return e;
+        if (plan.rotate_q) {
+            p.q.ptr = q_rot;
+            p.q.stride_h = p.d;
+            p.q.stride_s = (int64_t)p.hq * p.d;
+            p.q.stride_b = (int64_t)p.sq * p.hq * p.d;
+        }
+    }
+    if (allow_fast && g_policy == 0 && plan.nsplit == 1 && !p.partials_only && fwd_sm100_supported(p))
+        return launch_fwd_sm100(p);
+
+    if (p.partials_only && plan.nsplit == 1) { o_part = p.o_partial; lse_part = p.lse_partial; }
+    int e = (g_policy == 0 && plan.use_decode) ? launch_fwd_decode(p, plan, o_part, lse_part)
+                                                : launch_fwd_generic(p, plan, o_part, lse_part);
+    if (e) return e;
+    if (plan.nsplit > 1) return launch_fwd_combine(p, plan.nsplit, o_part, lse_part, p.partials_only);
+    return FA_OK;
+}
+
+}  // namespace fa
+
+using namespace fa;
+
+extern "C" {
+
+int fa_fwd(const fa_fwd_params* p) {
+    if (!p) return fail(FA_ERR_NULL, "params is null");
+    if (int e = check_common(*p)) return e;
+    if (p->cu_seqlens_q || p->cu_seqlens_k || p->block_table || p->seqused_k)
+        return fail(FA_ERR_UNSUPPORTED, "fa_fwd takes dense tensors; use fa_varlen_fwd / fa_fwd_kvcache");
+    fa_fwd_params q = *p;
+    q.num_splits = 1; q.s_new = 0; q.rotary_cos = q.rotary_sin = nullptr; q.kv_begin = 0; q.kv_end = 0; q.partials_only = 0;
+    return run_forward(q, true);
+}
+
+int fa_varlen_fwd(const fa_fwd_params* p) {
+    if (!p) return fail(FA_ERR_NULL, "params is null");
+    if (int e = check_common(*p)) return e;
+    if (!p->cu_seqlens_q) return fail(FA_ERR_NULL, "cu_seqlens_q is null");
+    if (!p->cu_seqlens_k && !p->block_table) return fail(FA_ERR_NULL, "cu_seqlens_k is null");
+    if (p->block_table && !p->seqused_k && !p->cu_seqlens_k) return fail(FA_ERR_NULL, "paged varlen needs seqused_k or cu_seqlens_k");
+    fa_fwd_params q = *p;
+    q.s_new = 0; q.rotary_cos = q.rotary_sin = nullptr;
+    if (!q.block_table) q.num_splits = 1;
+    return run_forward(q, true);
+}
+
+int fa_fwd_kvcache(const fa_fwd_params* p) {
+    if (!p) return fail(FA_ERR_NULL, "params is null");
+    if (int e = check_common(*p)) return e;
+    if (p->block_table && p->page_size <= 0) return fail(FA_ERR_BAD_SHAPE, "page_size must be positive");
+    if (p->block_table && p->cache_batch_idx) return fail(FA_ERR_UNSUPPORTED, "cache_batch_idx is not used with a paged cache");
+    if (p->s_new > 0) {
+        if (!p->seqused_k) return fail(FA_ERR_NULL, "appending k/v needs cache_seqlens");
+        if (int e = check_tensor("k_new", p->k_new, true)) return e;
+        if (int e = check_tensor("v_new", p->v_new, true)) return e;
+    }
+    if ((p->rotary_cos != nullptr) != (p->rotary_sin != nullptr)) return fail(FA_ERR_NULL, "rotary_cos and rotary_sin go together");
+    if (p->rotary_cos) {
+        if (!p->seqused_k) return fail(FA_ERR_NULL, "rotary needs cache_seqlens");
+        if (p->cu_seqlens_q) return fail(FA_ERR_UNSUPPORTED, "rotary with packed q is not supported");
+        if (p->rotary_dim <= 0 || p->rotary_dim > p->d || (p->rotary_dim % 2)) return fail(FA_ERR_BAD_SHAPE, "rotary_dim must be even and <= headdim");
+        if (p->seqlen_ro <= 0) return fail(FA_ERR_BAD_SHAPE, "seqlen_ro must be positive");
+    }
+    return run_forward(*p, false);
+}
+
+size_t fa_fwd_workspace_bytes(const fa_fwd_params* p) {
+    if (!p || p->hkv <= 0 || p->hq <= 0) return 0;
+    FwdPlan plan;
+    plan_forward(*p, plan);
+    return plan.q_rot_bytes + plan.o_part_bytes + plan.lse_part_bytes;
+}
+
+int fa_fwd_num_splits(const fa_fwd_params* p) {
+    if (!p || p->hkv <= 0 || p->hq <= 0) return 1;
+    FwdPlan plan;
+    plan_forward(*p, plan);
+    return plan.nsplit;
+}
+
+static int check_bwd(const fa_bwd_params& p) {
+    if (p.dtype != FA_F16 && p.dtype != FA_BF16) return fail(FA_ERR_BAD_DTYPE, "only fp16 and bf16 are supported");
+    if (p.b < 0 || p.sq < 0 || p.sk < 0 || p.hq <= 0 || p.hkv <= 0) return fail(FA_ERR_BAD_SHAPE, "negative or zero size");
+    if (p.hq % p.hkv) return fail(FA_ERR_BAD_SHAPE, "number of heads in q must be divisible by the number of heads in k/v");
+    if (p.d <= 0 || p.d > 256 || p.dv_dim <= 0 || p.dv_dim > 256 || (p.d % 8) || (p.dv_dim % 8))
+        return fail(FA_ERR_BAD_SHAPE, "head dimension must be a multiple of 8 in [8, 256]");
+    const char* names[8] = {"dout", "q", "k", "v", "out", "dq", "dk", "dv"};
+    const fa_tensor* ts[8] = {&p.dout, &p.q, &p.k, &p.v, &p.o, &p.dq, &p.dk, &p.dv};
+    for (int i = 0; i < 8; ++i) if (int e = check_tensor(names[i], *ts[i], true)) return e;
+    if (!p.lse) return fail(FA_ERR_NULL, "softmax_lse is null");
+    return FA_OK;
+}
+
+static int run_backward(const fa_bwd_params& pin) {
+    fa_bwd_params p = pin;
+    if (p.b == 0) return FA_OK;
+    // window normalisation of the reference's backward host code (fag_general_host.cpp:81-92)
+    if (p.window_left >= p.sk - 1) p.window_left = -1;
+    if (p.window_right >= p.sq - 1 && !p.cu_seqlens_q) p.window_right = -1;
+    const bool fast = g_policy == 0 && bwd_sm100_supported(p);
+    const size_t need = fast ? bwd_sm100_workspace(p) : bwd_generic_workspace(p);
+    if (!p.workspace || p.workspace_bytes < need)
+        return fail(FA_ERR_WORKSPACE, "workspace of %zu bytes required, %zu given", need, p.workspace_bytes);
+    return fast ? launch_bwd_sm100(p) : launch_bwd_generic(p);
+}
+
+int fa_bwd(const fa_bwd_params* p) {
+    if (!p) return fail(FA_ERR_NULL, "params is null");
+    if (int e = check_bwd(*p)) return e;
+    if (p->cu_seqlens_q || p->cu_seqlens_k) return fail(FA_ERR_UNSUPPORTED, "fa_bwd takes dense tensors; use fa_varlen_bwd");
+    return run_backward(*p);
+}
+
+int fa_varlen_bwd(const fa_bwd_params* p) {
+    if (!p) return fail(FA_ERR_NULL, "params is null");
+    if (int e = check_bwd(*p)) return e;
+    if (!p->cu_seqlens_q || !p->cu_seqlens_k) return fail(FA_ERR_NULL, "cu_seqlens_q / cu_seqlens_k is null");
+    return run_backward(*p);
+}
+
+size_t fa_bwd_workspace_bytes(const fa_bwd_params* p) {
+    if (!p || p->hq <= 0) return 0;
+    const size_t a = bwd_generic_workspace(*p), b = bwd_sm100_workspace(*p);
+    return a > b ? a : b;
+}
+
+int fa_combine(const fa_combine_params* c) {
+    if (!c) return fail(FA_ERR_NULL, "params is null");
+    if (!c->o_partial || !c->lse_partial || !c->o) return fail(FA_ERR_NULL, "null pointer");
+    if (c->nsplit <= 0 || c->rows < 0 || c->dv <= 0) return fail(FA_ERR_BAD_SHAPE, "bad sizes");
+    if (c->out_dtype < 0 || c->out_dtype > 2) return fail(FA_ERR_BAD_DTYPE, "out_dtype must be f16, bf16 or fp32");
+    return fa::combine_flat(*c);
+}
+
+const char* fa_last_error(void) { return g_err; }
+const char* fa_version(void) { return "fa_b200 0.1.0 (sm_100a)"; }
+const char* fa_last_kernel(void) { return g_kernel; }
+void fa_set_kernel_policy(int policy) { g_policy = policy; }
+
+}  // extern "C"

@@ -1,0 +1,47 @@
+// Host-side internals shared by the translation units of libfa_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+#include "../../include/fa_b200.h"
+
+namespace fa {
+
+// error reporting (thread-local message, see fa_api.cu)
+int fail(int code, const char* fmt, ...);
+void note_kernel(const char* name);
+int cuda_ok(cudaError_t e, const char* what);
+
+// Resolved launch plan of one forward call.
+struct FwdPlan {
+    int pack_gqa;        // rows of one KV head's query group are stacked into the M dimension
+    int nsplit;          // KV splits (>= 1)
+    int blocks_per_split;// KV blocks (of kGenericBN keys) per split
+    int rotate_q;        // q is rotated into the workspace first
+    size_t q_rot_bytes, o_part_bytes, lse_part_bytes;
+    int use_sm100;       // tcgen05 kernel eligible
+    int use_decode;      // warp-per-split decode kernel eligible
+};
+
+constexpr int kGenericBM = 64;
+constexpr int kGenericBN = 64;
+
+int  sm_count();
+void plan_forward(const fa_fwd_params& p, FwdPlan& plan);
+
+// kernels' host launchers (each returns an fa_status)
+int launch_fwd_generic(const fa_fwd_params& p, const FwdPlan& plan, float* o_part, float* lse_part);
+int launch_fwd_decode(const fa_fwd_params& p, const FwdPlan& plan, float* o_part, float* lse_part);
+int launch_fwd_sm100(const fa_fwd_params& p);
+bool fwd_sm100_supported(const fa_fwd_params& p);
+int launch_append_rotary(const fa_fwd_params& p, void* q_rot, int rotate_q_by_pos);
+int launch_fwd_combine(const fa_fwd_params& p, int nsplit, const float* o_part, const float* lse_part,
+                       int to_partial);
+int combine_flat(const fa_combine_params& c);
+int launch_bwd_generic(const fa_bwd_params& p);
+int launch_bwd_sm100(const fa_bwd_params& p);
+bool bwd_sm100_supported(const fa_bwd_params& p);
+size_t bwd_generic_workspace(const fa_bwd_params& p);
+size_t bwd_sm100_workspace(const fa_bwd_params& p);
+
+}  // namespace fa

@@ -1,0 +1,119 @@
+"""The extension module of the v3 API: `fwd`, `bwd`, `get_scheduler_metadata` with the
+positional signatures of the reference's pybind module
+(csrc/ascend910/flash_attn_npu_3/flash_api.cpp:829-835; fwd :60-96, bwd :573-596,
+get_scheduler_metadata :506-530) plus `fwd_combine`, which the reference's Python calls
+(flash_attn_npu_3/flash_attn_npu_interface.py:961) but its module never defines."""
+from typing import Optional
+
+import torch
+
+import fa_b200_capi as capi
+from fa_b200_capi import CombineParams, SchedParams, check, lib, ptr
+from flash_attn_npu import flash_attn_npu as _v2
+
+
+def _reject(cond, what):
+    if cond:
+        raise RuntimeError(f"FlashAttention on B200 does not support {what}")
+
+
+def fwd(q, k, v, k_new, v_new, qv, out_, cu_seqlens_q, cu_seqlens_k, cu_seqlens_k_new, seqused_q, seqused_k,
+        max_seqlen_q, max_seqlen_k, page_table, kv_batch_idx, leftpad_k, rotary_cos, rotary_sin, seqlens_rotary,
+        q_descale, k_descale, v_descale, softmax_scale, is_causal, window_size_left, window_size_right,
+        attention_chunk, softcap, is_rotary_interleaved, scheduler_metadata, num_splits, pack_gqa, sm_margin):
+    """mha_fwd (csrc/ascend910/flash_attn_npu_3/flash_api.cpp:60-504): one entry for dense,
+    packed, paged and KV-cache calls -> [out, softmax_lse, out_accum, softmax_lse_accum].
+    The same features are rejected as there (:149-161): qv, FP8 descales, attention_chunk,
+    leftpad_k, seqused_q, cu_seqlens_k_new, seqlens_rotary."""
+    _reject(qv is not None, "qv")
+    _reject(q_descale is not None or k_descale is not None or v_descale is not None, "FP8 descale")
+    _reject(attention_chunk != 0, "attention_chunk")
+    _reject(leftpad_k is not None, "leftpad_k")
+    _reject(seqused_q is not None, "seqused_q")
+    _reject(cu_seqlens_k_new is not None, "cu_seqlens_k_new")
+    _reject(seqlens_rotary is not None, "seqlens_rotary")
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    cache_like = page_table is not None or seqused_k is not None or k_new is not None or kv_batch_idx is not None
+    if cache_like:
+        # scheduler_metadata only carries the split count decided on the device-resident lengths;
+        # the kernels read the lengths themselves, so the call is sync-free with or without it.
+        out, lse = _v2.kvcache_forward(q, k, v, k_new, v_new, seqused_k, rotary_cos, rotary_sin, kv_batch_idx,
+                                       page_table, None, out_, softmax_scale, is_causal, window_size_left,
+                                       window_size_right, softcap, is_rotary_interleaved,
+                                       num_splits if num_splits is not None else 0,
+                                       cu_seqlens_q=cu_seqlens_q, max_seqlen_q=max_seqlen_q)
+        return [out, lse, None, None]
+    if cu_seqlens_q is not None:
+        out, lse, _, _ = _v2.varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, None, None, None, None,
+                                        max_seqlen_q, max_seqlen_k, 0.0, softmax_scale, False, is_causal,
+                                        window_size_left, window_size_right, softcap, False, None)
+        return [out, lse, None, None]
+    out, lse, _, _ = _v2.fwd(q, k, v, out_, None, 0.0, softmax_scale, is_causal, window_size_left,
+                             window_size_right, softcap, False, None)
+    return [out, lse, None, None]
+
+
+def bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_seqlens_q, cu_seqlens_k, seqused_q, seqused_k,
+        max_seqlen_q, max_seqlen_k, softmax_scale, is_causal, window_size_left, window_size_right, softcap,
+        deterministic, sm_margin):
+    """mha_bwd (csrc/ascend910/flash_attn_npu_3/flash_api.cpp:573-827) -> [dq, dk, dv, softmax_d]."""
+    _reject(seqused_q is not None or seqused_k is not None, "seqused_q / seqused_k in the backward pass")
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    if cu_seqlens_q is not None:
+        return _v2.varlen_bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_seqlens_q, cu_seqlens_k, None,
+                              max_seqlen_q, max_seqlen_k, 0.0, softmax_scale, False, is_causal, window_size_left,
+                              window_size_right, softcap, deterministic, None, None)
+    return _v2.bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, None, 0.0, softmax_scale, is_causal,
+                   window_size_left, window_size_right, softcap, deterministic, None, None)
+
+
+def get_scheduler_metadata(batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k, headdim, headdim_v,
+                           qkv_dtype, seqused_k, cu_seqlens_q, cu_seqlens_k, cu_seqlens_k_new, seqused_q,
+                           leftpad_k, page_size, max_seqlen_k_new, is_causal, window_size_left, window_size_right,
+                           attention_chunk, has_softcap, num_splits, pack_gqa, sm_margin):
+    """get_scheduler_metadata (csrc/ascend910/flash_attn_npu_3/flash_api.cpp:506-571): a device
+    tensor holding the KV split plan computed on the device from the device-resident lengths.
+    Returned as uint8 like the reference's blob."""
+    capi.require_cuda(seqused_k)
+    n = lib.fa_scheduler_metadata_ints(batch_size)
+    meta = torch.empty((n,), dtype=torch.int32, device=seqused_k.device)
+    p = SchedParams()
+    p.seqused_k, p.cu_seqlens_q = seqused_k.data_ptr(), ptr(cu_seqlens_q)
+    p.b, p.sq, p.sk, p.hq, p.hkv = batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k
+    p.d, p.dv, p.page_size, p.s_new = headdim, headdim_v, page_size or 0, max_seqlen_k_new or 0
+    p.causal, p.window_left, p.window_right = int(is_causal), window_size_left, window_size_right
+    p.num_splits = num_splits or 0
+    p.meta = meta.data_ptr()
+    p.stream = capi.stream_ptr(seqused_k.device)
+    with torch.cuda.device(seqused_k.device):
+        check(lib.fa_scheduler_metadata(p))
+    return meta.view(torch.uint8)
+
+
+def fwd_combine(out_partial, lse_partial, out=None, out_dtype=None):
+    """LSE-weighted combine. out_partial (nsplit, ..., dv) fp32, lse_partial (nsplit, ...) fp32
+    -> (out (..., dv), lse (...))."""
+    capi.require_cuda(out_partial, lse_partial)
+    nsplit = out_partial.shape[0]
+    dv = out_partial.shape[-1]
+    op = out_partial.contiguous().float()
+    lp = lse_partial.contiguous().float()
+    rows = lp[0].numel()
+    out_dtype = out_dtype or (out.dtype if out is not None else torch.float32)
+    code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[out_dtype]
+    res = torch.empty(out_partial.shape[1:], dtype=out_dtype, device=op.device)
+    lse = torch.empty(lse_partial.shape[1:], dtype=torch.float32, device=op.device)
+    c = CombineParams()
+    c.o_partial, c.lse_partial = op.data_ptr(), lp.data_ptr()
+    c.o_split_stride, c.o_row_stride, c.lse_split_stride = rows * dv, dv, rows
+    c.o, c.o_stride, c.lse = res.data_ptr(), dv, lse.data_ptr()
+    c.nsplit, c.rows, c.dv, c.out_dtype = nsplit, rows, dv, code
+    c.stream = capi.stream_ptr(op.device)
+    with torch.cuda.device(op.device):
+        check(lib.fa_combine(c))
+    if out is not None:
+        out.copy_(res)
+        res = out
+    return res, lse

@@ -1,0 +1,223 @@
+/*
+ * C-ABI of the B200 (sm_100a) FlashAttention library  --  libfa_b200.so
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers, sizes and
+ * element strides, launches on the caller's stream, never allocates, never
+ * synchronises and never reads device memory on the host.  Return value:
+ * FA_OK or an fa_status error; fa_last_error() gives the message of the last
+ * failure on the calling thread.  There is no CPU fallback behind any of them.
+ *
+ * The entry points stand in for the pybind functions of the reference's two
+ * extension modules (paths inside the reference project):
+ *   v2  csrc/ascend910/flash_attn_npu/flash_api.cpp:1330-1338
+ *         fwd :639, varlen_fwd :848, fwd_kvcache :356, bwd :1279, varlen_bwd :1092
+ *   v3  csrc/ascend910/flash_attn_npu_3/flash_api.cpp:829-835
+ *         fwd :60, bwd :573, get_scheduler_metadata :506
+ * Outputs and workspaces are allocated by the caller (the reference allocates
+ * them as at::Tensor inside those functions, e.g. flash_api.cpp:443, :567).
+ */
+#ifndef FA_B200_H
+#define FA_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    FA_OK = 0,
+    FA_ERR_NULL = 1,        /* required pointer is null                      */
+    FA_ERR_BAD_DTYPE = 2,   /* dtype is not f16 / bf16                       */
+    FA_ERR_BAD_SHAPE = 3,   /* sizes out of range or inconsistent            */
+    FA_ERR_MISALIGNED = 4,  /* pointer or stride not a multiple of 16 bytes  */
+    FA_ERR_UNSUPPORTED = 5, /* feature the reference rejects as well         */
+    FA_ERR_WORKSPACE = 6,   /* workspace missing or too small                */
+    FA_ERR_CUDA = 7         /* a CUDA runtime call failed                    */
+} fa_status;
+
+typedef enum { FA_F16 = 0, FA_BF16 = 1 } fa_dtype;
+
+/* A (batch, seq, head, dim) view; strides in ELEMENTS, dim stride is 1.
+ * Packed "TND" tensors: batch stride unused, row index = cu_seqlens[b] + i.
+ * Paged caches: batch = block, seq = row inside the page. */
+typedef struct {
+    void*   ptr;
+    int64_t stride_b;
+    int64_t stride_s;
+    int64_t stride_h;
+} fa_tensor;
+
+/* ------------------------------------------------------------------------
+ * Forward.  One parameter block serves the three forward entry points.
+ *   fa_fwd          dense (B,S,H,D)                  mha_fwd         flash_api.cpp:639
+ *   fa_varlen_fwd   packed (T,H,D) + cu_seqlens      mha_varlen_fwd  flash_api.cpp:848
+ *   fa_fwd_kvcache  dense or paged KV cache, in-place append of k_new/v_new,
+ *                   rotary, split-KV                 mha_fwd_kvcache flash_api.cpp:356
+ *                   (v3: mha_fwd csrc/ascend910/flash_attn_npu_3/flash_api.cpp:60)
+ * Window sizes are the caller's raw values; -1 = unbounded.  `causal` forces
+ * window_right = 0.  The mask is aligned to the bottom-right corner.
+ * Rows without any visible key give O = 0 and LSE = +inf.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    fa_tensor q, k, v, o;
+    float*    lse;                 /* fp32 */
+    int64_t   lse_stride_b, lse_stride_h, lse_stride_s;
+
+    const int32_t* cu_seqlens_q;   /* (b+1) or null                                   */
+    const int32_t* cu_seqlens_k;   /* (b+1) or null                                   */
+    const int32_t* seqused_k;      /* (b) keys in use per sequence (cache_seqlens)    */
+    const int32_t* block_table;    /* (b, block_table_stride) or null = not paged      */
+    int64_t        block_table_stride;
+    int32_t        page_size;
+    const int32_t* cache_batch_idx;/* (b) or null; dense cache only                    */
+    const float*   alibi_slopes;   /* (hq) or (b,hq) fp32, or null                     */
+    int64_t        alibi_stride_b; /* 0 when slopes are shared by the batch            */
+
+    int32_t b, sq, sk;             /* sq/sk: max lengths for varlen / cache            */
+    int32_t total_q;               /* rows of a packed q tensor (cu_seqlens_q != null) */
+    int32_t hq, hkv, d, dv;
+    float   scale, softcap;
+    int32_t causal, window_left, window_right;
+    int32_t dtype;                 /* fa_dtype                                         */
+
+    /* new tokens appended in place at positions seqused_k[b] .. +s_new-1 (kvcache)   */
+    fa_tensor k_new, v_new;
+    int32_t   s_new;
+    const void* rotary_cos;        /* (seqlen_ro, rotary_dim/2), q's dtype, or null    */
+    const void* rotary_sin;
+    int32_t   rotary_dim, rotary_interleaved, seqlen_ro;
+
+    /* split-KV.  num_splits: 0 = heuristic, 1 = none, n = exactly n.               */
+    int32_t num_splits;
+    /* Restrict every sequence to keys [kv_begin, kv_end) (kv_end <= 0: no limit)
+     * and, if partials_only != 0, leave fp32 partial (O, LSE) in o_partial /
+     * lse_partial instead of combining: the cross-GPU KV-sharded decode.           */
+    int32_t kv_begin, kv_end, partials_only;
+    float*  o_partial;             /* (splits, rows, dv) fp32, rows = b*sq*hq          */
+    float*  lse_partial;           /* (splits, rows) fp32                              */
+    void*   workspace;             /* >= fa_fwd_workspace_bytes()                      */
+    size_t  workspace_bytes;
+    const void* sched_meta;        /* blob from fa_scheduler_metadata, or null         */
+    void*   stream;                /* cudaStream_t                                     */
+} fa_fwd_params;
+
+int    fa_fwd(const fa_fwd_params* p);
+int    fa_varlen_fwd(const fa_fwd_params* p);
+int    fa_fwd_kvcache(const fa_fwd_params* p);
+size_t fa_fwd_workspace_bytes(const fa_fwd_params* p);
+/* Number of KV splits the library will use for these parameters (>= 1). */
+int    fa_fwd_num_splits(const fa_fwd_params* p);
+
+/* ------------------------------------------------------------------------
+ * Backward.   fa_bwd: mha_bwd flash_api.cpp:1279 (launch_fag_general,
+ * fag_general_host.cpp:18);  fa_varlen_bwd: mha_varlen_bwd flash_api.cpp:1092;
+ * v3 mha_bwd csrc/ascend910/flash_attn_npu_3/flash_api.cpp:573.
+ * dq/dk/dv are written in the input dtype.  deterministic != 0 selects a fixed
+ * accumulation order for dQ.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    fa_tensor dout, q, k, v, o, dq, dk, dv;
+    const float* lse;
+    int64_t lse_stride_b, lse_stride_h, lse_stride_s;
+    const int32_t* cu_seqlens_q;
+    const int32_t* cu_seqlens_k;
+    int32_t b, sq, sk;             /* max lengths when packed                          */
+    int32_t total_q, total_k;      /* rows of packed q / k tensors                     */
+    int32_t hq, hkv, d, dv_dim;
+    float   scale, softcap;
+    int32_t causal, window_left, window_right;
+    int32_t dtype;
+    int32_t deterministic;
+    void*   workspace;             /* >= fa_bwd_workspace_bytes()                      */
+    size_t  workspace_bytes;
+    void*   stream;
+} fa_bwd_params;
+
+int    fa_bwd(const fa_bwd_params* p);
+int    fa_varlen_bwd(const fa_bwd_params* p);
+size_t fa_bwd_workspace_bytes(const fa_bwd_params* p);
+
+/* ------------------------------------------------------------------------
+ * LSE-weighted combine of split partials: CombineScale.hpp:76-357; v3 Python
+ * flash_attn_combine (flash_attn_npu_3/flash_attn_npu_interface.py:961).
+ * o_partial (nsplit, rows, dv) fp32 already normalised, lse_partial (nsplit, rows).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    const float* o_partial;
+    const float* lse_partial;
+    int64_t o_split_stride, o_row_stride;    /* elements */
+    int64_t lse_split_stride;
+    void*   o;                               /* (rows, dv) in out_dtype, row stride o_stride */
+    int64_t o_stride;
+    float*  lse;                             /* (rows) or null */
+    int32_t nsplit, rows, dv;
+    int32_t out_dtype;                       /* fa_dtype, or 2 = fp32 */
+    void*   stream;
+} fa_combine_params;
+
+int fa_combine(const fa_combine_params* p);
+
+/* ------------------------------------------------------------------------
+ * int8 latent (MLA) paged decode.  No counterpart in the reference (it has no
+ * quantised path).  K_j = [scale_j * latent_j (512) | rope_j (64)], V_j = the
+ * dequantised latent; one shared KV head, seqlen_q = 1.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    const void*   q_nope;       /* (b, hq, 512) bf16, row stride q_nope_stride_b / _h */
+    const void*   q_rope;       /* (b, hq, 64) bf16                                   */
+    int64_t q_nope_stride_b, q_nope_stride_h, q_rope_stride_b, q_rope_stride_h;
+    const int8_t* latent;       /* (blocks, page, 512) int8, contiguous               */
+    const float*  scales;       /* (blocks, page) fp32                                */
+    const void*   rope;         /* (blocks, page, 64) bf16                            */
+    const int32_t* block_table; int64_t block_table_stride; int32_t page_size;
+    const int32_t* cache_seqlens;
+    void*   o;                  /* (b, hq, 512) bf16; o_stride_b / _h                 */
+    int64_t o_stride_b, o_stride_h;
+    float*  lse;                /* (b, hq) fp32 or null                               */
+    int32_t b, hq;
+    float   scale;
+    int32_t num_splits;         /* 0 = heuristic                                      */
+    int32_t kv_begin, kv_end, partials_only;
+    float*  o_partial;          /* (splits, b*hq, 512) fp32                           */
+    float*  lse_partial;        /* (splits, b*hq) fp32                                */
+    void*   workspace; size_t workspace_bytes;
+    void*   stream;
+} fa_mla_params;
+
+int    fa_mla_decode(const fa_mla_params* p);
+size_t fa_mla_workspace_bytes(const fa_mla_params* p);
+int    fa_mla_num_splits(const fa_mla_params* p);
+
+/* ------------------------------------------------------------------------
+ * Device-side schedule for the kvcache forward: get_scheduler_metadata
+ * csrc/ascend910/flash_attn_npu_3/flash_api.cpp:506-571 (ComputeFAMetadata,
+ * fa_metadata.aicpu:32-151).  Fills `meta` (int32, fa_scheduler_metadata_ints()
+ * entries) on the stream from the device-resident lengths, without a host sync.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    const int32_t* seqused_k;   /* (b) */
+    const int32_t* cu_seqlens_q;/* (b+1) or null */
+    int32_t b, sq, sk, hq, hkv, d, dv, page_size, s_new, causal, window_left, window_right;
+    int32_t num_splits;
+    int32_t* meta;
+    void*   stream;
+} fa_sched_params;
+
+int    fa_scheduler_metadata(const fa_sched_params* p);
+size_t fa_scheduler_metadata_ints(int32_t b);
+
+/* host-only helpers */
+const char* fa_last_error(void);
+const char* fa_version(void);
+/* Name of the kernel family the last forward / backward call on this thread used
+ * ("sm100_tcgen05", "generic_mma", "decode_splitkv", ...); for tests and benchmarks. */
+const char* fa_last_kernel(void);
+/* Force the kernel family: 0 = automatic, 1 = generic tensor-core kernels only. */
+void        fa_set_kernel_policy(int policy);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H */

@@ -1,0 +1,128 @@
+"""Backward parity on the GPU: autograd through flash_attn_func / flash_attn_varlen_func against the
+float64 oracle (restating tests/fa_small_op_golden.py) and the reference-generated fixtures."""
+import os
+
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+from parity import assert_within
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _api(version):
+    if version == 2:
+        import flash_attn_npu as m
+    else:
+        import flash_attn_npu_3 as m
+    return m
+
+
+def gpu_grads(version, q, k, v, do, scale, causal, window, softcap, deterministic=False):
+    m = _api(version)
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    if version == 2:
+        out, lse, _ = m.flash_attn_func(qc, kc, vc, softmax_scale=scale, causal=causal, window_size=window,
+                                        softcap=softcap, deterministic=deterministic, return_attn_probs=True)
+    else:
+        out, lse = m.flash_attn_func(qc, kc, vc, softmax_scale=scale, causal=causal, window_size=window,
+                                     softcap=softcap, deterministic=deterministic, return_attn_probs=True)
+    dq, dk, dv = torch.autograd.grad(out, (qc, kc, vc), do.cuda())
+    return out.detach().cpu(), lse.detach().cpu(), dq.cpu(), dk.cpu(), dv.cpu()
+
+
+def oracle_grads(q, k, v, do, scale, causal, window, softcap):
+    """(low-precision golden, fp32 golden): the same function fed the low-precision tensors (its score
+    recompute then runs in that dtype) and fed fp32 copies; LSE from the fp32 forward oracle."""
+    _, lse = orc.attention_fwd(q.float(), k.float(), v.float(), scale, causal, window, softcap, data_type=torch.float32)
+    lp = orc.attention_bwd(q, k, v, do, lse, scale, causal, window, softcap)
+    f32 = orc.attention_bwd(q.float(), k.float(), v.float(), do.float(), lse, scale, causal, window, softcap)
+    return lp, f32
+
+
+@pytest.mark.parametrize("idx", range(4))
+def test_reference_golden_fixtures(idx):
+    fx = torch.load(os.path.join(GOLD, "bwd_cases.pt"), weights_only=False)[idx]
+    _, _, dq, dk, dv = gpu_grads(2, fx["q"], fx["k"], fx["v"], fx["dout"], fx["scale"], fx["causal"], fx["window"], fx["softcap"])
+    # the fixture is the reference golden's low-precision output; its own distance to fp32 is ~1e-2
+    for name, got, ref in (("dq", dq, fx["dq"]), ("dk", dk, fx["dk"]), ("dv", dv, fx["dv"])):
+        assert (got.float() - ref.float()).abs().max().item() <= 1e-2 + 1e-2 * ref.float().abs().max().item(), name
+
+
+# (dtype, B, H, Hkv, Sq, Sk, D, causal, wl, wr, softcap): from tests/test_flash_attn_npu_v2_bwd.py:147-283
+CASES = [
+    (torch.bfloat16, 1, 2, 2, 256, 256, 128, True, -1, -1, 0.0),
+    (torch.bfloat16, 2, 4, 4, 512, 512, 128, False, -1, -1, 0.0),
+    (torch.float16, 2, 4, 2, 300, 420, 64, True, -1, -1, 0.0),
+    (torch.bfloat16, 1, 8, 2, 513, 513, 128, True, -1, -1, 0.0),
+    (torch.bfloat16, 1, 4, 1, 384, 384, 128, True, 128, 0, 0.0),
+    (torch.float16, 1, 2, 2, 256, 320, 64, False, 64, 32, 0.0),
+    (torch.bfloat16, 1, 2, 2, 200, 200, 192, True, -1, -1, 0.0),
+    (torch.bfloat16, 1, 2, 1, 160, 224, 256, False, -1, -1, 0.0),
+    (torch.bfloat16, 1, 2, 2, 128, 128, 72, True, -1, -1, 0.0),
+    (torch.float16, 1, 2, 2, 256, 256, 128, True, -1, -1, 20.0),
+    (torch.bfloat16, 1, 2, 2, 300, 100, 64, True, -1, -1, 0.0),
+    (torch.bfloat16, 2, 4, 4, 1024, 1024, 128, True, -1, -1, 0.0),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+@pytest.mark.parametrize("version", [2, 3])
+def test_dense_backward_matrix(case, version):
+    dt, b, h, hkv, sq, sk, d, causal, wl, wr, cap = case
+    if version == 3 and (b, sq) != (1, 256) and sq not in (300, 513):
+        pytest.skip("v3 shares the kernels; a subset suffices")
+    q = (torch.rand(b, sq, h, d) * 2 - 1).to(dt)
+    k = (torch.rand(b, sk, hkv, d) * 2 - 1).to(dt)
+    v = (torch.rand(b, sk, hkv, d) * 2 - 1).to(dt)
+    do = (torch.rand(b, sq, h, d) * 2 - 1).to(dt)
+    scale = d ** -0.5
+    lp, f32 = oracle_grads(q, k, v, do, scale, causal, (wl, wr), cap)
+    _, _, dq, dk, dv = gpu_grads(version, q, k, v, do, scale, causal, (wl, wr), cap)
+    for name, got, a, b_ in zip(("dq", "dk", "dv"), (dq, dk, dv), lp, f32):
+        assert_within(name, got, a, b_)
+
+
+def test_backward_is_bitwise_reproducible():
+    torch.manual_seed(11)
+    q, k, v, do = (torch.randn(1, 700, 4, 128).bfloat16() for _ in range(4))
+    a = gpu_grads(2, q, k, v, do, 0.09, True, (-1, -1), 0.0, deterministic=True)
+    b = gpu_grads(2, q, k, v, do, 0.09, True, (-1, -1), 0.0, deterministic=True)
+    for x, y in zip(a[2:], b[2:]):
+        assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("version", [2, 3])
+def test_varlen_backward(version):
+    fx = torch.load(os.path.join(GOLD, "varlen_bwd_case.pt"), weights_only=False)
+    m = _api(version)
+    cu_q = torch.tensor([0] + torch.tensor(fx["lens_q"]).cumsum(0).tolist(), dtype=torch.int32)
+    cu_k = torch.tensor([0] + torch.tensor(fx["lens_k"]).cumsum(0).tolist(), dtype=torch.int32)
+    qc, kc, vc = (fx[n].cuda().requires_grad_(True) for n in ("q", "k", "v"))
+    res = m.flash_attn_varlen_func(qc, kc, vc, cu_q.cuda(), cu_k.cuda(), max(fx["lens_q"]), max(fx["lens_k"]),
+                                   softmax_scale=fx["scale"], causal=True, return_attn_probs=True)
+    out = res[0]
+    dq, dk, dv = torch.autograd.grad(out, (qc, kc, vc), fx["dout"].cuda())
+    _, lse32 = orc.attention_varlen_fwd(fx["q"].float(), fx["k"].float(), fx["v"].float(), cu_q, cu_k, fx["scale"], True,
+                                        data_type=torch.float32)
+    f32 = orc.attention_varlen_bwd(fx["q"].float(), fx["k"].float(), fx["v"].float(), fx["dout"].float(), lse32, cu_q,
+                                   cu_k, fx["scale"], True)
+    lp = (fx["dq"], fx["dk"], fx["dv"])
+    for name, got, a, b_ in zip(("dq", "dk", "dv"), (dq, dk, dv), lp, f32):
+        assert_within(name, got.cpu(), a, b_)
+
+
+def test_packed_backward_variants():
+    import flash_attn_npu as m
+    torch.manual_seed(12)
+    b, s, h, d = 1, 200, 2, 64
+    qkv = (torch.rand(b, s, 3, h, d) * 2 - 1).bfloat16()
+    do = (torch.rand(b, s, h, d) * 2 - 1).bfloat16()
+    lp, f32 = oracle_grads(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], do, d ** -0.5, True, (-1, -1), 0.0)
+    x = qkv.cuda().requires_grad_(True)
+    out = m.flash_attn_qkvpacked_func(x, causal=True)
+    (g,) = torch.autograd.grad(out, (x,), do.cuda())
+    for i, name in enumerate(("dq", "dk", "dv")):
+        assert_within(name, g[:, :, i].cpu(), lp[i], f32[i])

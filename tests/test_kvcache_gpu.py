@@ -1,0 +1,266 @@
+"""flash_attn_with_kvcache on the GPU: paged gathers, in-place append and rotary (bit-exact),
+split-KV and combine, GQA stacking, the v3 packed-q path and the scheduler metadata."""
+import os
+
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+from parity import assert_lse, assert_within
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def paged_setup(gen, b, lens, hkv, d, page, dt, extra=1, scale=1.0):
+    nblk = [(l + extra + page - 1) // page for l in lens]
+    pool = sum(nblk)
+    perm = torch.randperm(pool, generator=gen).int()
+    table = torch.zeros(b, max(nblk), dtype=torch.int32)
+    off = 0
+    for i, n in enumerate(nblk):
+        table[i, :n] = perm[off:off + n]
+        off += n
+    kc = (torch.randn(pool, page, hkv, d, generator=gen) * scale).to(dt)
+    vc = (torch.randn(pool, page, hkv, d, generator=gen) * scale).to(dt)
+    return kc, vc, table
+
+
+def test_paged_fixture_from_reference_golden():
+    import flash_attn_npu as m
+    fx = torch.load(os.path.join(GOLD, "paged_case.pt"), weights_only=False)
+    lens = torch.tensor(fx["cache_seqlens"], dtype=torch.int32)
+    for ns in (0, 1, 3):
+        out, lse = m.flash_attn_with_kvcache(fx["q"].cuda(), fx["k_cache"].cuda(), fx["v_cache"].cuda(),
+                                             cache_seqlens=lens.cuda(), block_table=fx["block_table"].cuda(),
+                                             softmax_scale=fx["scale"], causal=True, num_splits=ns,
+                                             return_softmax_lse=True)
+        assert (out.cpu().float() - fx["out"].float()).abs().max().item() <= 2 ** -6
+        assert_lse(lse, fx["lse"])
+
+
+# (dtype, B, H, Hkv, Sq, Sk, D, paged, causal, wl, wr, softcap) -- tests/test_flash_attn_npu_v2.py:145-286
+CASES = [
+    (torch.bfloat16, 1, 1, 1, 1, 1024, 128, 1, True, -1, -1, 0.0),
+    (torch.bfloat16, 2, 4, 4, 1024, 1024, 128, 1, True, -1, -1, 0.0),
+    (torch.float16, 3, 1, 1, 512, 512, 128, 1, False, -1, -1, 0.0),
+    (torch.bfloat16, 1, 1, 1, 1, 4096, 128, 1, False, -1, -1, 0.0),
+    (torch.bfloat16, 2, 6, 2, 2, 1024, 128, 1, True, -1, -1, 0.0),
+    (torch.bfloat16, 1, 1, 1, 1024, 1024, 128, 1, True, 512, 256, 0.0),
+    (torch.float16, 1, 128, 1, 1, 1024, 128, 0, True, 542, 647, 0.0),
+    (torch.bfloat16, 4, 32, 8, 1, 2048, 128, 0, False, -1, -1, 0.0),
+    (torch.bfloat16, 2, 64, 8, 1, 4096, 128, 0, False, -1, -1, 0.0),
+    (torch.bfloat16, 2, 128, 8, 1, 4096, 128, 0, False, -1, -1, 0.0),
+    (torch.bfloat16, 2, 32, 4, 16, 1024, 256, 0, False, -1, -1, 0.0),
+    (torch.bfloat16, 1, 32, 4, 1, 2048, 128, 1, False, -1, -1, 0.0),
+    (torch.bfloat16, 1, 128, 4, 1, 2048, 128, 1, True, -1, -1, 0.0),
+    (torch.bfloat16, 1, 32, 8, 1, 2048, 256, 1, False, -1, -1, 0.0),
+    (torch.bfloat16, 2, 16, 2, 5, 4096, 128, 1, True, -1, -1, 0.0),
+    (torch.bfloat16, 1, 32, 8, 13, 2048, 256, 1, False, -1, -1, 0.0),
+    (torch.bfloat16, 2, 32, 8, 65, 2048, 128, 0, False, -1, -1, 0.0),
+    (torch.bfloat16, 1, 10, 2, 15, 2048, 128, 1, False, -1, -1, 0.0),
+    (torch.bfloat16, 1, 3, 1, 128, 2048, 1, 1, False, -1, -1, 0.0),
+    (torch.bfloat16, 2, 256, 16, 8, 640, 1, 1, False, -1, -1, 0.0),
+    (torch.bfloat16, 1, 32, 4, 4, 2048, 128, 1, False, -1, -1, 30.0),
+    (torch.bfloat16, 1, 64, 4, 8, 2048, 128, 1, True, -1, -1, 30.0),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_kvcache_matrix(case):
+    import flash_attn_npu as m
+    dt, b, h, hkv, sq, sk, d, paged, causal, wl, wr, cap = case
+    page = 128
+    q = (torch.rand(b, sq, h, d) * 10 - 5).to(dt)
+    if paged:
+        nb = (sk + page - 1) // page
+        kc = (torch.rand(max(64, nb * b), page, hkv, d) * 10 - 5).to(dt)
+        vc = (torch.rand(max(64, nb * b), page, hkv, d) * 10 - 5).to(dt)
+        table = torch.arange(nb * b, dtype=torch.int32).reshape(b, nb)
+    else:
+        kc = (torch.rand(b, sk, hkv, d) * 10 - 5).to(dt)
+        vc = (torch.rand(b, sk, hkv, d) * 10 - 5).to(dt)
+        table = None
+    lens = torch.full((b,), sk, dtype=torch.int32)
+    scale = d ** -0.5
+    lp_o, _ = orc.kvcache_fwd(q, kc.clone(), vc.clone(), lens, scale, block_table=table, causal=causal, window=(wl, wr), softcap=cap)
+    f_o, f_l = orc.kvcache_fwd(q.float(), kc.float(), vc.float(), lens, scale, block_table=table, causal=causal,
+                               window=(wl, wr), softcap=cap)
+    out, lse = m.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=lens.cuda(),
+                                         block_table=None if table is None else table.cuda(), softmax_scale=scale,
+                                         causal=causal, window_size=(wl, wr), softcap=cap, return_softmax_lse=True)
+    assert_within("out", out.cpu(), lp_o, f_o)
+    assert_lse(lse, f_l)
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("paged", [True, False])
+@pytest.mark.parametrize("s_new,sq,causal", [(1, 1, True), (3, 3, True), (2, 5, False)])
+def test_append_and_rotary_bit_exact(interleaved, paged, s_new, sq, causal):
+    """KV append and block_table gathers are bit-exact: every appended row equals the oracle's bits (rotary in
+    fp32 with separately rounded products), and no other cache byte changes."""
+    import flash_attn_npu as m
+    gen = torch.Generator().manual_seed(21 + s_new)
+    b, h, hkv, d, page, rd = 3, 8, 2, 128, 64, 64
+    lens = [70, 127, 200]
+    dt = torch.bfloat16
+    if paged:
+        kc, vc, table = paged_setup(gen, b, lens, hkv, d, page, dt, extra=s_new)
+    else:
+        kc = torch.randn(b, 256, hkv, d, generator=gen).to(dt)
+        vc = torch.randn(b, 256, hkv, d, generator=gen).to(dt)
+        table = None
+    q = torch.randn(b, sq, h, d, generator=gen).to(dt)
+    kn = torch.randn(b, s_new, hkv, d, generator=gen).to(dt)
+    vn = torch.randn(b, s_new, hkv, d, generator=gen).to(dt)
+    cos, sin = orc.rotary_tables(512, rd, dtype=dt)
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    ref_o, ref_l = orc.kvcache_fwd(q, kc_ref, vc_ref, lens, d ** -0.5, k_new=kn, v_new=vn, rotary_cos=cos, rotary_sin=sin,
+                                   rotary_interleaved=interleaved, block_table=table, causal=causal)
+    kc32, vc32 = kc.clone(), vc.clone()
+    f_o, f_l = orc.kvcache_fwd(q, kc32, vc32, lens, d ** -0.5, k_new=kn, v_new=vn, rotary_cos=cos, rotary_sin=sin,
+                               rotary_interleaved=interleaved, block_table=table, causal=causal)
+    kg, vg = kc.cuda(), vc.cuda()
+    out, lse = m.flash_attn_with_kvcache(q.cuda(), kg, vg, kn.cuda(), vn.cuda(), rotary_cos=cos.cuda(), rotary_sin=sin.cuda(),
+                                         cache_seqlens=lens_t.cuda(), block_table=None if table is None else table.cuda(),
+                                         causal=causal, rotary_interleaved=interleaved, return_softmax_lse=True)
+    assert torch.equal(kg.cpu().view(torch.int16), kc_ref.view(torch.int16)), "K cache differs from the oracle's bits"
+    assert torch.equal(vg.cpu().view(torch.int16), vc_ref.view(torch.int16)), "V cache differs from the oracle's bits"
+    assert not torch.equal(kc_ref, kc)
+    assert (out.cpu().float() - ref_o.float()).abs().max().item() <= 2 ** -6
+    assert_lse(lse, ref_l)
+
+
+def test_config4_shape_small_with_splits():
+    """Configuration 4 scaled down: GQA 32/8, D128, page 256, permuted table, append + rotary, varied lengths."""
+    import flash_attn_npu as m
+    gen = torch.Generator().manual_seed(4)
+    b, h, hkv, d, page = 6, 32, 8, 128, 256
+    lens = torch.randint(100, 5000, (b,), generator=gen).tolist()
+    dt = torch.bfloat16
+    kc, vc, table = paged_setup(gen, b, lens, hkv, d, page, dt)
+    q = torch.randn(b, 1, h, d, generator=gen).to(dt)
+    kn = torch.randn(b, 1, hkv, d, generator=gen).to(dt)
+    vn = torch.randn(b, 1, hkv, d, generator=gen).to(dt)
+    cos, sin = orc.rotary_tables(8192, 128, dtype=dt)
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    kr, vr = kc.clone(), vc.clone()
+    ref_o, ref_l = orc.kvcache_fwd(q, kr, vr, lens, d ** -0.5, k_new=kn, v_new=vn, rotary_cos=cos, rotary_sin=sin,
+                                   rotary_interleaved=False, block_table=table, causal=True)
+    kf, vf = kc.float(), vc.float()
+    cosf, sinf = cos, sin
+    for ns in (0, 1, 5):
+        kg, vg = kc.cuda(), vc.cuda()
+        out, lse = m.flash_attn_with_kvcache(q.cuda(), kg, vg, kn.cuda(), vn.cuda(), rotary_cos=cos.cuda(),
+                                             rotary_sin=sin.cuda(), cache_seqlens=lens_t.cuda(), block_table=table.cuda(),
+                                             causal=True, rotary_interleaved=False, num_splits=ns, return_softmax_lse=True)
+        assert torch.equal(kg.cpu().view(torch.int16), kr.view(torch.int16))
+        assert torch.equal(vg.cpu().view(torch.int16), vr.view(torch.int16))
+        assert (out.cpu().float() - ref_o.float()).abs().max().item() <= 2 ** -6
+        assert_lse(lse, ref_l)
+
+
+def test_cache_batch_idx_and_int_seqlens():
+    import flash_attn_npu as m
+    torch.manual_seed(8)
+    kc, vc = torch.randn(5, 300, 2, 64).bfloat16(), torch.randn(5, 300, 2, 64).bfloat16()
+    q = torch.randn(2, 1, 4, 64).bfloat16()
+    idx = torch.tensor([3, 1], dtype=torch.int32)
+    ref_o, ref_l = orc.kvcache_fwd(q, kc, vc, [222, 222], 0.125, cache_batch_idx=idx)
+    out, lse = m.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=222, cache_batch_idx=idx.cuda(),
+                                         return_softmax_lse=True)
+    assert (out.cpu().float() - ref_o.float()).abs().max().item() <= 2 ** -6
+    assert_lse(lse, ref_l)
+
+
+@pytest.mark.parametrize("num_splits", [0, 2])
+def test_v3_packed_q_paged_varied_lengths(num_splits):
+    """v3 kvcache with packed q (cu_seqlens_q), paged cache and per-sequence lengths
+    (tests/test_flash_attn_npu_v3.py:305-331)."""
+    import flash_attn_npu_3 as m3
+    gen = torch.Generator().manual_seed(1234)
+    b, h, hkv, d, page = 4, 8, 2, 128, 128
+    lq = torch.randint(1, 17, (b,), generator=gen).tolist()
+    lk = [int(torch.randint(q_, 1500, (1,), generator=gen)) for q_ in lq]
+    dt = torch.bfloat16
+    kc, vc, table = paged_setup(gen, b, lk, hkv, d, page, dt, extra=0, scale=2.0)
+    q = (torch.randn(sum(lq), h, d, generator=gen) * 2).to(dt)
+    cu_q = torch.tensor([0] + torch.tensor(lq).cumsum(0).tolist(), dtype=torch.int32)
+    out, lse, *_ = m3.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=torch.tensor(lk, dtype=torch.int32).cuda(),
+                                              page_table=table.cuda(), cu_seqlens_q=cu_q.cuda(), max_seqlen_q=max(lq), causal=True,
+                                              num_splits=num_splits, return_softmax_lse=True)
+    o = 0
+    for i in range(b):
+        ki = orc.gather_paged(kc, table[i], lk[i])
+        vi = orc.gather_paged(vc, table[i], lk[i])
+        qi = q[o:o + lq[i]].unsqueeze(0)
+        r_o, r_l = orc.attention_fwd(qi, ki.unsqueeze(0), vi.unsqueeze(0), d ** -0.5, True)
+        assert (out[o:o + lq[i]].cpu().float() - r_o[0].float()).abs().max().item() <= 2 ** -5
+        assert_lse(lse[:, o:o + lq[i]], r_l[0])
+        o += lq[i]
+
+
+def test_combine_entry_point_matches_oracle():
+    import flash_attn_npu_3 as m3
+    torch.manual_seed(9)
+    op = torch.randn(5, 3, 7, 64)
+    lp = torch.randn(5, 3, 7) * 3
+    lp[2] = float("-inf")
+    lp[:, 1, 3] = float("-inf")
+    out, lse = m3.flash_attn_combine(op.cuda(), lp.cuda(), out_dtype=torch.float32)
+    r_o, r_l = orc.combine_partials(op.reshape(5, 21, 64), lp.reshape(5, 21), torch.float32)
+    assert (out.cpu().reshape(21, 64) - r_o).abs().max().item() < 1e-5
+    assert orc.max_abs_err(lse.cpu().reshape(21), r_l) < 1e-5
+
+
+def test_kv_range_partials_recombine_to_the_full_result():
+    """The cross-device mode: every shard attends to a key range and leaves fp32 (O, LSE); combining the shards'
+    partials equals the unsharded call."""
+    import flash_attn_npu as m
+    import flash_attn_npu_3 as m3
+    from flash_attn_npu import flash_attn_npu as ext
+    gen = torch.Generator().manual_seed(10)
+    b, h, hkv, d, page = 3, 8, 2, 128, 64
+    lens = [900, 130, 2000]
+    kc, vc, table = paged_setup(gen, b, lens, hkv, d, page, torch.bfloat16, extra=0)
+    q = torch.randn(b, 1, h, d, generator=gen).bfloat16()
+    lens_t = torch.tensor(lens, dtype=torch.int32).cuda()
+    full, full_lse = m.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=lens_t, block_table=table.cuda(),
+                                               return_softmax_lse=True)
+    shards = 4
+    per = (max(lens) + shards * page - 1) // (shards * page) * page
+    po = torch.empty(shards, b * h, d, device="cuda")
+    pl = torch.empty(shards, b * h, device="cuda")
+    for s in range(shards):
+        ext.kvcache_forward(q.cuda(), kc.cuda(), vc.cuda(), None, None, lens_t, None, None, None, table.cuda(), None, None,
+                            d ** -0.5, False, -1, -1, 0.0, False, 0, kv_range=(s * per, (s + 1) * per), partials=(po[s], pl[s]))
+    out, lse = m3.flash_attn_combine(po, pl, out_dtype=torch.bfloat16)
+    assert (out.reshape(b, 1, h, d).float() - full.float()).abs().max().item() <= 2 ** -7
+    assert (lse.reshape(b, h, 1) - full_lse).abs().max().item() < 1e-4
+
+
+def test_scheduler_metadata_matches_host_computation():
+    import flash_attn_npu_3 as m3
+    import fa_b200_capi as capi
+    lens = torch.tensor([1000, 64, 65, 7000, 1], dtype=torch.int32)
+    meta = m3.get_scheduler_metadata(5, 1, 8192, 32, 8, 128, lens.cuda(), page_size=256, causal=True).view(torch.int32).cpu()
+    assert meta[0].item() == 0x46413130 and meta[1].item() == 5
+    nsplit, bps = meta[2].item(), meta[3].item()
+    assert meta[4].item() == 7000
+    nb = [(l + 63) // 64 for l in lens.tolist()]
+    assert meta[5].item() == sum(nb)
+    run = 0
+    for i, l in enumerate(lens.tolist()):
+        act = min(nsplit, (nb[i] + bps - 1) // bps)
+        assert meta[8 + 4 * i: 12 + 4 * i].tolist() == [l, nb[i], act, run]
+        run += act
+    assert meta[6].item() == run
+    # the blob is accepted by the kvcache call and does not change the result
+    torch.manual_seed(3)
+    kc, vc = torch.randn(5, 8192, 8, 128).bfloat16().cuda(), torch.randn(5, 8192, 8, 128).bfloat16().cuda()
+    q = torch.randn(5, 1, 32, 128).bfloat16().cuda()
+    a = m3.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=lens.cuda(), causal=True,
+                                   scheduler_metadata=meta.cuda().view(torch.uint8))
+    b_ = m3.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=lens.cuda(), causal=True)
+    assert torch.equal(a, b_)
