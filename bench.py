@@ -1,0 +1,385 @@
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1 and per rank for N > 1, weak scaling): BASELINE configuration 2,
+flash_attn_func forward + backward in bf16, batch 4, seqlen 4096, 32 query heads,
+32 KV heads, headdim 128, causal, softmax_scale 1/sqrt(128); q/k/v/dout i.i.d. N(0,1)
+from a seed (synthetic).  One step = one forward + one backward over that batch.
+The metric is fwd+bwd TFLOP/s with the standard FlashAttention accounting
+(forward 4*B*H*S*S*D/2 under the causal mask, backward 2.5 x forward).
+
+`--impl reference` times the CPU oracle (a port of the reference's Python goldens; the
+reference's device code needs an Ascend toolchain) on a bounded sample of the same workload.
+Prints one JSON line on rank 0.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "flash-attention-npu_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+B, S, H, HKV, D = 4, 4096, 32, 32, 128
+SCALE = D ** -0.5
+WORKLOAD = "config2: flash_attn_func fwd+bwd bf16 B4 S4096 Hq32 Hkv32 D128 causal"
+FWD_FLOPS = 4.0 * B * H * S * S * D / 2.0
+BWD_FLOPS = 2.5 * FWD_FLOPS
+STEP_FLOPS = FWD_FLOPS + BWD_FLOPS
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                clk, mx = float(parts[0]), float(parts[1])
+            except ValueError:
+                continue
+            smax = mx
+            if t0 - 0.05 <= ts <= t1 + 0.15:
+                sm.append(clk)
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        if not sm:
+            sm = [float(l.split(",")[0]) for _, l in self.lines[-3:] if l and l.split(",")[0].strip().replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_oracle_sample(heads=2):
+    """The CPU oracle on one batch entry and `heads` heads of the workload (forward fp32 math on bf16
+    inputs, backward in float64 like the reference golden).  Returns (TFLOP/s, seconds, cores, text)."""
+    from oracle import attention_oracle as orc
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    q, k, v, do = (torch.randn(1, S, heads, D, generator=g).bfloat16() for _ in range(4))
+    t0 = time.perf_counter()
+    out, lse = orc.attention_fwd(q, k, v, SCALE, causal=True)
+    orc.attention_bwd(q, k, v, do, lse, SCALE, causal=True, head_chunk=1)
+    dt = time.perf_counter() - t0
+    flops = STEP_FLOPS * heads / (B * H)
+    return flops / dt / 1e12, dt, cores, f"1 of {B} batch entries x {heads} of {H} heads of the workload, fwd + bwd"
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(args.warmup):
+        cpu_oracle_sample(1)
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        v, dt, cores, sample = cpu_oracle_sample(2)
+        vals.append((v, dt))
+    wall = time.perf_counter() - t_all
+    value = sum(STEP_FLOPS * 2 / (B * H) for _ in vals) / sum(dt for _, dt in vals) / 1e12
+    line = {
+        "impl": "reference", "metric": "fwd_bwd_attention_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "CPU oracle (port of the reference's torch goldens) on host cores"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode side measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch.distributed as dist
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    import fa_b200_capi as capi
+    import flash_attn_npu as fa
+    from flash_attn_npu import flash_attn_npu as ext
+
+    g = torch.Generator().manual_seed(1234 + rank)
+    host = [torch.randn(B, S, hh, D, generator=g).bfloat16().pin_memory() for hh in (H, HKV, HKV, H)]
+    q, k, v, do = (t.to(dev) for t in host)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    def step():
+        out, lse, _, _ = ext.fwd(q, k, v, None, None, 0.0, SCALE, True, -1, -1, 0.0, False, None)
+        ext.bwd(do, q, k, v, out, lse, dq, dk, dv, None, 0.0, SCALE, True, -1, -1, 0.0, False, None, None)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    fwd_kernel = None
+    out, lse, _, _ = ext.fwd(q, k, v, None, None, 0.0, SCALE, True, -1, -1, 0.0, False, None)
+    fwd_kernel = capi.last_kernel()
+    ext.bwd(do, q, k, v, out, lse, dq, dk, dv, None, 0.0, SCALE, True, -1, -1, 0.0, False, None, None)
+    bwd_kernel = capi.last_kernel()
+
+    # ---- device-timed region: K steps, per-kernel events lent to the library ---------------------------
+    nev = 8
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(nev)] for _ in range(2 * args.steps)]
+    for row in evs:
+        for e in row:
+            e.record()
+    torch.cuda.synchronize()
+    arr_t = ctypes.c_void_p * nev
+    arrays = [arr_t(*[e.cuda_event for e in row]) for row in evs]
+    used = [0] * (2 * args.steps)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    t0 = time.time()
+    start.record()
+    for i in range(args.steps):
+        capi.lib.fa_set_kernel_events(arrays[2 * i], nev)
+        out, lse, _, _ = ext.fwd(q, k, v, None, None, 0.0, SCALE, True, -1, -1, 0.0, False, None)
+        used[2 * i] = capi.lib.fa_kernel_events_used()
+        capi.lib.fa_set_kernel_events(arrays[2 * i + 1], nev)
+        ext.bwd(do, q, k, v, out, lse, dq, dk, dv, None, 0.0, SCALE, True, -1, -1, 0.0, False, None, None)
+        used[2 * i + 1] = capi.lib.fa_kernel_events_used()
+    capi.lib.fa_set_kernel_events(None, 0)
+    stop.record()
+    barrier()
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    ms = start.elapsed_time(stop) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    # per-kernel durations (ms), averaged over the steps
+    fwd_ms = statistics.mean(evs[2 * i][0].elapsed_time(evs[2 * i][used[2 * i] - 1]) for i in range(args.steps))
+    bwd_parts = []
+    nb = used[1]
+    for j in range(1, nb):
+        bwd_parts.append(statistics.mean(evs[2 * i + 1][j - 1].elapsed_time(evs[2 * i + 1][j]) for i in range(args.steps)))
+    bwd_ms = sum(bwd_parts)
+    launches = sum(u - 1 for u in used)
+
+    # ---- end to end through the public API with host buffers ---------------------------------------------
+    e2e_steps = max(2, min(args.steps, 5))
+    hq, hk, hv, hdo = host
+    out_h = torch.empty_like(hq)
+    gq_h, gk_h, gv_h = torch.empty_like(hq), torch.empty_like(hk), torch.empty_like(hv)
+
+    def e2e_step():
+        qd = hq.to(dev, non_blocking=True).requires_grad_(True)
+        kd = hk.to(dev, non_blocking=True).requires_grad_(True)
+        vd = hv.to(dev, non_blocking=True).requires_grad_(True)
+        dod = hdo.to(dev, non_blocking=True)
+        o = fa.flash_attn_func(qd, kd, vd, causal=True, softmax_scale=SCALE)
+        gq, gk, gv = torch.autograd.grad(o, (qd, kd, vd), dod)
+        out_h.copy_(o.detach(), non_blocking=True)
+        gq_h.copy_(gq, non_blocking=True)
+        gk_h.copy_(gk, non_blocking=True)
+        gv_h.copy_(gv, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2.record()
+    barrier()
+    e2e_ms = s2.elapsed_time(e2) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    h2d = sum(t.numel() * 2 for t in host)
+    d2h = sum(t.numel() * 2 for t in (out_h, gq_h, gk_h, gv_h))
+
+    decode = None
+    if rank == 0 and not args.no_decode:
+        try:
+            decode = paged_decode_side_measurement(dev)
+        except Exception as exc:  # the side measurement must not take the headline down
+            decode = {"error": str(exc)[:200]}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks = measured_peaks()
+    # dominant kernel = the longest single launch of the step
+    parts = [("fwd:" + fwd_kernel, fwd_ms, FWD_FLOPS)]
+    names = ["bwd:delta", "bwd:dk_dv", "bwd:dq"] if len(bwd_parts) == 3 else [f"bwd:{j}" for j in range(len(bwd_parts))]
+    # flops per backward launch: dK/dV pass recomputes S and dP (2) and does dV, dK (2); dQ pass S, dP, dQ (3)
+    unit = FWD_FLOPS / 2.0
+    flops_of = {"bwd:delta": 0.0, "bwd:dk_dv": 4 * unit, "bwd:dq": 3 * unit}
+    for n, t in zip(names, bwd_parts):
+        parts.append((n, t, flops_of.get(n, BWD_FLOPS)))
+    dom = max(parts, key=lambda x: x[1])
+    sustained = ms * args.steps > 1500.0
+    peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+    achieved = dom[2] / (dom[1] * 1e-3) / 1e12
+    line = {
+        "metric": "fwd_bwd_attention_tflops", "value": STEP_FLOPS * world / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu": "one full batch per rank, no collective",
+                   "l2": "inputs larger than L2 (q,k,v,dout 128 MiB each)", "seed": 1234,
+                   "fwd_kernel": fwd_kernel, "bwd_kernel": bwd_kernel},
+        "fwd_tflops": FWD_FLOPS / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": BWD_FLOPS / (bwd_ms * 1e-3) / 1e12,
+        "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+        "kernels_ms": {n: t for n, t, _ in parts},
+        "roofline": {"bound": "tensor", "kernel": dom[0], "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "traffic": None,
+                     "peak_source": peaks["_source"] + (" sustained" if sustained else " burst") + " cuBLAS bf16",
+                     "frac_of_nominal_2250": achieved / 2250.0,
+                     "fwd_frac": FWD_FLOPS / (fwd_ms * 1e-3) / 1e12 / peak},
+        "e2e": {"value": STEP_FLOPS * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }
+    if decode is not None:
+        line["paged_decode"] = decode
+    if not args.no_cpu and world == 1:
+        v_cpu, dt, cores, sample = cpu_oracle_sample(2)
+        line["cpu_baseline"] = {"value": v_cpu, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
+                                "seconds": dt}
+    else:
+        line["cpu_baseline"] = None
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def paged_decode_side_measurement(dev, iters=10):
+    """BASELINE configuration 4 (paged decode, B128 Hq32 Hkv8 D128 page 256, lengths U[1024,32768], append +
+    rotary) timed with CUDA events; reports achieved HBM GB/s over the algorithmic bytes (K and V rows read
+    once, 4096 B per cached token and KV head set, plus q / out / table / appended rows)."""
+    import flash_attn_npu as fa
+    g = torch.Generator().manual_seed(4)
+    b, hq, hkv, d, page = 128, 32, 8, 128, 256
+    lens = torch.randint(1024, 32769, (b,), generator=g, dtype=torch.int32)
+    nblk = (lens + 1 + page - 1) // page
+    pool = int(nblk.sum())
+    perm = torch.randperm(pool, generator=g).int()
+    table = torch.zeros(b, int(nblk.max()), dtype=torch.int32)
+    off = 0
+    for i in range(b):
+        n = int(nblk[i])
+        table[i, :n] = perm[off:off + n]
+        off += n
+    kc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
+    q = torch.randn(b, 1, hq, d, device=dev, dtype=torch.bfloat16)
+    kn = torch.randn(b, 1, hkv, d, device=dev, dtype=torch.bfloat16)
+    vn = torch.randn(b, 1, hkv, d, device=dev, dtype=torch.bfloat16)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    ang = torch.outer(torch.arange(32800, dtype=torch.float32), inv)
+    cos, sin = torch.cos(ang).bfloat16().to(dev), torch.sin(ang).bfloat16().to(dev)
+    lens_d, table_d = lens.to(dev), table.to(dev)
+
+    def call():
+        return fa.flash_attn_with_kvcache(q, kc, vc, kn, vn, rotary_cos=cos, rotary_sin=sin, cache_seqlens=lens_d,
+                                          block_table=table_d, causal=True, rotary_interleaved=False)
+
+    for _ in range(3):
+        call()
+    import fa_b200_capi as capi
+    kern = capi.last_kernel()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        call()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / iters
+    tokens = int((lens + 1).sum())
+    bytes_ = tokens * hkv * d * 2 * 2 + b * hq * d * 2 * 2 + table.numel() * 4 + b * hkv * d * 2 * 2
+    peaks = measured_peaks()
+    gbs = bytes_ / (ms * 1e-3) / 1e9
+    return {"workload": "config4: paged decode bf16 B128 Sq1 Hq32 Hkv8 D128 page256 L~U[1024,32768], append+rotary",
+            "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": bytes_, "kernel": kern,
+            "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8000": gbs / 8000.0,
+            "cache_gb": pool * page * hkv * d * 2 * 2 / 1e9}
+
+
+if __name__ == "__main__":
+    main()

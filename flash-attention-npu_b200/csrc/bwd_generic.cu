@@ -413,7 +413,7 @@ template <typename T, int HD, int BN, int DSPLIT>
 static int launch_bwd_t(const fa_bwd_params& p, float* delta, cudaStream_t st) {
     const int64_t toks = p.cu_seqlens_q ? p.total_q : (int64_t)p.b * p.sq;
     const int64_t rows = toks * p.hq;
-    if (rows > 0) bwd_delta_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p, delta);
+    if (rows > 0) { bwd_delta_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p, delta); mark_kernel(st); }
     const size_t smem1 = (size_t)(2 * BN + 4 * 64) * HD * 2 + 2 * 64 * BN * 2;
     const size_t smem2 = (size_t)(2 * 64 + 4 * 64) * HD * 2;
     auto k1 = bwd_dkdv_kernel<T, HD, BN, DSPLIT>;
@@ -421,8 +421,8 @@ static int launch_bwd_t(const fa_bwd_params& p, float* delta, cudaStream_t st) {
     if (int e = cuda_ok(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1), "cudaFuncSetAttribute")) return e;
     if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2), "cudaFuncSetAttribute")) return e;
     dim3 g1(ceil_div(p.sk, BN), p.hkv, p.b), g2(ceil_div(p.sq, 64), p.hq, p.b);
-    if (g1.x && g1.y && g1.z) k1<<<g1, 128, smem1, st>>>(p, delta);
-    if (g2.x && g2.y && g2.z) k2<<<g2, 128, smem2, st>>>(p, delta);
+    if (g1.x && g1.y && g1.z) { k1<<<g1, 128, smem1, st>>>(p, delta); mark_kernel(st); }
+    if (g2.x && g2.y && g2.z) { k2<<<g2, 128, smem2, st>>>(p, delta); mark_kernel(st); }
     return cuda_ok(cudaGetLastError(), "bwd_generic launch");
 }
 

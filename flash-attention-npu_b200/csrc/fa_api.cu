@@ -10,6 +10,13 @@ namespace fa {
 static thread_local char g_err[512] = "";
 static thread_local const char* g_kernel = "";
 static int g_policy = 0;
+// optional per-kernel timing: the caller lends CUDA events, one is recorded after every launch
+static thread_local cudaEvent_t* g_events = nullptr;
+static thread_local int g_nevents = 0, g_event_idx = 0;
+
+void mark_kernel(cudaStream_t st) {
+    if (g_events && g_event_idx < g_nevents) cudaEventRecord(g_events[g_event_idx++], st);
+}
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -95,8 +102,14 @@ static int run_forward(const fa_fwd_params& pin, bool allow_fast) {
     fa_fwd_params p = pin;
     if (p.b == 0 || p.hq == 0) return FA_OK;
     if ((p.cu_seqlens_q ? p.total_q : p.sq) == 0) return FA_OK;
+    // Window normalisation of the reference's forward host code (flash_api.cpp:684-704, :936-956,
+    // :483-505): a side that reaches the (longest) key length is unbounded.  For the right side this
+    // is not a no-op when seqlen_q exceeds the window, so it is applied here exactly as there.
+    if (p.sk > 0 && p.window_left >= p.sk) p.window_left = -1;
+    if (p.sk > 0 && p.window_right >= p.sk) p.window_right = -1;
     FwdPlan plan;
     plan_forward(p, plan);
+    mark_kernel(reinterpret_cast<cudaStream_t>(p.stream));
     const size_t need = plan.q_rot_bytes + plan.o_part_bytes + plan.lse_part_bytes;
     if (need > 0 && (!p.workspace || p.workspace_bytes < need))
         return fail(FA_ERR_WORKSPACE, "workspace of %zu bytes required, %zu given", need, p.workspace_bytes);
@@ -107,10 +120,7 @@ static int run_forward(const fa_fwd_params& pin, bool allow_fast) {
 
     // in-place append (and rotary) first; the attention kernels then see the updated cache
     if (p.s_new > 0 || plan.rotate_q) {
-        int wl = p.window_left, wr = p.window_right;
-        if (p.sk > 0 && wl >= p.sk) wl = -1;
-        if (p.sk > 0 && wr >= p.sk) wr = -1;
-        const int by_pos = (p.causal || wl >= 0 || wr >= 0) ? 1 : 0;
+        const int by_pos = (p.causal || p.window_left >= 0 || p.window_right >= 0) ? 1 : 0;
         if (int e = launch_append_rotary(p, q_rot, by_pos)) return e;
         if (plan.rotate_q) {
             p.q.ptr = q_rot;
@@ -211,6 +221,7 @@ static int run_backward(const fa_bwd_params& pin) {
     // window normalisation of the reference's backward host code (fag_general_host.cpp:81-92)
     if (p.window_left >= p.sk - 1) p.window_left = -1;
     if (p.window_right >= p.sq - 1 && !p.cu_seqlens_q) p.window_right = -1;
+    mark_kernel(reinterpret_cast<cudaStream_t>(p.stream));
     const bool fast = g_policy == 0 && bwd_sm100_supported(p);
     const size_t need = fast ? bwd_sm100_workspace(p) : bwd_generic_workspace(p);
     if (!p.workspace || p.workspace_bytes < need)
@@ -249,6 +260,17 @@ int fa_combine(const fa_combine_params* c) {
 const char* fa_last_error(void) { return g_err; }
 const char* fa_version(void) { return "fa_b200 0.1.0 (sm_100a)"; }
 const char* fa_last_kernel(void) { return g_kernel; }
+void fa_debug_set(int key, int value) {
+    if (key == 1) fa::fwd_sm100_set_p_in_tmem(value);
+    if (key == 3) fa::sm100_error_flag(true);
+}
+int fa_debug_get(int key) { return key == 2 ? fa::sm100_error_flag(false) : 0; }
+void fa_set_kernel_events(void** events, int count) {
+    g_events = reinterpret_cast<cudaEvent_t*>(events);
+    g_nevents = events ? count : 0;
+    g_event_idx = 0;
+}
+int fa_kernel_events_used(void) { return g_event_idx; }
 void fa_set_kernel_policy(int policy) { g_policy = policy; }
 
 }  // extern "C"

@@ -11,6 +11,8 @@ namespace fa {
 int fail(int code, const char* fmt, ...);
 void note_kernel(const char* name);
 int cuda_ok(cudaError_t e, const char* what);
+// records the next lent timing event (if any) on the stream; call after every kernel launch
+void mark_kernel(cudaStream_t st);
 
 // Resolved launch plan of one forward call.
 struct FwdPlan {
@@ -34,6 +36,9 @@ int launch_fwd_generic(const fa_fwd_params& p, const FwdPlan& plan, float* o_par
 int launch_fwd_decode(const fa_fwd_params& p, const FwdPlan& plan, float* o_part, float* lse_part);
 int launch_fwd_sm100(const fa_fwd_params& p);
 bool fwd_sm100_supported(const fa_fwd_params& p);
+void fwd_sm100_set_p_in_tmem(int v);
+// reads (and optionally clears) the code a timed-out wait left behind; synchronises
+int sm100_error_flag(bool clear);
 int launch_append_rotary(const fa_fwd_params& p, void* q_rot, int rotate_q_by_pos);
 int launch_fwd_combine(const fa_fwd_params& p, int nsplit, const float* o_part, const float* lse_part,
                        int to_partial);

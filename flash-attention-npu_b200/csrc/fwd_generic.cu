@@ -314,6 +314,7 @@ static int launch_one(const FwdArgs& a, cudaStream_t st) {
     dim3 grid(ceil_div(rows, kGenericBM), a.pack ? p.hkv : p.hq, p.b * a.nsplit);
     if (grid.x == 0 || grid.y == 0 || grid.z == 0) return FA_OK;
     kern<<<grid, 128, smem, st>>>(a);
+    mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_generic launch");
 }
 
@@ -412,6 +413,7 @@ int launch_append_rotary(const fa_fwd_params& p, void* q_rot, int rotate_q_by_po
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
     if (p.dtype == FA_F16) append_rotary_kernel<__half><<<grid, 64, 0, st>>>(p, reinterpret_cast<__half*>(q_rot), rotate_q_by_pos);
     else append_rotary_kernel<__nv_bfloat16><<<grid, 64, 0, st>>>(p, reinterpret_cast<__nv_bfloat16*>(q_rot), rotate_q_by_pos);
+    mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "append_rotary launch");
 }
 
@@ -484,6 +486,7 @@ int launch_fwd_combine(const fa_fwd_params& p, int nsplit, const float* o_part, 
                                                                 nsplit, rows, p.dv, p.hq, sq_dense, p.o.stride_b, p.o.stride_s, p.o.stride_h,
                                                                 p.lse_stride_b, p.lse_stride_h, p.lse_stride_s, 0);
     }
+    mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "combine launch");
 }
 

@@ -1,0 +1,402 @@
+// Forward attention on Blackwell tensor cores (tcgen05 + TMEM + TMA), sm_100a.
+//
+// One CTA owns a 128-row query tile of one head and walks 128-key tiles.
+//   warp 4 (one lane)  TMA producer: Q once, K and V tiles through two-stage rings.
+//   warp 5 (one lane)  MMA issuer:   S = Q K^T into one of two TMEM score buffers, O += P V
+//                                     into the TMEM output accumulator.
+//   warps 0-3          softmax:      one thread per query row reads its score row from TMEM,
+//                                     keeps the running max / sum, writes P (rounded to the input
+//                                     type) into swizzled shared memory for the second MMA and
+//                                     rescales O in TMEM when the running max moves.
+// Scores of tile j+1 are computed while tile j goes through softmax.  Math as the reference's
+// forward (mha_fwd_kvcache.cpp:632-969, online_softmax.hpp:623-875, rescale_o.hpp:318-531).
+//
+// Every mbarrier wait is bounded; a timeout records a code in g_fwd_sm100_error and the CTA
+// frees its tensor memory and returns.
+#include "fa_utils.cuh"
+#include "fa_internal.h"
+#include "sm100_ptx.cuh"
+
+namespace fa {
+
+using namespace sm100;
+
+__device__ int g_fwd_sm100_error = 0;
+
+struct alignas(64) Sm100FwdArgs {
+    CUtensorMap tq, tk, tv;
+    void* o;
+    float* lse;
+    int64_t o_sb, o_ss, o_sh;
+    int64_t lse_sb, lse_sh, lse_ss;
+    const int32_t* cu_q;
+    const int32_t* cu_k;
+    int b, sq, sk, hq, hkv;
+    float scale_log2;
+    int causal, wl, wr;
+    int p_in_tmem;
+};
+
+template <int D>
+struct FwdSm100Smem {
+    static constexpr int kTile = 128;
+    static constexpr int kSub = 128 * 128;                  // bytes of one [128 rows][64 elem] sub-tile
+    static constexpr int kQ = (D / 64) * kSub;
+    static constexpr int kKV = (D / 64) * kSub;
+    static constexpr int kP = 2 * kSub;
+    static constexpr int oQ = 0;
+    static constexpr int oK = oQ + kQ;                      // 2 stages
+    static constexpr int oV = oK + 2 * kKV;                 // 2 stages
+    static constexpr int oP = oV + 2 * kKV;
+    static constexpr int oBar = oP + kP;
+    static constexpr int kBytes = oBar + 256;
+};
+
+// barrier slots (8 bytes each)
+enum { B_Q = 0, B_KF0, B_KF1, B_KE0, B_KE1, B_VF0, B_VF1, B_VE0, B_VE1, B_S0, B_S1, B_P, B_PV, B_COUNT };
+
+template <typename T, int D>
+__global__ void __launch_bounds__(192, 1) fwd_sm100_kernel(const __grid_constant__ Sm100FwdArgs a) {
+    using L = FwdSm100Smem<D>;
+    constexpr int NSUB = D / 64;
+    constexpr int KSTEPS = D / 16;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t COL_S0 = 0, COL_S1 = 128, COL_O = 256;
+    constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
+    constexpr uint32_t IDESC_QK = umma_idesc(FMT, 128, 128, 0, 0);
+    constexpr uint32_t IDESC_PV = umma_idesc(FMT, 128, D, 0, 1);
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
+    const uint32_t sQ = sbase + L::oQ, sK = sbase + L::oK, sV = sbase + L::oV, sP = sbase + L::oP;
+    const uint32_t bars = sbase + L::oBar;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * B_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * B_COUNT + 8);
+    auto bar = [&](int i) { return bars + 8u * i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int mblk = gridDim.x - 1 - blockIdx.x;            // heavy (late) tiles first under a causal mask
+    int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
+    if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
+    const int m0 = mblk * 128;
+    if (m0 >= sq) return;
+    if (g_fwd_sm100_error) return;
+    const int hk = h / (a.hq / a.hkv);
+    const int wl = a.wl, wr = a.causal ? 0 : a.wr;
+    const int rows = min(128, sq - m0);
+
+    // key tiles this query tile touches
+    int lo_first, hi_first, lo_last, hi_last;
+    window_bounds(m0, sq, sk, wl, wr, lo_first, hi_first);
+    window_bounds(m0 + rows - 1, sq, sk, wl, wr, lo_last, hi_last);
+    int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
+    if (sk <= 0 || lo_first >= sk) { t_lo = 0; t_hi = 0; }
+    const int ntiles = max(0, t_hi - t_lo);
+
+    T* obase = reinterpret_cast<T*>(a.o) + (a.cu_q ? 0 : (int64_t)b * a.o_sb) + (int64_t)(q_off + m0) * a.o_ss + (int64_t)h * a.o_sh;
+    float* lbase = a.lse ? a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + (int64_t)(q_off + m0) * a.lse_ss : nullptr;
+
+    if (ntiles == 0) {                                      // nothing visible: O = 0, LSE = +inf
+        if (tid < rows) {
+            uint4 z = make_uint4(0, 0, 0, 0);
+            T* orow = obase + (int64_t)tid * a.o_ss;
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
+            if (lbase) lbase[(int64_t)tid * a.lse_ss] = INFINITY;
+        }
+        return;
+    }
+
+    if (tid == 0) {
+        for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), i == B_P ? 128u : 1u);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    int* err = &g_fwd_sm100_error;
+
+    const int qrow0 = (a.cu_q ? q_off : 0) + m0;            // TMA row coordinate of the query tile
+    const int qb = a.cu_q ? 0 : b;
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
+            mbar_expect_tx(bar(B_Q), L::kQ);
+#pragma unroll
+            for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + s * L::kSub, &a.tq, bar(B_Q), s * 64, h, qrow0, qb);
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int st = j & 1, use = j >> 1;
+                const int krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128;
+                if (use > 0) ok = mbar_wait(bar(B_KE0 + st), (use - 1) & 1, abort_flag, err, 1);
+                if (!ok) break;
+                mbar_expect_tx(bar(B_KF0 + st), L::kKV);
+#pragma unroll
+                for (int s = 0; s < NSUB; ++s) tma_load_4d(sK + st * L::kKV + s * L::kSub, &a.tk, bar(B_KF0 + st), s * 64, hk, krow, qb);
+                if (use > 0) ok = mbar_wait(bar(B_VE0 + st), (use - 1) & 1, abort_flag, err, 2);
+                if (!ok) break;
+                mbar_expect_tx(bar(B_VF0 + st), L::kKV);
+#pragma unroll
+                for (int s = 0; s < NSUB; ++s) tma_load_4d(sV + st * L::kKV + s * L::kSub, &a.tv, bar(B_VF0 + st), s * 64, hk, krow, qb);
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            bool ok = mbar_wait(bar(B_Q), 0, abort_flag, err, 3);
+            auto issue_pv = [&](int i) -> bool {
+                const int st = i & 1, use = i >> 1;
+                if (!mbar_wait(bar(B_P), i & 1, abort_flag, err, 4)) return false;
+                if (!mbar_wait(bar(B_VF0 + st), use & 1, abort_flag, err, 5)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint64_t bd = umma_desc(sV + st * L::kKV + kk * 2048, L::kSub, 1024);
+                    if (a.p_in_tmem) {
+                        umma_ts(tmem + COL_O, tmem + ((i & 1) ? COL_S1 : COL_S0) + kk * 8, bd, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
+                    } else {
+                        const uint64_t ad = umma_desc(sP + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
+                        umma_ss(tmem + COL_O, ad, bd, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
+                umma_commit(bar(B_VE0 + st));
+                umma_commit(bar(B_PV));
+                return true;
+            };
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int st = j & 1, use = j >> 1;
+                ok = mbar_wait(bar(B_KF0 + st), use & 1, abort_flag, err, 6);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_s = tmem + ((j & 1) ? COL_S1 : COL_S0);
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    const uint64_t ad = umma_desc(sQ + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
+                    const uint64_t bd = umma_desc(sK + st * L::kKV + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
+                    umma_ss(d_s, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(bar(B_KE0 + st));
+                umma_commit(bar(B_S0 + (j & 1)));
+                if (j > 0) ok = issue_pv(j - 1);
+            }
+            if (ok) issue_pv(ntiles - 1);
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax: thread = query row
+        const int r = tid;                                   // 0..127, TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const int qi = m0 + r;
+        int klo = 1, khi = 0;
+        if (r < rows) window_bounds(qi, sq, sk, wl, wr, klo, khi);
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int n0 = (t_lo + j) * 128;
+            ok = mbar_wait(bar(B_S0 + (j & 1)), (j >> 1) & 1, abort_flag, err, 7);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_s = tmem + lane_base + ((j & 1) ? COL_S1 : COL_S0);
+            uint32_t sreg[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
+            tmem_wait_ld();
+            const bool full = n0 >= lo_last && n0 + 127 <= hi_first;     // no masking needed anywhere in the tile
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x = __uint_as_float(sreg[c][i]) * a.scale_log2;
+                    if (!full) { const int col = n0 + c * 32 + i; x = (col >= klo && col <= khi) ? x : -INFINITY; }
+                    sreg[c][i] = __float_as_uint(x);
+                    mx = fmaxf(mx, x);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m_run - m_safe);
+            m_run = m_new;
+            float sum = 0.f;
+            uint32_t preg[64];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = exp2f(__uint_as_float(sreg[c][i]) - m_safe);
+                    const float p1 = exp2f(__uint_as_float(sreg[c][i + 1]) - m_safe);
+                    sum += p0 + p1;
+                    preg[c * 16 + i / 2] = Elem<T>::pack(p0, p1);
+                }
+            }
+            l_run = l_run * alpha + sum;
+            if (j > 0) {
+                ok = mbar_wait(bar(B_PV), (j - 1) & 1, abort_flag, err, 8);      // O holds tiles < j, P buffer is free
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, alpha < 1.f)) {
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t oreg[32];
+                        tmem_ld32(tmem + lane_base + COL_O + c * 32, oreg);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                        tmem_st32(tmem + lane_base + COL_O + c * 32, oreg);
+                    }
+                }
+            }
+            if (a.p_in_tmem) {
+                // P over the score buffer: 64 columns of packed pairs
+                uint32_t* pp = preg;
+                tmem_st32(t_s, *reinterpret_cast<uint32_t(*)[32]>(pp));
+                tmem_st32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(pp + 32));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {               // 16-byte chunk c holds keys 8c..8c+7
+                    const uint32_t addr = sP + (c >> 3) * L::kSub + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(preg[4 * c]), "r"(preg[4 * c + 1]),
+                                 "r"(preg[4 * c + 2]), "r"(preg[4 * c + 3]) : "memory");
+                }
+                fence_proxy_async_smem();
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(B_P));
+        }
+        if (ok) ok = mbar_wait(bar(B_PV), (ntiles - 1) & 1, abort_flag, err, 9);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            T* orow = obase + (int64_t)r * a.o_ss;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t oreg[32];
+                tmem_ld32(tmem + lane_base + COL_O + c * 32, oreg);
+                tmem_wait_ld();
+                if (r < rows) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 pk;
+                        pk.x = Elem<T>::pack(__uint_as_float(oreg[8 * v + 0]) * inv, __uint_as_float(oreg[8 * v + 1]) * inv);
+                        pk.y = Elem<T>::pack(__uint_as_float(oreg[8 * v + 2]) * inv, __uint_as_float(oreg[8 * v + 3]) * inv);
+                        pk.z = Elem<T>::pack(__uint_as_float(oreg[8 * v + 4]) * inv, __uint_as_float(oreg[8 * v + 5]) * inv);
+                        pk.w = Elem<T>::pack(__uint_as_float(oreg[8 * v + 6]) * inv, __uint_as_float(oreg[8 * v + 7]) * inv);
+                        reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
+                    }
+                }
+            }
+            if (r < rows && lbase) lbase[(int64_t)r * a.lse_ss] = l_run > 0.f ? (m_run + log2f(l_run)) * kLn2 : INFINITY;
+        }
+    }
+    // ---- teardown: nothing of this CTA may still touch tensor memory ------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// (dim, head, row, batch) view with a [64 x 1 x 128 x 1] box and 128-byte swizzle
+int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads, int64_t rows, int batch,
+                  int64_t stride_h, int64_t stride_s, int64_t stride_b, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)batch};
+    cuuint64_t strides[3] = {(cuuint64_t)stride_h * 2, (cuuint64_t)stride_s * 2, (cuuint64_t)stride_b * 2};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, dtype == FA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return FA_OK;
+}
+
+static int g_p_in_tmem = 0;
+void fwd_sm100_set_p_in_tmem(int v) { g_p_in_tmem = v; }
+
+bool fwd_sm100_supported(const fa_fwd_params& p) {
+    if (p.d != p.dv || (p.d != 64 && p.d != 128)) return false;
+    if (p.softcap > 0.f || p.alibi_slopes || p.block_table || p.seqused_k || p.cache_batch_idx) return false;
+    if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
+    if (p.kv_begin != 0 || p.kv_end > 0 || p.partials_only) return false;
+    if (p.sq <= 0 || p.sk <= 0) return false;
+    if (p.cu_seqlens_q && (p.total_q <= 0 || p.total_k <= 0)) return false;
+    const fa_tensor* ts[3] = {&p.q, &p.k, &p.v};
+    for (const fa_tensor* t : ts) {
+        if (t->stride_h <= 0 || t->stride_s <= 0) return false;
+        if (!p.cu_seqlens_q && p.b > 1 && t->stride_b <= 0) return false;
+    }
+    return encode_fn() != nullptr;
+}
+
+template <typename T, int D>
+static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
+    auto kern = fwd_sm100_kernel<T, D>;
+    const int smem = FwdSm100Smem<D>::kBytes + 1024;
+    if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+    dim3 grid((p.sq + 127) / 128, p.hq, p.b);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
+    kern<<<grid, 192, smem, st>>>(a);
+    mark_kernel(st);
+    return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
+}
+
+int launch_fwd_sm100(const fa_fwd_params& p) {
+    Sm100FwdArgs a;
+    const bool packed = p.cu_seqlens_q != nullptr;
+    const int64_t q_rows = packed ? p.total_q : p.sq;
+    const int64_t k_rows = packed ? p.total_k : p.sk;
+    const int nb = packed ? 1 : p.b;
+    auto bstride = [&](const fa_tensor& t, int64_t rows) { return packed || p.b == 1 ? rows * t.stride_s : t.stride_b; };
+    if (int e = make_tile_map(&a.tq, p.dtype, p.q.ptr, p.d, p.hq, q_rows, nb, p.q.stride_h, p.q.stride_s, bstride(p.q, q_rows), 128)) return e;
+    if (int e = make_tile_map(&a.tk, p.dtype, p.k.ptr, p.d, p.hkv, k_rows, nb, p.k.stride_h, p.k.stride_s, bstride(p.k, k_rows), 128)) return e;
+    if (int e = make_tile_map(&a.tv, p.dtype, p.v.ptr, p.d, p.hkv, k_rows, nb, p.v.stride_h, p.v.stride_s, bstride(p.v, k_rows), 128)) return e;
+    a.o = p.o.ptr; a.lse = p.lse;
+    a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
+    a.lse_sb = p.lse_stride_b; a.lse_sh = p.lse_stride_h; a.lse_ss = p.lse_stride_s;
+    a.cu_q = p.cu_seqlens_q; a.cu_k = p.cu_seqlens_k;
+    a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv;
+    a.scale_log2 = p.scale * kLog2e;
+    a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
+    a.p_in_tmem = g_p_in_tmem;
+    note_kernel(a.p_in_tmem ? "sm100_tcgen05_ts" : "sm100_tcgen05");
+    if (p.dtype == FA_F16) return p.d == 64 ? launch_sm100_t<__half, 64>(p, a) : launch_sm100_t<__half, 128>(p, a);
+    return p.d == 64 ? launch_sm100_t<__nv_bfloat16, 64>(p, a) : launch_sm100_t<__nv_bfloat16, 128>(p, a);
+}
+
+int sm100_error_flag(bool clear) {
+    int v = 0;
+    cudaMemcpyFromSymbol(&v, g_fwd_sm100_error, sizeof(int));
+    if (clear) { int z = 0; cudaMemcpyToSymbol(g_fwd_sm100_error, &z, sizeof(int)); }
+    return v;
+}
+
+}  // namespace fa

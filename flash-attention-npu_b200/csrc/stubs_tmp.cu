@@ -1,7 +1,5 @@
 #include "fa_internal.h"
 namespace fa {
-bool fwd_sm100_supported(const fa_fwd_params&) { return false; }
-int launch_fwd_sm100(const fa_fwd_params&) { return fail(FA_ERR_UNSUPPORTED, "n/a"); }
 int launch_fwd_decode(const fa_fwd_params&, const FwdPlan&, float*, float*) { return fail(FA_ERR_UNSUPPORTED, "n/a"); }
 bool bwd_sm100_supported(const fa_bwd_params&) { return false; }
 int launch_bwd_sm100(const fa_bwd_params&) { return fail(FA_ERR_UNSUPPORTED, "n/a"); }

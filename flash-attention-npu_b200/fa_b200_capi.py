@@ -22,7 +22,7 @@ class FwdParams(C.Structure):
         ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_k", C.c_void_p), ("seqused_k", C.c_void_p),
         ("block_table", C.c_void_p), ("block_table_stride", C.c_int64), ("page_size", C.c_int32),
         ("cache_batch_idx", C.c_void_p), ("alibi_slopes", C.c_void_p), ("alibi_stride_b", C.c_int64),
-        ("b", C.c_int32), ("sq", C.c_int32), ("sk", C.c_int32), ("total_q", C.c_int32),
+        ("b", C.c_int32), ("sq", C.c_int32), ("sk", C.c_int32), ("total_q", C.c_int32), ("total_k", C.c_int32),
         ("hq", C.c_int32), ("hkv", C.c_int32), ("d", C.c_int32), ("dv", C.c_int32),
         ("scale", C.c_float), ("softcap", C.c_float),
         ("causal", C.c_int32), ("window_left", C.c_int32), ("window_right", C.c_int32), ("dtype", C.c_int32),
@@ -106,6 +106,10 @@ EXPORTS = {
     "fa_version": (C.c_char_p, []),
     "fa_last_kernel": (C.c_char_p, []),
     "fa_set_kernel_policy": (None, [C.c_int]),
+    "fa_debug_set": (None, [C.c_int, C.c_int]),
+    "fa_debug_get": (C.c_int, [C.c_int]),
+    "fa_set_kernel_events": (None, [C.POINTER(C.c_void_p), C.c_int]),
+    "fa_kernel_events_used": (C.c_int, []),
 }
 
 

@@ -142,6 +142,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k_, leftpad_k_
     p.lse_stride_b, p.lse_stride_h, p.lse_stride_s = 0, lse.stride(0), lse.stride(1)
     p.cu_seqlens_q, p.cu_seqlens_k = cu_seqlens_q.data_ptr(), ptr(cu_seqlens_k)
     p.b, p.sq, p.sk, p.total_q = batch, max_seqlen_q, max_seqlen_k, total_q
+    p.total_k = 0 if paged else k.shape[0]
     p.hq, p.hkv, p.d, p.dv = hq, hkv, d, v.size(-1)
     p.scale, p.softcap = softmax_scale, softcap
     p.causal, p.window_left, p.window_right = int(is_causal), window_size_left, window_size_right

@@ -77,6 +77,7 @@ typedef struct {
 
     int32_t b, sq, sk;             /* sq/sk: max lengths for varlen / cache            */
     int32_t total_q;               /* rows of a packed q tensor (cu_seqlens_q != null) */
+    int32_t total_k;               /* rows of a packed k/v tensor (cu_seqlens_k != null) */
     int32_t hq, hkv, d, dv;
     float   scale, softcap;
     int32_t causal, window_left, window_right;
@@ -216,6 +217,19 @@ const char* fa_version(void);
 const char* fa_last_kernel(void);
 /* Force the kernel family: 0 = automatic, 1 = generic tensor-core kernels only. */
 void        fa_set_kernel_policy(int policy);
+
+/* Debug switches and status, for tests: key 1 = keep P in tensor memory for the second MMA of the
+ * tcgen05 forward (set), key 2 = error code left by a timed-out wait in a tcgen05 kernel (get;
+ * synchronises the device), key 3 = clear that code (set). */
+void        fa_debug_set(int key, int value);
+int         fa_debug_get(int key);
+
+/* Per-kernel timing for benchmarks: lend `count` cudaEvent_t handles (created with timing
+ * enabled) to the calling thread.  The next forward / backward call records events[0] before
+ * its first launch and one more event after every kernel it launches, on the call's stream;
+ * fa_kernel_events_used() tells how many were recorded.  Pass (NULL, 0) to stop. */
+void        fa_set_kernel_events(void** events, int count);
+int         fa_kernel_events_used(void);
 
 #ifdef __cplusplus
 }

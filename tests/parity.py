@@ -2,14 +2,33 @@
 
 Tolerance (stated with every check): max-abs error against the oracle run in fp32 must not
 exceed 2 x max-abs(oracle in the low-precision dtype - oracle in fp32) on the same inputs,
-with a floor of 1e-5 * max(1, max|LSE|) for LSE (the oracle's own LSE error is exactly 0
-because it computes scores and the row sum in fp32 in both modes) and 1e-5 for tensors."""
+with two floors: for LSE 1e-5 * max(1, max|LSE|) (the oracle's own LSE error is exactly 0
+because it computes scores and the row sum in fp32 in both modes; 4 x that floor is allowed),
+and for tensors half a unit in the last place of the output dtype at the tensor's largest
+magnitude (one rounding of a correct result to bf16 / fp16 can be that far from fp32, and the
+oracle's own maximum is a sample of the same rounding noise)."""
+import math
+
 import torch
 
 from oracle import attention_oracle as orc
 
 
-def assert_within(name, got, ref_lp, ref32, floor=orc.ABS_FLOOR, slack=1.0):
+def half_ulp(dtype, magnitude):
+    bits = {torch.bfloat16: 8, torch.float16: 11}.get(dtype)
+    if bits is None or magnitude <= 0:
+        return 0.0
+    return 2.0 ** (math.floor(math.log2(magnitude)) - bits)
+
+
+def assert_within(name, got, ref_lp, ref32, floor=orc.ABS_FLOOR, slack=1.0, roundings=1):
+    """`roundings`: how many low-precision roundings sit between fp32 truth and the result that the
+    oracle does not share: 1 for the forward (the output cast), 2 for the backward (the kernels, like
+    the reference's device code fag_epilogue_op.hpp:1394/:1480, round P and dS to the input dtype before
+    the second GEMMs while the float64 golden does not, then cast the output)."""
+    fin = torch.isfinite(ref32)
+    mag = ref32[fin].abs().max().item() if fin.any() else 0.0
+    floor = max(floor, roundings * half_ulp(got.dtype, mag))
     tol = orc.tolerance(ref_lp, ref32, floor) * slack
     err = orc.max_abs_err(got.detach().cpu(), ref32)
     assert err <= tol, f"{name}: max-abs err {err:.3e} > tol {tol:.3e} (2 x oracle lp-vs-fp32 error)"
