@@ -307,6 +307,316 @@ __global__ void __launch_bounds__(192, 1) fwd_sm100_kernel(const __grid_constant
     }
 }
 
+
+// =================================================================================================
+// Two query tiles per CTA (256 rows), P kept in tensor memory.
+//   warps 0-3 / 4-7   softmax of query tile A / B (thread = row, TMEM lane = warp % 4 * 32 + lane)
+//   warp 8            TMA producer and TMEM allocation
+//   warp 9            MMA issuer
+// Tensor memory: S_A | S_B | O_A | O_B, 128 columns each.  P (16-bit pairs) overwrites the first 64
+// columns of its score buffer and feeds the second MMA as the A operand straight from TMEM.
+// The two tiles ping-pong: while tile A is in softmax the tensor core runs P_B V and Q_B K^T, and
+// vice versa.  The running max used as exponent base is only moved when the true max has grown by
+// more than 2^8 (the accumulator is rescaled then), so rescaling O is rare and stays in the
+// softmax warps.
+// =================================================================================================
+template <int D>
+struct FwdSm100Smem2 {
+    static constexpr int kSub = 128 * 128;
+    static constexpr int kQ = (D / 64) * kSub;              // one query tile
+    static constexpr int kKV = (D / 64) * kSub;
+    static constexpr int oQ = 0;                            // 2 tiles
+    static constexpr int oK = oQ + 2 * kQ;                  // 2 stages
+    static constexpr int oV = oK + 2 * kKV;                 // 2 stages
+    static constexpr int oBar = oV + 2 * kKV;
+    static constexpr int kBytes = oBar + 256;
+};
+
+enum { C_Q = 0, C_KF0, C_KF1, C_KE0, C_KE1, C_VF0, C_VF1, C_VE0, C_VE1, C_SA, C_SB, C_PA, C_PB, C_OA, C_OB, C_COUNT };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constant__ Sm100FwdArgs a) {
+    using L = FwdSm100Smem2<D>;
+    constexpr int NSUB = D / 64;
+    constexpr int KSTEPS = D / 16;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
+    constexpr uint32_t IDESC_QK = umma_idesc(FMT, 128, 128, 0, 0);
+    constexpr uint32_t IDESC_PV = umma_idesc(FMT, 128, D, 0, 1);
+    constexpr float kRescaleThreshold = 8.f;
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
+    const uint32_t sQ = sbase + L::oQ, sK = sbase + L::oK, sV = sbase + L::oV;
+    const uint32_t bars = sbase + L::oBar;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * C_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * C_COUNT + 8);
+    auto bar = [&](int i) { return bars + 8u * i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int mblk = gridDim.x - 1 - blockIdx.x;
+    int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
+    if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
+    const int m0 = mblk * 256;
+    if (m0 >= sq) return;
+    if (g_fwd_sm100_error) return;
+    const int hk = h / (a.hq / a.hkv);
+    const int wl = a.wl, wr = a.causal ? 0 : a.wr;
+    const int rows_cta = min(256, sq - m0);
+    const bool has_b = rows_cta > 128;
+
+    int lo_first, hi_first, lo_last, hi_last;
+    window_bounds(m0, sq, sk, wl, wr, lo_first, hi_first);
+    window_bounds(m0 + rows_cta - 1, sq, sk, wl, wr, lo_last, hi_last);
+    int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
+    if (sk <= 0 || lo_first >= sk) { t_lo = 0; t_hi = 0; }
+    const int ntiles = max(0, t_hi - t_lo);
+
+    T* obase = reinterpret_cast<T*>(a.o) + (a.cu_q ? 0 : (int64_t)b * a.o_sb) + (int64_t)(q_off + m0) * a.o_ss + (int64_t)h * a.o_sh;
+    float* lbase = a.lse ? a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + (int64_t)(q_off + m0) * a.lse_ss : nullptr;
+
+    if (ntiles == 0) {
+        if (tid < rows_cta) {
+            uint4 z = make_uint4(0, 0, 0, 0);
+            T* orow = obase + (int64_t)tid * a.o_ss;
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
+            if (lbase) lbase[(int64_t)tid * a.lse_ss] = INFINITY;
+        }
+        return;
+    }
+
+    if (tid == 0) {
+        for (int i = 0; i < C_COUNT; ++i) mbar_init(bar(i), (i == C_PA || i == C_PB) ? 128u : 1u);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    int* err = &g_fwd_sm100_error;
+    const int qrow0 = (a.cu_q ? q_off : 0) + m0;
+    const int qb = a.cu_q ? 0 : b;
+
+    if (warp == 8) {
+        if (lane == 0) {
+            tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
+            mbar_expect_tx(bar(C_Q), has_b ? 2 * L::kQ : L::kQ);
+#pragma unroll
+            for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, h, qrow0, qb);
+            if (has_b) {
+#pragma unroll
+                for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + L::kQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, h, qrow0 + 128, qb);
+            }
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int st = j & 1, use = j >> 1;
+                const int krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128;
+                if (use > 0) ok = mbar_wait(bar(C_KE0 + st), (use - 1) & 1, abort_flag, err, 1);
+                if (!ok) break;
+                mbar_expect_tx(bar(C_KF0 + st), L::kKV);
+#pragma unroll
+                for (int s = 0; s < NSUB; ++s) tma_load_4d(sK + st * L::kKV + s * L::kSub, &a.tk, bar(C_KF0 + st), s * 64, hk, krow, qb);
+                if (use > 0) ok = mbar_wait(bar(C_VE0 + st), (use - 1) & 1, abort_flag, err, 2);
+                if (!ok) break;
+                mbar_expect_tx(bar(C_VF0 + st), L::kKV);
+#pragma unroll
+                for (int s = 0; s < NSUB; ++s) tma_load_4d(sV + st * L::kKV + s * L::kSub, &a.tv, bar(C_VF0 + st), s * 64, hk, krow, qb);
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0) {
+            auto issue_qk = [&](int x, int st) {
+                const uint32_t d_s = tmem + x * 128;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    const uint64_t ad = umma_desc(sQ + x * L::kQ + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
+                    const uint64_t bd = umma_desc(sK + st * L::kKV + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
+                    umma_ss(d_s, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(bar(C_SA + x));
+            };
+            auto issue_pv = [&](int x, int st, int j) {
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint64_t bd = umma_desc(sV + st * L::kKV + kk * 2048, L::kSub, 1024);
+                    umma_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8, bd, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+            };
+            bool ok = mbar_wait(bar(C_Q), 0, abort_flag, err, 3);
+            if (ok) ok = mbar_wait(bar(C_KF0), 0, abort_flag, err, 4);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0, 0);
+                if (has_b) issue_qk(1, 0);
+                umma_commit(bar(C_KE0));
+            }
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int st = j & 1, use = j >> 1;
+                const bool more = j + 1 < ntiles;
+                const int st1 = (j + 1) & 1, use1 = (j + 1) >> 1;
+                ok = mbar_wait(bar(C_PA), j & 1, abort_flag, err, 5);
+                if (ok) ok = mbar_wait(bar(C_VF0 + st), use & 1, abort_flag, err, 6);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(0, st, j);
+                if (more) {
+                    ok = mbar_wait(bar(C_KF0 + st1), use1 & 1, abort_flag, err, 7);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(0, st1);
+                } else {
+                    umma_commit(bar(C_OA));
+                }
+                if (has_b) {
+                    ok = mbar_wait(bar(C_PB), j & 1, abort_flag, err, 8);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(1, st, j);
+                }
+                umma_commit(bar(C_VE0 + st));
+                if (more) {
+                    if (has_b) issue_qk(1, st1);
+                    umma_commit(bar(C_KE0 + st1));
+                } else if (has_b) {
+                    umma_commit(bar(C_OB));
+                }
+            }
+        }
+    } else if (warp < 4 || has_b) {
+        // ---------------------------------------------------------------- softmax of tile x
+        const int x = warp >> 2;
+        const int r = tid & 127;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t t_s = tmem + lane_base + x * 128;
+        const uint32_t t_o = tmem + lane_base + 256 + x * 128;
+        const int rows = min(128, rows_cta - x * 128);
+        const int qi = m0 + x * 128 + r;
+        int klo = 1, khi = 0;
+        if (r < rows) window_bounds(qi, sq, sk, wl, wr, klo, khi);
+        int lo_l, hi_f, tmp;
+        window_bounds(m0 + x * 128, sq, sk, wl, wr, tmp, hi_f);
+        window_bounds(m0 + x * 128 + rows - 1, sq, sk, wl, wr, lo_l, tmp);
+        float m_used = -INFINITY, l_run = 0.f;
+        const float sc = a.scale_log2;
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int n0 = (t_lo + j) * 128;
+            ok = mbar_wait(bar(C_SA + x), j & 1, abort_flag, err, 9);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sreg[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
+            tmem_wait_ld();
+            const bool full = n0 >= lo_l && n0 + 127 <= hi_f;
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            if (!full) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int col = n0 + c * 32 + i;
+                        if (col < klo || col > khi) sreg[c][i] = 0xff800000u;     // -inf
+                    }
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(sreg[c][i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(sreg[c][i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(sreg[c][i + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(sreg[c][i + 3]));
+                }
+            }
+            const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;       // log2 domain
+            if (m_used == -INFINITY) m_used = m_new;
+            if (j > 0 && __any_sync(0xffffffffu, m_new > m_used + kRescaleThreshold)) {
+                const float m_next = fmaxf(m_used, m_new);
+                const float alpha = m_used == -INFINITY ? 1.f : ex2_approx(m_used - m_next);
+                m_used = m_next;
+                l_run *= alpha;
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t oreg[32];
+                    tmem_ld32(t_o + c * 32, oreg);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                    tmem_st32(t_o + c * 32, oreg);
+                }
+            }
+            const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+                uint32_t preg[32];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = ex2_approx(fmaf(__uint_as_float(sreg[2 * hlf + c][i]), sc, neg_m));
+                        const float p1 = ex2_approx(fmaf(__uint_as_float(sreg[2 * hlf + c][i + 1]), sc, neg_m));
+                        s0 += p0;
+                        s1 += p1;
+                        preg[c * 16 + i / 2] = Elem<T>::pack(p0, p1);
+                    }
+                }
+                tmem_st32(t_s + hlf * 32, preg);
+            }
+            l_run += s0 + s1;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(C_PA + x));
+        }
+        if (ok) ok = mbar_wait(bar(C_OA + x), 0, abort_flag, err, 10);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            T* orow = obase + (int64_t)(x * 128 + r) * a.o_ss;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t oreg[32];
+                tmem_ld32(t_o + c * 32, oreg);
+                tmem_wait_ld();
+                if (r < rows) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 pk;
+                        pk.x = Elem<T>::pack(__uint_as_float(oreg[8 * v + 0]) * inv, __uint_as_float(oreg[8 * v + 1]) * inv);
+                        pk.y = Elem<T>::pack(__uint_as_float(oreg[8 * v + 2]) * inv, __uint_as_float(oreg[8 * v + 3]) * inv);
+                        pk.z = Elem<T>::pack(__uint_as_float(oreg[8 * v + 4]) * inv, __uint_as_float(oreg[8 * v + 5]) * inv);
+                        pk.w = Elem<T>::pack(__uint_as_float(oreg[8 * v + 6]) * inv, __uint_as_float(oreg[8 * v + 7]) * inv);
+                        reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
+                    }
+                }
+            }
+            if (r < rows && lbase) lbase[(int64_t)(x * 128 + r) * a.lse_ss] = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : INFINITY;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -339,15 +649,17 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
     return FA_OK;
 }
 
-static int g_p_in_tmem = 0;
-void fwd_sm100_set_p_in_tmem(int v) { g_p_in_tmem = v; }
+// 0: one query tile per CTA, P through shared memory; 1: same with P in tensor memory;
+// 2: two query tiles per CTA, P in tensor memory (default)
+static int g_variant = 2;
+void fwd_sm100_set_p_in_tmem(int v) { g_variant = v; }
 
 bool fwd_sm100_supported(const fa_fwd_params& p) {
     if (p.d != p.dv || (p.d != 64 && p.d != 128)) return false;
     if (p.softcap > 0.f || p.alibi_slopes || p.block_table || p.seqused_k || p.cache_batch_idx) return false;
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
     if (p.kv_begin != 0 || p.kv_end > 0 || p.partials_only) return false;
-    if (p.sq <= 0 || p.sk <= 0) return false;
+    if (p.sq <= 0 || p.sk <= 0 || !(p.scale > 0.f)) return false;
     if (p.cu_seqlens_q && (p.total_q <= 0 || p.total_k <= 0)) return false;
     const fa_tensor* ts[3] = {&p.q, &p.k, &p.v};
     for (const fa_tensor* t : ts) {
@@ -359,12 +671,20 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
 
 template <typename T, int D>
 static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
-    auto kern = fwd_sm100_kernel<T, D>;
-    const int smem = FwdSm100Smem<D>::kBytes + 1024;
-    if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-    dim3 grid((p.sq + 127) / 128, p.hq, p.b);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
-    kern<<<grid, 192, smem, st>>>(a);
+    if (g_variant == 2) {
+        auto kern = fwd_sm100_kernel2<T, D>;
+        const int smem = FwdSm100Smem2<D>::kBytes + 1024;
+        if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+        dim3 grid((p.sq + 255) / 256, p.hq, p.b);
+        kern<<<grid, 320, smem, st>>>(a);
+    } else {
+        auto kern = fwd_sm100_kernel<T, D>;
+        const int smem = FwdSm100Smem<D>::kBytes + 1024;
+        if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+        dim3 grid((p.sq + 127) / 128, p.hq, p.b);
+        kern<<<grid, 192, smem, st>>>(a);
+    }
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
 }
@@ -386,8 +706,8 @@ int launch_fwd_sm100(const fa_fwd_params& p) {
     a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv;
     a.scale_log2 = p.scale * kLog2e;
     a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
-    a.p_in_tmem = g_p_in_tmem;
-    note_kernel(a.p_in_tmem ? "sm100_tcgen05_ts" : "sm100_tcgen05");
+    a.p_in_tmem = g_variant == 1;
+    note_kernel(g_variant == 2 ? "sm100_tcgen05_2q" : g_variant == 1 ? "sm100_tcgen05_ts" : "sm100_tcgen05");
     if (p.dtype == FA_F16) return p.d == 64 ? launch_sm100_t<__half, 64>(p, a) : launch_sm100_t<__half, 128>(p, a);
     return p.d == 64 ? launch_sm100_t<__nv_bfloat16, 64>(p, a) : launch_sm100_t<__nv_bfloat16, 128>(p, a);
 }

@@ -23,9 +23,10 @@ def half_ulp(dtype, magnitude):
 
 def assert_within(name, got, ref_lp, ref32, floor=orc.ABS_FLOOR, slack=1.0, roundings=1):
     """`roundings`: how many low-precision roundings sit between fp32 truth and the result that the
-    oracle does not share: 1 for the forward (the output cast), 2 for the backward (the kernels, like
-    the reference's device code fag_epilogue_op.hpp:1394/:1480, round P and dS to the input dtype before
-    the second GEMMs while the float64 golden does not, then cast the output)."""
+    oracle does not share: 1 for the forward (the output cast), 3 for the backward: the kernels, like
+    the reference's device code (fag_epilogue_op.hpp:1394, :1480), round P and dS to the input dtype
+    before the second GEMMs and read the forward's already rounded O for D = rowsum(dO o O), while the
+    float64 golden does none of that; then the output cast."""
     fin = torch.isfinite(ref32)
     mag = ref32[fin].abs().max().item() if fin.any() else 0.0
     floor = max(floor, roundings * half_ulp(got.dtype, mag))
