@@ -91,6 +91,8 @@ EXPORTS = {
     "fa_fwd": (C.c_int, [C.POINTER(FwdParams)]),
     "fa_varlen_fwd": (C.c_int, [C.POINTER(FwdParams)]),
     "fa_fwd_kvcache": (C.c_int, [C.POINTER(FwdParams)]),
+    "fa_fwd_kvcache_static": (C.c_int, [C.POINTER(FwdParams)]),
+    "fa_static_scratch_bytes": (C.c_size_t, []),
     "fa_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(FwdParams)]),
     "fa_fwd_num_splits": (C.c_int, [C.POINTER(FwdParams)]),
     "fa_bwd": (C.c_int, [C.POINTER(BwdParams)]),

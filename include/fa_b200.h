@@ -107,6 +107,15 @@ typedef struct {
 int    fa_fwd(const fa_fwd_params* p);
 int    fa_varlen_fwd(const fa_fwd_params* p);
 int    fa_fwd_kvcache(const fa_fwd_params* p);
+/* The same call for hosts that cannot provide scratch memory (a sealed memory pool, a plugin that
+ * must not allocate inside a step).  No counterpart in the reference, which allocates its workspace
+ * inside the op.  `workspace` / `workspace_bytes` are ignored; scratch comes from a 64 MiB pool built
+ * into the library (fa_static_scratch_bytes()), present on every GPU that loads it.  Calls needing
+ * more are refused with FA_ERR_WORKSPACE.  Allocates nothing.  The first call on a device resolves
+ * the pool's address and should happen before any stream capture.  All calls share the pool:
+ * calls that overlap on the GPU race; keep them ordered on one stream. */
+int    fa_fwd_kvcache_static(const fa_fwd_params* p);
+size_t fa_static_scratch_bytes(void);
 size_t fa_fwd_workspace_bytes(const fa_fwd_params* p);
 /* Number of KV splits the library will use for these parameters (>= 1). */
 int    fa_fwd_num_splits(const fa_fwd_params* p);
