@@ -1,0 +1,571 @@
+// Backward attention on Blackwell tensor cores (tcgen05 + TMEM + TMA), sm_100a.
+//
+// Two kernels after the delta pass (D = rowsum(dO o O)), no atomics, fixed accumulation order:
+//
+//  dK/dV kernel   one CTA per (128-key tile, KV head, batch) walks the 128-row query tiles of every
+//                 head of the group.  Scores are computed transposed so that keys sit on the TMEM
+//                 lanes:  S^T = K Q^T, dP^T = V dO^T.  One thread per key row turns them into
+//                 P^T = exp(S^T - LSE) and dS^T = P^T o (dP^T - D) (rounded to the input type, written
+//                 back over the score columns), which feed dV += P^T dO and dK += dS^T Q as the
+//                 TMEM-resident A operand.  dK and dV stay in TMEM across all query tiles and heads.
+//  dQ kernel      one CTA per (128-row query tile, head, batch) walks the key tiles:
+//                 S = Q K^T, dP = dO V^T, dS = P o (dP - D), dQ += dS K.
+//
+// Math as the reference's backward (fag_kernel.cpp:400-465, fag_epilogue_op.hpp:1287-1322, :1394,
+// :1447-1480, fag_epilogue_post.hpp:149-200): P and dS rounded before the second GEMMs, dQ and dK
+// multiplied by the softmax scale at the end.  Tensor memory: S | dP | acc | acc (128 columns each).
+// Warps 0-7 do the element-wise work (thread = TMEM lane, each warpgroup takes 64 of the 128 score
+// columns), warp 8 is the TMA producer, warp 9 issues the MMAs.  All waits are bounded.
+#include "fa_utils.cuh"
+#include "fa_internal.h"
+#include "sm100_ptx.cuh"
+
+namespace fa {
+
+using namespace sm100;
+
+__device__ int g_bwd_sm100_error = 0;
+
+int bwd_sm100_error_flag(bool clear) {
+    int v = 0;
+    cudaMemcpyFromSymbol(&v, g_bwd_sm100_error, sizeof(int));
+    if (clear) { int z = 0; cudaMemcpyToSymbol(g_bwd_sm100_error, &z, sizeof(int)); }
+    return v;
+}
+
+struct alignas(64) Sm100BwdArgs {
+    CUtensorMap tq, tdo, tk, tv;
+    void *dq, *dk, *dv;
+    int64_t dq_sb, dq_ss, dq_sh, dk_sb, dk_ss, dk_sh, dv_sb, dv_ss, dv_sh;
+    const float* lse;
+    int64_t lse_sb, lse_sh, lse_ss;
+    const float* delta;                 // [token][head]
+    const int32_t* cu_q;
+    const int32_t* cu_k;
+    int b, sq, sk, hq, hkv;
+    float scale, scale_log2;
+    int causal, wl, wr;
+};
+
+template <int D>
+struct BwdSm100Smem {
+    static constexpr int kSub = 128 * 128;
+    static constexpr int kTileB = (D / 64) * kSub;          // one [128][D] tile
+    static constexpr int oFix0 = 0;                         // K (dkdv) or Q (dq)
+    static constexpr int oFix1 = oFix0 + kTileB;            // V (dkdv) or dO (dq)
+    static constexpr int oRing0 = oFix1 + kTileB;           // 2 stages: Q (dkdv) or K (dq)
+    static constexpr int oRing1 = oRing0 + 2 * kTileB;      // 2 stages: dO (dkdv) or V (dq)
+    static constexpr int oVec = oRing1 + 2 * kTileB;        // per warp: 2 stages x (64 lse2 + 64 delta) floats
+    static constexpr int oBar = oVec + 8 * 256 * 4;
+    static constexpr int kBytes = oBar + 256;
+};
+
+enum { E_FIX = 0, E_RF0, E_RF1, E_RE0, E_RE1, E_S, E_P, E_ACC, E_COUNT };
+
+template <typename T>
+__device__ __forceinline__ void store_row_scaled(T* dst, const uint32_t (&r)[32], float s) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        uint4 pk;
+        pk.x = Elem<T>::pack(__uint_as_float(r[8 * v + 0]) * s, __uint_as_float(r[8 * v + 1]) * s);
+        pk.y = Elem<T>::pack(__uint_as_float(r[8 * v + 2]) * s, __uint_as_float(r[8 * v + 3]) * s);
+        pk.z = Elem<T>::pack(__uint_as_float(r[8 * v + 4]) * s, __uint_as_float(r[8 * v + 5]) * s);
+        pk.w = Elem<T>::pack(__uint_as_float(r[8 * v + 6]) * s, __uint_as_float(r[8 * v + 7]) * s);
+        reinterpret_cast<uint4*>(dst)[v] = pk;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// dK / dV
+// ------------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(320, 1) bwd_dkdv_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
+    using L = BwdSm100Smem<D>;
+    constexpr int NSUB = D / 64, KSTEPS = D / 16;
+    constexpr uint32_t TMEM_COLS = 512, COL_ST = 0, COL_DPT = 128, COL_DK = 256, COL_DV = 384;
+    constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
+    constexpr uint32_t IDESC_ST = umma_idesc(FMT, 128, 128, 0, 0);
+    constexpr uint32_t IDESC_ACC = umma_idesc(FMT, 128, D, 0, 1);
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
+    const uint32_t sK = sbase + L::oFix0, sV = sbase + L::oFix1, sQ = sbase + L::oRing0, sdO = sbase + L::oRing1;
+    float* sVec = reinterpret_cast<float*>(sgen + L::oVec);
+    const uint32_t bars = sbase + L::oBar;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * E_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * E_COUNT + 8);
+    auto bar = [&](int i) { return bars + 8u * i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.z, hk = blockIdx.y, n0 = blockIdx.x * 128;
+    int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
+    if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
+    if (n0 >= sk) return;
+    if (g_bwd_sm100_error) return;
+    const int G = a.hq / a.hkv;
+    const int wl = a.wl, wr = a.causal ? 0 : a.wr;
+    const int diff = sk - sq;
+    const int krows = min(128, sk - n0);
+
+    int i_lo = 0, i_hi = sq - 1;
+    if (wr >= 0) i_lo = max(0, n0 - diff - wr);
+    if (wl >= 0) i_hi = min(sq - 1, n0 + krows - 1 + wl - diff);
+    const int mb_lo = i_lo / 128, mb_hi = i_hi >= i_lo ? i_hi / 128 + 1 : mb_lo;
+    const int nmb = mb_hi - mb_lo;
+    const int steps = nmb * G;
+
+    T* dkb = reinterpret_cast<T*>(a.dk) + (a.cu_q ? 0 : (int64_t)b * a.dk_sb) + (int64_t)(k_off + n0) * a.dk_ss + (int64_t)hk * a.dk_sh;
+    T* dvb = reinterpret_cast<T*>(a.dv) + (a.cu_q ? 0 : (int64_t)b * a.dv_sb) + (int64_t)(k_off + n0) * a.dv_ss + (int64_t)hk * a.dv_sh;
+
+    if (steps == 0) {                                       // no query sees these keys
+        if (tid < 256) {
+            const int r = tid & 127;
+            T* row = (tid < 128 ? dkb + (int64_t)r * a.dk_ss : dvb + (int64_t)r * a.dv_ss);
+            if (r < krows) {
+                const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(row)[c] = z;
+            }
+        }
+        return;
+    }
+
+    if (tid == 0) {
+        for (int i = 0; i < E_COUNT; ++i) mbar_init(bar(i), i == E_P ? 256u : 1u);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 8) { tmem_alloc(smem_addr(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    int* err = &g_bwd_sm100_error;
+    const int bb = a.cu_q ? 0 : b;
+
+    if (warp == 8) {
+        if (lane == 0) {
+            tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tdo); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
+            mbar_expect_tx(bar(E_FIX), 2 * L::kTileB);
+            const int krow = (a.cu_q ? k_off : 0) + n0;
+#pragma unroll
+            for (int s = 0; s < NSUB; ++s) {
+                tma_load_4d(sK + s * L::kSub, &a.tk, bar(E_FIX), s * 64, hk, krow, bb);
+                tma_load_4d(sV + s * L::kSub, &a.tv, bar(E_FIX), s * 64, hk, krow, bb);
+            }
+            bool ok = true;
+            for (int s = 0; s < steps && ok; ++s) {
+                const int st = s & 1, use = s >> 1;
+                const int h = hk * G + s / nmb;
+                const int qrow = (a.cu_q ? q_off : 0) + (mb_lo + s % nmb) * 128;
+                if (use > 0) ok = mbar_wait(bar(E_RE0 + st), (use - 1) & 1, abort_flag, err, 21);
+                if (!ok) break;
+                mbar_expect_tx(bar(E_RF0 + st), 2 * L::kTileB);
+#pragma unroll
+                for (int c = 0; c < NSUB; ++c) {
+                    tma_load_4d(sQ + st * L::kTileB + c * L::kSub, &a.tq, bar(E_RF0 + st), c * 64, h, qrow, bb);
+                    tma_load_4d(sdO + st * L::kTileB + c * L::kSub, &a.tdo, bar(E_RF0 + st), c * 64, h, qrow, bb);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0) {
+            bool ok = mbar_wait(bar(E_FIX), 0, abort_flag, err, 22);
+            for (int s = 0; s < steps && ok; ++s) {
+                const int st = s & 1, use = s >> 1;
+                ok = mbar_wait(bar(E_RF0 + st), use & 1, abort_flag, err, 23);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {       // S^T = K Q^T
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss(tmem + COL_ST, umma_desc(sK + off, 16, 1024), umma_desc(sQ + st * L::kTileB + off, 16, 1024), IDESC_ST, kk > 0);
+                }
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {       // dP^T = V dO^T
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss(tmem + COL_DPT, umma_desc(sV + off, 16, 1024), umma_desc(sdO + st * L::kTileB + off, 16, 1024), IDESC_ST, kk > 0);
+                }
+                umma_commit(bar(E_S));
+                ok = mbar_wait(bar(E_P), s & 1, abort_flag, err, 24);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {            // dV += P^T dO, dK += dS^T Q  (K = 128 query rows)
+                    const uint32_t pcol = (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
+                    umma_ts(tmem + COL_DV, tmem + COL_ST + pcol, umma_desc(sdO + st * L::kTileB + kk * 2048, L::kSub, 1024), IDESC_ACC, (s > 0 || kk > 0));
+                }
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t pcol = (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
+                    umma_ts(tmem + COL_DK, tmem + COL_DPT + pcol, umma_desc(sQ + st * L::kTileB + kk * 2048, L::kSub, 1024), IDESC_ACC, (s > 0 || kk > 0));
+                }
+                umma_commit(bar(E_RE0 + st));
+            }
+            if (ok) umma_commit(bar(E_ACC));
+        }
+    } else {
+        // ------------------------------------------------------------ element-wise: thread = key row
+        const int g = warp >> 2;                             // which 64 query columns
+        const int r = tid & 127;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const int n = n0 + r;
+        // query rows that see key n: [qi_lo, qi_hi]
+        int qi_lo = 0, qi_hi = sq - 1;
+        if (wr >= 0) qi_lo = max(0, n - diff - wr);
+        if (wl >= 0) qi_hi = min(sq - 1, n + wl - diff);
+        if (n >= sk) { qi_lo = 1; qi_hi = 0; }
+        bool ok = true;
+        for (int s = 0; s < steps && ok; ++s) {
+            const int h = hk * G + s / nmb;
+            const int i0 = (mb_lo + s % nmb) * 128;
+            // Each warp stages the LSE (log2 domain) and delta of its 64 query columns in its own slice
+            // of shared memory: lanes load two columns each, then only a warp-level sync is needed.
+            float* vec = sVec + warp * 256 + (s & 1) * 128;          // [0,64) lse2, [64,128) delta
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int c = lane + 32 * t;
+                const int i = i0 + g * 64 + c;
+                float l2 = INFINITY, dl = 0.f;
+                if (i < sq) {
+                    const int64_t tok = (int64_t)q_off + i;
+                    l2 = a.lse[(a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + tok * a.lse_ss] * kLog2e;
+                    dl = a.delta[((a.cu_q ? tok : (int64_t)b * a.sq + i)) * a.hq + h];
+                }
+                vec[c] = l2;
+                vec[64 + c] = dl;
+            }
+            __syncwarp();
+            ok = mbar_wait(bar(E_S), s & 1, abort_flag, err, 25);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t pP[32], pS[32];
+#pragma unroll
+            for (int c4 = 0; c4 < 2; ++c4) {
+                uint32_t sr[32], dr[32];
+                tmem_ld32(tmem + lane_base + COL_ST + g * 64 + c4 * 32, sr);
+                tmem_ld32(tmem + lane_base + COL_DPT + g * 64 + c4 * 32, dr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int lc = c4 * 32 + i;
+                    const int c = g * 64 + lc;
+                    const float2 l2 = *reinterpret_cast<const float2*>(vec + lc);
+                    const float2 dl = *reinterpret_cast<const float2*>(vec + 64 + lc);
+                    float p0 = ex2_approx(fmaf(__uint_as_float(sr[i]), a.scale_log2, -l2.x));
+                    float p1 = ex2_approx(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -l2.y));
+                    const int qi = i0 + c;
+                    p0 = (qi >= qi_lo && qi <= qi_hi) ? p0 : 0.f;
+                    p1 = (qi + 1 >= qi_lo && qi + 1 <= qi_hi) ? p1 : 0.f;
+                    const float d0 = p0 * (__uint_as_float(dr[i]) - dl.x);
+                    const float d1 = p1 * (__uint_as_float(dr[i + 1]) - dl.y);
+                    pP[c4 * 16 + i / 2] = Elem<T>::pack(p0, p1);
+                    pS[c4 * 16 + i / 2] = Elem<T>::pack(d0, d1);
+                }
+            }
+            tmem_st32(tmem + lane_base + COL_ST + g * 64, pP);
+            tmem_st32(tmem + lane_base + COL_DPT + g * 64, pS);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(E_P));
+        }
+        if (ok) ok = mbar_wait(bar(E_ACC), 0, abort_flag, err, 26);
+        if (ok) {
+            tc_fence_after();
+            // warpgroup 0 writes dK (x scale), warpgroup 1 writes dV
+            T* row = g == 0 ? dkb + (int64_t)r * a.dk_ss : dvb + (int64_t)r * a.dv_ss;
+            const float sc = g == 0 ? a.scale : 1.f;
+            const uint32_t col = g == 0 ? COL_DK : COL_DV;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t acc[32];
+                tmem_ld32(tmem + lane_base + col + c * 32, acc);
+                tmem_wait_ld();
+                if (r < krows) store_row_scaled<T>(row + c * 32, acc, sc);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// dQ
+// ------------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(320, 1) bwd_dq_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
+    using L = BwdSm100Smem<D>;
+    constexpr int NSUB = D / 64, KSTEPS = D / 16;
+    constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 128, COL_DQ = 256;
+    constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
+    constexpr uint32_t IDESC_S = umma_idesc(FMT, 128, 128, 0, 0);
+    constexpr uint32_t IDESC_ACC = umma_idesc(FMT, 128, D, 0, 1);
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
+    const uint32_t sQ = sbase + L::oFix0, sdO = sbase + L::oFix1, sK = sbase + L::oRing0, sV = sbase + L::oRing1;
+    const uint32_t bars = sbase + L::oBar;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * E_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * E_COUNT + 8);
+    auto bar = [&](int i) { return bars + 8u * i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int mblk = gridDim.x - 1 - blockIdx.x;
+    int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
+    if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
+    const int m0 = mblk * 128;
+    if (m0 >= sq) return;
+    if (g_bwd_sm100_error) return;
+    const int hk = h / (a.hq / a.hkv);
+    const int wl = a.wl, wr = a.causal ? 0 : a.wr;
+    const int rows = min(128, sq - m0);
+
+    int lo_first, hi_first, lo_last, hi_last;
+    window_bounds(m0, sq, sk, wl, wr, lo_first, hi_first);
+    window_bounds(m0 + rows - 1, sq, sk, wl, wr, lo_last, hi_last);
+    int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
+    if (sk <= 0 || lo_first >= sk) { t_lo = 0; t_hi = 0; }
+    const int ntiles = max(0, t_hi - t_lo);
+
+    T* dqb = reinterpret_cast<T*>(a.dq) + (a.cu_q ? 0 : (int64_t)b * a.dq_sb) + (int64_t)(q_off + m0) * a.dq_ss + (int64_t)h * a.dq_sh;
+    if (ntiles == 0) {
+        if (tid < rows) {
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            T* row = dqb + (int64_t)tid * a.dq_ss;
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(row)[c] = z;
+        }
+        return;
+    }
+    if (tid == 0) {
+        for (int i = 0; i < E_COUNT; ++i) mbar_init(bar(i), i == E_P ? 256u : 1u);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 8) { tmem_alloc(smem_addr(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    int* err = &g_bwd_sm100_error;
+    const int bb = a.cu_q ? 0 : b;
+
+    if (warp == 8) {
+        if (lane == 0) {
+            tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tdo); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
+            mbar_expect_tx(bar(E_FIX), 2 * L::kTileB);
+            const int qrow = (a.cu_q ? q_off : 0) + m0;
+#pragma unroll
+            for (int s = 0; s < NSUB; ++s) {
+                tma_load_4d(sQ + s * L::kSub, &a.tq, bar(E_FIX), s * 64, h, qrow, bb);
+                tma_load_4d(sdO + s * L::kSub, &a.tdo, bar(E_FIX), s * 64, h, qrow, bb);
+            }
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int st = j & 1, use = j >> 1;
+                const int krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128;
+                if (use > 0) ok = mbar_wait(bar(E_RE0 + st), (use - 1) & 1, abort_flag, err, 31);
+                if (!ok) break;
+                mbar_expect_tx(bar(E_RF0 + st), 2 * L::kTileB);
+#pragma unroll
+                for (int c = 0; c < NSUB; ++c) {
+                    tma_load_4d(sK + st * L::kTileB + c * L::kSub, &a.tk, bar(E_RF0 + st), c * 64, hk, krow, bb);
+                    tma_load_4d(sV + st * L::kTileB + c * L::kSub, &a.tv, bar(E_RF0 + st), c * 64, hk, krow, bb);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0) {
+            bool ok = mbar_wait(bar(E_FIX), 0, abort_flag, err, 32);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int st = j & 1, use = j >> 1;
+                ok = mbar_wait(bar(E_RF0 + st), use & 1, abort_flag, err, 33);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {       // S = Q K^T
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss(tmem + COL_S, umma_desc(sQ + off, 16, 1024), umma_desc(sK + st * L::kTileB + off, 16, 1024), IDESC_S, kk > 0);
+                }
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {       // dP = dO V^T
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss(tmem + COL_DP, umma_desc(sdO + off, 16, 1024), umma_desc(sV + st * L::kTileB + off, 16, 1024), IDESC_S, kk > 0);
+                }
+                umma_commit(bar(E_S));
+                ok = mbar_wait(bar(E_P), j & 1, abort_flag, err, 34);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {            // dQ += dS K  (K = 128 keys)
+                    const uint32_t pcol = (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
+                    umma_ts(tmem + COL_DQ, tmem + COL_DP + pcol, umma_desc(sK + st * L::kTileB + kk * 2048, L::kSub, 1024), IDESC_ACC, (j > 0 || kk > 0));
+                }
+                umma_commit(bar(E_RE0 + st));
+            }
+            if (ok) umma_commit(bar(E_ACC));
+        }
+    } else {
+        const int g = warp >> 2;
+        const int r = tid & 127;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const int qi = m0 + r;
+        int klo = 1, khi = 0;
+        float lse2 = INFINITY, dl = 0.f;
+        if (r < rows) {
+            window_bounds(qi, sq, sk, wl, wr, klo, khi);
+            const int64_t tok = (int64_t)q_off + qi;
+            lse2 = a.lse[(a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + tok * a.lse_ss] * kLog2e;
+            dl = a.delta[((a.cu_q ? tok : (int64_t)b * a.sq + qi)) * a.hq + h];
+        }
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int n0 = (t_lo + j) * 128;
+            ok = mbar_wait(bar(E_S), j & 1, abort_flag, err, 35);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t pS[32];
+#pragma unroll
+            for (int c4 = 0; c4 < 2; ++c4) {
+                uint32_t sr[32], dr[32];
+                tmem_ld32(tmem + lane_base + COL_S + g * 64 + c4 * 32, sr);
+                tmem_ld32(tmem + lane_base + COL_DP + g * 64 + c4 * 32, dr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int col = n0 + g * 64 + c4 * 32 + i;
+                    float p0 = ex2_approx(fmaf(__uint_as_float(sr[i]), a.scale_log2, -lse2));
+                    float p1 = ex2_approx(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -lse2));
+                    p0 = (col >= klo && col <= khi) ? p0 : 0.f;
+                    p1 = (col + 1 >= klo && col + 1 <= khi) ? p1 : 0.f;
+                    pS[c4 * 16 + i / 2] = Elem<T>::pack(p0 * (__uint_as_float(dr[i]) - dl), p1 * (__uint_as_float(dr[i + 1]) - dl));
+                }
+            }
+            tmem_st32(tmem + lane_base + COL_DP + g * 64, pS);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(E_P));
+        }
+        if (ok) ok = mbar_wait(bar(E_ACC), 0, abort_flag, err, 36);
+        if (ok) {
+            tc_fence_after();
+            // each warpgroup writes half of the head dim of its row
+            T* row = dqb + (int64_t)r * a.dq_ss;
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+                const int cc = g * (D / 64) + c;
+                uint32_t acc[32];
+                tmem_ld32(tmem + lane_base + COL_DQ + cc * 32, acc);
+                tmem_wait_ld();
+                if (r < rows) store_row_scaled<T>(row + cc * 32, acc, a.scale);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// host
+// ------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void bwd_delta_sm100_kernel(const fa_bwd_params p, float* delta) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t toks = p.cu_seqlens_q ? p.total_q : (int64_t)p.b * p.sq;
+    if (row >= toks * p.hq) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t tok = row / p.hq;
+    const int h = (int)(row % p.hq);
+    int64_t ooff, doff;
+    if (p.cu_seqlens_q) {
+        ooff = tok * p.o.stride_s + (int64_t)h * p.o.stride_h;
+        doff = tok * p.dout.stride_s + (int64_t)h * p.dout.stride_h;
+    } else {
+        const int64_t bb = tok / p.sq, i = tok % p.sq;
+        ooff = bb * p.o.stride_b + i * p.o.stride_s + (int64_t)h * p.o.stride_h;
+        doff = bb * p.dout.stride_b + i * p.dout.stride_s + (int64_t)h * p.dout.stride_h;
+    }
+    const T* o = reinterpret_cast<const T*>(p.o.ptr) + ooff;
+    const T* d = reinterpret_cast<const T*>(p.dout.ptr) + doff;
+    float acc = 0.f;
+    for (int c = lane * 8; c < p.dv_dim; c += 256) {
+        const uint4 ov = *reinterpret_cast<const uint4*>(o + c);
+        const uint4 dv = *reinterpret_cast<const uint4*>(d + c);
+        const T* oe = reinterpret_cast<const T*>(&ov);
+        const T* de = reinterpret_cast<const T*>(&dv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc += Elem<T>::to_float(oe[e]) * Elem<T>::to_float(de[e]);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) delta[row] = acc;
+}
+
+bool bwd_sm100_supported(const fa_bwd_params& p) {
+    if (p.d != p.dv_dim || (p.d != 64 && p.d != 128)) return false;
+    if (p.softcap > 0.f || !(p.scale > 0.f)) return false;
+    if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
+    if (p.sq <= 0 || p.sk <= 0) return false;
+    if (p.cu_seqlens_q && (p.total_q <= 0 || p.total_k <= 0)) return false;
+    const fa_tensor* ts[4] = {&p.q, &p.k, &p.v, &p.dout};
+    for (const fa_tensor* t : ts) {
+        if (t->stride_h <= 0 || t->stride_s <= 0) return false;
+        if (!p.cu_seqlens_q && p.b > 1 && t->stride_b <= 0) return false;
+    }
+    return tensor_map_encoder_available();
+}
+
+size_t bwd_sm100_workspace(const fa_bwd_params& p) { return bwd_generic_workspace(p); }
+
+template <typename T, int D>
+static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* delta, cudaStream_t st) {
+    const int64_t toks = p.cu_seqlens_q ? p.total_q : (int64_t)p.b * p.sq;
+    const int64_t rows = toks * p.hq;
+    bwd_delta_sm100_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p, delta);
+    mark_kernel(st);
+    auto k1 = bwd_dkdv_sm100_kernel<T, D>;
+    auto k2 = bwd_dq_sm100_kernel<T, D>;
+    const int smem = BwdSm100Smem<D>::kBytes + 1024;
+    if (int e = cuda_ok(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+    if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+    dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g2((p.sq + 127) / 128, p.hq, p.b);
+    k1<<<g1, 320, smem, st>>>(a);
+    mark_kernel(st);
+    k2<<<g2, 320, smem, st>>>(a);
+    mark_kernel(st);
+    return cuda_ok(cudaGetLastError(), "bwd_sm100 launch");
+}
+
+int launch_bwd_sm100(const fa_bwd_params& p) {
+    Sm100BwdArgs a;
+    const bool packed = p.cu_seqlens_q != nullptr;
+    const int64_t q_rows = packed ? p.total_q : p.sq, k_rows = packed ? p.total_k : p.sk;
+    const int nb = packed ? 1 : p.b;
+    auto bstride = [&](const fa_tensor& t, int64_t rows) { return packed || p.b == 1 ? rows * t.stride_s : t.stride_b; };
+    if (int e = make_tile_map(&a.tq, p.dtype, p.q.ptr, p.d, p.hq, q_rows, nb, p.q.stride_h, p.q.stride_s, bstride(p.q, q_rows), 128)) return e;
+    if (int e = make_tile_map(&a.tdo, p.dtype, p.dout.ptr, p.d, p.hq, q_rows, nb, p.dout.stride_h, p.dout.stride_s, bstride(p.dout, q_rows), 128)) return e;
+    if (int e = make_tile_map(&a.tk, p.dtype, p.k.ptr, p.d, p.hkv, k_rows, nb, p.k.stride_h, p.k.stride_s, bstride(p.k, k_rows), 128)) return e;
+    if (int e = make_tile_map(&a.tv, p.dtype, p.v.ptr, p.d, p.hkv, k_rows, nb, p.v.stride_h, p.v.stride_s, bstride(p.v, k_rows), 128)) return e;
+    a.dq = p.dq.ptr; a.dk = p.dk.ptr; a.dv = p.dv.ptr;
+    a.dq_sb = p.dq.stride_b; a.dq_ss = p.dq.stride_s; a.dq_sh = p.dq.stride_h;
+    a.dk_sb = p.dk.stride_b; a.dk_ss = p.dk.stride_s; a.dk_sh = p.dk.stride_h;
+    a.dv_sb = p.dv.stride_b; a.dv_ss = p.dv.stride_s; a.dv_sh = p.dv.stride_h;
+    a.lse = p.lse; a.lse_sb = p.lse_stride_b; a.lse_sh = p.lse_stride_h; a.lse_ss = p.lse_stride_s;
+    a.delta = reinterpret_cast<const float*>(p.workspace);
+    a.cu_q = p.cu_seqlens_q; a.cu_k = p.cu_seqlens_k;
+    a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv;
+    a.scale = p.scale; a.scale_log2 = p.scale * kLog2e;
+    a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
+    float* delta = reinterpret_cast<float*>(p.workspace);
+    note_kernel("sm100_tcgen05_bwd");
+    if (p.dtype == FA_F16) return p.d == 64 ? launch_bwd_sm100_t<__half, 64>(p, a, delta, st) : launch_bwd_sm100_t<__half, 128>(p, a, delta, st);
+    return p.d == 64 ? launch_bwd_sm100_t<__nv_bfloat16, 64>(p, a, delta, st) : launch_bwd_sm100_t<__nv_bfloat16, 128>(p, a, delta, st);
+}
+
+}  // namespace fa

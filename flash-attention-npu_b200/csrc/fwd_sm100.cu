@@ -334,12 +334,6 @@ struct FwdSm100Smem2 {
 
 enum { C_Q = 0, C_KF0, C_KF1, C_KE0, C_KE1, C_VF0, C_VF1, C_VE0, C_VE1, C_SA, C_SB, C_PA, C_PB, C_OA, C_OB, C_COUNT };
 
-__device__ __forceinline__ float ex2_approx(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 template <typename T, int D>
 __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constant__ Sm100FwdArgs a) {
     using L = FwdSm100Smem2<D>;
@@ -633,6 +627,8 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+bool tensor_map_encoder_available() { return encode_fn() != nullptr; }
+
 // (dim, head, row, batch) view with a [64 x 1 x 128 x 1] box and 128-byte swizzle
 int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads, int64_t rows, int batch,
                   int64_t stride_h, int64_t stride_s, int64_t stride_b, int box_rows) {
@@ -716,7 +712,8 @@ int sm100_error_flag(bool clear) {
     int v = 0;
     cudaMemcpyFromSymbol(&v, g_fwd_sm100_error, sizeof(int));
     if (clear) { int z = 0; cudaMemcpyToSymbol(g_fwd_sm100_error, &z, sizeof(int)); }
-    return v;
+    const int w = bwd_sm100_error_flag(clear);
+    return v ? v : w;
 }
 
 }  // namespace fa

@@ -152,5 +152,19 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 }  // namespace sm100
+
+// (dim, head, row, batch) view with a [64 x 1 x box_rows x 1] box and 128-byte swizzle (fwd_sm100.cu)
+int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads, int64_t rows, int batch,
+                  int64_t stride_h, int64_t stride_s, int64_t stride_b, int box_rows);
+bool tensor_map_encoder_available();
+// code left by a timed-out wait in the backward kernels (bwd_sm100.cu); synchronises
+int bwd_sm100_error_flag(bool clear);
+
 }  // namespace fa

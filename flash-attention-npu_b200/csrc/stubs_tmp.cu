@@ -1,9 +1,6 @@
 #include "fa_internal.h"
 namespace fa {
 int launch_fwd_decode(const fa_fwd_params&, const FwdPlan&, float*, float*) { return fail(FA_ERR_UNSUPPORTED, "n/a"); }
-bool bwd_sm100_supported(const fa_bwd_params&) { return false; }
-int launch_bwd_sm100(const fa_bwd_params&) { return fail(FA_ERR_UNSUPPORTED, "n/a"); }
-size_t bwd_sm100_workspace(const fa_bwd_params&) { return 0; }
 }
 extern "C" {
 int fa_mla_decode(const fa_mla_params*) { return fa::fail(FA_ERR_UNSUPPORTED, "n/a"); }
