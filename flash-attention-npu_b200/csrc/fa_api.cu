@@ -76,8 +76,20 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
     const int mblocks = (rows + kGenericBM - 1) / kGenericBM;
     const int nblocks = (p.sk + kGenericBN - 1) / kGenericBN;
     int nsplit = 1;
+    plan.use_decode = fwd_decode_supported(p) ? 1 : 0;
     if (p.num_splits > 1) nsplit = p.num_splits;
-    else if (p.num_splits == 0 && cache_like && nblocks > 1 && p.sq <= 64) {
+    else if (p.num_splits == 0 && plan.use_decode && nblocks > 1) {
+        // decode kernel: the unit of parallelism is a warp per (sequence, KV head, split); aim at about
+        // 1024 keys per split, at least four waves of warps, and never fewer than 256 keys per split
+        const long base = (long)p.hkv * (p.b > 0 ? p.b : 1);
+        const long target = 16L * sm_count();
+        const long by_occ = (target + base - 1) / base;
+        const long by_bal = (p.sk + 1023) / 1024;
+        const long cap = (p.sk + 255) / 256;
+        long n = by_occ > by_bal ? by_occ : by_bal;
+        if (n > cap) n = cap;
+        nsplit = (int)(n < 1 ? 1 : n);
+    } else if (p.num_splits == 0 && cache_like && nblocks > 1 && p.sq <= 64) {
         const long base = (long)mblocks * (plan.pack_gqa ? p.hkv : p.hq) * (p.b > 0 ? p.b : 1);
         const long target = 4L * sm_count();
         long by_occ = base >= target ? 1 : (target + base - 1) / base;
@@ -262,9 +274,14 @@ const char* fa_version(void) { return "fa_b200 0.1.0 (sm_100a)"; }
 const char* fa_last_kernel(void) { return g_kernel; }
 void fa_debug_set(int key, int value) {
     if (key == 1) fa::fwd_sm100_set_p_in_tmem(value);
-    if (key == 3) fa::sm100_error_flag(true);
+    if (key == 3) { fa::sm100_error_flag(true); fa::decode_error_flag(true); }
+    if (key == 4) fa::decode_set_use_tma(value);
 }
-int fa_debug_get(int key) { return key == 2 ? fa::sm100_error_flag(false) : 0; }
+int fa_debug_get(int key) {
+    if (key != 2) return 0;
+    const int a = fa::sm100_error_flag(false);
+    return a ? a : fa::decode_error_flag(false);
+}
 void fa_set_kernel_events(void** events, int count) {
     g_events = reinterpret_cast<cudaEvent_t*>(events);
     g_nevents = events ? count : 0;

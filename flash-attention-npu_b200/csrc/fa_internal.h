@@ -34,6 +34,9 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan);
 // kernels' host launchers (each returns an fa_status)
 int launch_fwd_generic(const fa_fwd_params& p, const FwdPlan& plan, float* o_part, float* lse_part);
 int launch_fwd_decode(const fa_fwd_params& p, const FwdPlan& plan, float* o_part, float* lse_part);
+bool fwd_decode_supported(const fa_fwd_params& p);
+void decode_set_use_tma(int v);
+int decode_error_flag(bool clear);
 int launch_fwd_sm100(const fa_fwd_params& p);
 bool fwd_sm100_supported(const fa_fwd_params& p);
 void fwd_sm100_set_p_in_tmem(int v);

@@ -457,8 +457,8 @@ __global__ void combine_kernel(const float* __restrict__ o_part, const float* __
         float acc = 0.f;
         for (int s = 0; s < nsplit; ++s) {
             const float ls = lse_part[s * lse_split_stride + row];
-            const float w = ls == -INFINITY ? 0.f : expf(ls - l);
-            acc += w * o_part[s * o_split_stride + row * o_row_stride + c];
+            if (ls == -INFINITY) continue;                   // a split that saw no key: its O slot is not read
+            acc += expf(ls - l) * o_part[s * o_split_stride + row * o_row_stride + c];
         }
         store_out<OutT>(o + ooff + c, acc);
     }

@@ -1,6 +1,5 @@
 #include "fa_internal.h"
 namespace fa {
-int launch_fwd_decode(const fa_fwd_params&, const FwdPlan&, float*, float*) { return fail(FA_ERR_UNSUPPORTED, "n/a"); }
 }
 extern "C" {
 int fa_mla_decode(const fa_mla_params*) { return fa::fail(FA_ERR_UNSUPPORTED, "n/a"); }

@@ -229,7 +229,8 @@ void        fa_set_kernel_policy(int policy);
 
 /* Debug switches and status, for tests: key 1 = keep P in tensor memory for the second MMA of the
  * tcgen05 forward (set), key 2 = error code left by a timed-out wait in a tcgen05 kernel (get;
- * synchronises the device), key 3 = clear that code (set). */
+ * synchronises the device), key 3 = clear that code (set), key 4 = 0 makes the decode kernel load
+ * cache tiles with 16-byte cp.async copies instead of TMA (set). */
 void        fa_debug_set(int key, int value);
 int         fa_debug_get(int key);
 
