@@ -46,6 +46,7 @@ int launch_append_rotary(const fa_fwd_params& p, void* q_rot, int rotate_q_by_po
 int launch_fwd_combine(const fa_fwd_params& p, int nsplit, const float* o_part, const float* lse_part,
                        int to_partial);
 int combine_flat(const fa_combine_params& c);
+int combine_flat_keep(const fa_combine_params& c);
 int launch_bwd_generic(const fa_bwd_params& p);
 int launch_bwd_sm100(const fa_bwd_params& p);
 bool bwd_sm100_supported(const fa_bwd_params& p);

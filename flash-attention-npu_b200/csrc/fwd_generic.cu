@@ -492,12 +492,21 @@ int launch_fwd_combine(const fa_fwd_params& p, int nsplit, const float* o_part, 
 
 // public combine entry (flat rows)
 template <typename OutT>
-static void launch_flat_combine(const fa_combine_params& c, cudaStream_t st) {
+static void launch_flat_combine(const fa_combine_params& c, cudaStream_t st, int keep = 0) {
     const int wpb = 4;
     dim3 grid((unsigned)((c.rows + wpb - 1) / wpb));
     combine_kernel<OutT><<<grid, wpb * 32, 0, st>>>(c.o_partial, c.lse_partial, c.o_split_stride, c.o_row_stride, c.lse_split_stride,
                                                    reinterpret_cast<OutT*>(c.o), c.lse, c.nsplit, c.rows, c.dv,
-                                                   1, 0, 0, c.o_stride, 0, 0, 0, 1, 0);
+                                                   1, 0, 0, c.o_stride, 0, 0, 0, 1, keep);
+}
+
+// fp32 output, rows that saw no key keep LSE = -inf (partials that will be combined again)
+int combine_flat_keep(const fa_combine_params& c) {
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(c.stream);
+    if (c.rows == 0) return FA_OK;
+    launch_flat_combine<float>(c, st, 1);
+    mark_kernel(st);
+    return cuda_ok(cudaGetLastError(), "combine launch");
 }
 
 int combine_flat(const fa_combine_params& c) {
@@ -506,6 +515,7 @@ int combine_flat(const fa_combine_params& c) {
     if (c.out_dtype == FA_F16) launch_flat_combine<__half>(c, st);
     else if (c.out_dtype == FA_BF16) launch_flat_combine<__nv_bfloat16>(c, st);
     else launch_flat_combine<float>(c, st);
+    mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "combine launch");
 }
 

@@ -117,3 +117,46 @@ def fwd_combine(out_partial, lse_partial, out=None, out_dtype=None):
         out.copy_(res)
         res = out
     return res, lse
+
+
+def mla_decode(q_nope, q_rope, latent_i8, scales, rope, block_table, cache_seqlens, softmax_scale,
+               num_splits=0, kv_range=None, partials=None):
+    """int8 latent (MLA) paged decode, seqlen_q = 1, one shared KV head (no counterpart in the reference).
+    q_nope (B,1,H,512) / q_rope (B,1,H,64) bf16; latent_i8 (blocks,page,512) int8; scales (blocks,page)
+    fp32; rope (blocks,page,64) bf16 -> [out (B,1,H,512) bf16, lse (B,H,1) fp32].  With kv_range and
+    partials=(o fp32 (B*H,512), lse fp32 (B*H)) only fp32 partial results over that key range are left."""
+    from fa_b200_capi import MlaParams
+    capi.require_cuda(q_nope, q_rope, latent_i8, scales, rope, block_table, cache_seqlens)
+    if q_nope.dtype != torch.bfloat16 or q_rope.dtype != torch.bfloat16 or rope.dtype != torch.bfloat16:
+        raise RuntimeError("MLA decode takes bf16 queries and rope cache")
+    if latent_i8.dtype != torch.int8 or scales.dtype != torch.float32:
+        raise RuntimeError("MLA decode takes an int8 latent cache with fp32 per-token scales")
+    b, sq, h, dl = q_nope.shape
+    if sq != 1 or dl != 512 or q_rope.shape[-1] != 64 or latent_i8.shape[-1] != 512 or rope.shape[-1] != 64:
+        raise RuntimeError("MLA decode expects seqlen_q 1, a 512-dim latent and a 64-dim rope part")
+    if block_table.dtype != torch.int32 or cache_seqlens.dtype != torch.int32:
+        raise RuntimeError("block_table and cache_seqlens must be int32")
+    latent_i8, scales, rope = latent_i8.contiguous(), scales.contiguous(), rope.contiguous()
+    block_table = block_table.contiguous()
+    p = MlaParams()
+    p.q_nope, p.q_rope = q_nope.data_ptr(), q_rope.data_ptr()
+    p.q_nope_stride_b, p.q_nope_stride_h = q_nope.stride(0), q_nope.stride(2)
+    p.q_rope_stride_b, p.q_rope_stride_h = q_rope.stride(0), q_rope.stride(2)
+    p.latent, p.scales, p.rope = latent_i8.data_ptr(), scales.data_ptr(), rope.data_ptr()
+    p.block_table, p.block_table_stride, p.page_size = block_table.data_ptr(), block_table.stride(0), latent_i8.shape[1]
+    p.cache_seqlens = cache_seqlens.data_ptr()
+    out = torch.empty((b, 1, h, 512), dtype=torch.bfloat16, device=q_nope.device)
+    lse = torch.empty((b, h, 1), dtype=torch.float32, device=q_nope.device)
+    p.o, p.o_stride_b, p.o_stride_h, p.lse = out.data_ptr(), out.stride(0), out.stride(2), lse.data_ptr()
+    p.b, p.hq, p.scale, p.num_splits = b, h, softmax_scale, num_splits
+    if kv_range is not None:
+        p.kv_begin, p.kv_end = int(kv_range[0]), int(kv_range[1])
+    if partials is not None:
+        p.partials_only = 1
+        p.o_partial, p.lse_partial = partials[0].data_ptr(), partials[1].data_ptr()
+    ws = capi.workspace(lib.fa_mla_workspace_bytes(p), q_nope.device)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    p.stream = capi.stream_ptr(q_nope.device)
+    with torch.cuda.device(q_nope.device):
+        check(lib.fa_mla_decode(p))
+    return [out, lse]

@@ -309,3 +309,18 @@ def get_scheduler_metadata(batch_size, max_seqlen_q, max_seqlen_k, num_heads_q, 
                                        headdim_v, qkv_dtype, cache_seqlens, cu_seqlens_q, None, cu_seqlens_k_new,
                                        None, cache_leftpad, page_size, max_seqlen_k_new, causal, window_size[0],
                                        window_size[1], attention_chunk, has_softcap, num_splits, pack_gqa, sm_margin)
+
+
+def flash_attn_mla_with_kvcache(q_nope, q_rope, latent_cache_i8, latent_scales, rope_cache, cache_seqlens, page_table,
+                                softmax_scale=None, num_splits=0, return_softmax_lse=False):
+    """Decode step of multi-head latent attention against a paged, int8-quantised latent cache (an addition of
+    this library).  q_nope (batch, 1, nheads, 512) and q_rope (batch, 1, nheads, 64) bf16; latent_cache_i8
+    (num_blocks, page, 512) int8 with latent_scales (num_blocks, page) fp32 (key = value = scale * int8 row,
+    rounded to bf16); rope_cache (num_blocks, page, 64) bf16 is the positional part of the keys; all query heads
+    share the one KV head.  softmax_scale defaults to 576 ** -0.5.  Returns out (batch, 1, nheads, 512) bf16,
+    or (out, softmax_lse (batch, nheads, 1))."""
+    if softmax_scale is None:
+        softmax_scale = (q_nope.shape[-1] + q_rope.shape[-1]) ** (-0.5)
+    out, lse = _ext.mla_decode(q_nope, q_rope, latent_cache_i8, latent_scales, rope_cache, page_table, cache_seqlens,
+                               softmax_scale, num_splits)
+    return (out, lse) if return_softmax_lse else out
