@@ -13,9 +13,15 @@
 //
 // Math as the reference's backward (fag_kernel.cpp:400-465, fag_epilogue_op.hpp:1287-1322, :1394,
 // :1447-1480, fag_epilogue_post.hpp:149-200): P and dS rounded before the second GEMMs, dQ and dK
-// multiplied by the softmax scale at the end.  Tensor memory: S | dP | acc | acc (128 columns each).
-// Warps 0-7 do the element-wise work (thread = TMEM lane, each warpgroup takes 64 of the 128 score
-// columns), warp 8 is the TMA producer, warp 9 issues the MMAs.  All waits are bounded.
+// multiplied by the softmax scale at the end.
+//
+// A 128 x 128 score tile is processed as two 64-column halves that ping-pong between two TMEM buffers:
+// while the element-wise warps turn half u into P / dS, the tensor core already computes the scores of
+// half u+1 and then consumes half u.  Tensor memory: S0 S1 | dP0 dP1 (64 columns each) | acc | acc (128
+// each).  Warps 0-15 do the element-wise work (thread = TMEM lane, each group of four warps takes 16 of the
+// 64 score columns of a half: four warps per scheduler hide the TMEM and exp latencies), warp 16 is the
+// TMA producer, warp 17 issues the score MMAs and warp 18 the accumulating MMAs (one issuing thread alone
+// could not keep the tensor pipe fed).  All waits are bounded.
 #include "fa_utils.cuh"
 #include "fa_internal.h"
 #include "sm100_ptx.cuh"
@@ -55,12 +61,12 @@ struct BwdSm100Smem {
     static constexpr int oFix1 = oFix0 + kTileB;            // V (dkdv) or dO (dq)
     static constexpr int oRing0 = oFix1 + kTileB;           // 2 stages: Q (dkdv) or K (dq)
     static constexpr int oRing1 = oRing0 + 2 * kTileB;      // 2 stages: dO (dkdv) or V (dq)
-    static constexpr int oVec = oRing1 + 2 * kTileB;        // per warp: 2 stages x (64 lse2 + 64 delta) floats
-    static constexpr int oBar = oVec + 8 * 256 * 4;
+    static constexpr int oVec = oRing1 + 2 * kTileB;        // per warp: 2 stages x (16 lse2 + 16 delta) floats
+    static constexpr int oBar = oVec + 16 * 64 * 4;
     static constexpr int kBytes = oBar + 256;
 };
 
-enum { E_FIX = 0, E_RF0, E_RF1, E_RE0, E_RE1, E_S, E_P, E_ACC, E_COUNT };
+enum { E_FIX = 0, E_RF0, E_RF1, E_RE0, E_RE1, E_S0, E_S1, E_P0, E_P1, E_F0, E_F1, E_ACC, E_COUNT };
 
 template <typename T>
 __device__ __forceinline__ void store_row_scaled(T* dst, const uint32_t (&r)[32], float s) {
@@ -79,12 +85,12 @@ __device__ __forceinline__ void store_row_scaled(T* dst, const uint32_t (&r)[32]
 // dK / dV
 // ------------------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(320, 1) bwd_dkdv_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
+__global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
     using L = BwdSm100Smem<D>;
     constexpr int NSUB = D / 64, KSTEPS = D / 16;
-    constexpr uint32_t TMEM_COLS = 512, COL_ST = 0, COL_DPT = 128, COL_DK = 256, COL_DV = 384;
+    constexpr uint32_t TMEM_COLS = 512, COL_ST = 0, COL_DPT = 128, COL_DK = 256, COL_DV = 384;   // ST/DPT: 2 x 64
     constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
-    constexpr uint32_t IDESC_ST = umma_idesc(FMT, 128, 128, 0, 0);
+    constexpr uint32_t IDESC_ST = umma_idesc(FMT, 128, 64, 0, 0);
     constexpr uint32_t IDESC_ACC = umma_idesc(FMT, 128, D, 0, 1);
 
     extern __shared__ unsigned char smem_raw[];
@@ -132,11 +138,11 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_sm100_kernel(const __grid_con
     }
 
     if (tid == 0) {
-        for (int i = 0; i < E_COUNT; ++i) mbar_init(bar(i), i == E_P ? 256u : 1u);
+        for (int i = 0; i < E_COUNT; ++i) mbar_init(bar(i), (i == E_P0 || i == E_P1) ? 512u : 1u);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 8) { tmem_alloc(smem_addr(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    if (warp == 16) { tmem_alloc(smem_addr(tmem_slot), TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -144,7 +150,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_sm100_kernel(const __grid_con
     int* err = &g_bwd_sm100_error;
     const int bb = a.cu_q ? 0 : b;
 
-    if (warp == 8) {
+    if (warp == 16) {
         if (lane == 0) {
             tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tdo); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
             mbar_expect_tx(bar(E_FIX), 2 * L::kTileB);
@@ -169,46 +175,70 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_sm100_kernel(const __grid_con
                 }
             }
         }
-    } else if (warp == 9) {
-        if (lane == 0) {
+    } else if (warp == 17) {
+        {
+            const int units = steps * 2;
+            const uint64_t dK0 = umma_desc(sK, 16, 1024), dV0 = umma_desc(sV, 16, 1024);
+            const uint64_t dQk = umma_desc(sQ, 16, 1024), dOk = umma_desc(sdO, 16, 1024);           // K-major views
+            auto issue_sd = [&](int u) {                    // S^T and dP^T of half u into buffer u & 1
+                const int st = (u >> 1) & 1, hf = u & 1;
+                const uint32_t boff = st * L::kTileB + hf * 8192;
+                const uint64_t bq = umma_desc_at(dQk, boff), bo = umma_desc_at(dOk, boff);
+                const uint32_t d_s = tmem + COL_ST + hf * 64, d_p = tmem + COL_DPT + hf * 64;
+                umma_ss_w<0>(d_s, dK0, bq, IDESC_ST);
+#pragma unroll
+                for (int kk = 1; kk < KSTEPS; ++kk) {
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss_w<1>(d_s, umma_desc_at(dK0, off), umma_desc_at(bq, off), IDESC_ST);
+                }
+                umma_ss_w<0>(d_p, dV0, bo, IDESC_ST);
+#pragma unroll
+                for (int kk = 1; kk < KSTEPS; ++kk) {
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss_w<1>(d_p, umma_desc_at(dV0, off), umma_desc_at(bo, off), IDESC_ST);
+                }
+                umma_commit_w(bar(E_S0 + hf));
+            };
+            // this warp: score MMAs.  Half u may overwrite its TMEM buffer once the accumulating MMAs of half u-2
+            // (issued by warp 18) have read it.
             bool ok = mbar_wait(bar(E_FIX), 0, abort_flag, err, 22);
-            for (int s = 0; s < steps && ok; ++s) {
-                const int st = s & 1, use = s >> 1;
-                ok = mbar_wait(bar(E_RF0 + st), use & 1, abort_flag, err, 23);
+            for (int u = 0; u < units && ok; ++u) {
+                const int s1 = u >> 1;
+                if (u >= 2) ok = mbar_wait(bar(E_F0 + (u & 1)), (s1 - 1) & 1, abort_flag, err, 27);
+                if (ok && (u & 1) == 0) ok = mbar_wait(bar(E_RF0 + (s1 & 1)), (s1 >> 1) & 1, abort_flag, err, 23);
                 if (!ok) break;
                 tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk) {       // S^T = K Q^T
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss(tmem + COL_ST, umma_desc(sK + off, 16, 1024), umma_desc(sQ + st * L::kTileB + off, 16, 1024), IDESC_ST, kk > 0);
-                }
-#pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk) {       // dP^T = V dO^T
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss(tmem + COL_DPT, umma_desc(sV + off, 16, 1024), umma_desc(sdO + st * L::kTileB + off, 16, 1024), IDESC_ST, kk > 0);
-                }
-                umma_commit(bar(E_S));
-                ok = mbar_wait(bar(E_P), s & 1, abort_flag, err, 24);
-                if (!ok) break;
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {            // dV += P^T dO, dK += dS^T Q  (K = 128 query rows)
-                    const uint32_t pcol = (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-                    umma_ts(tmem + COL_DV, tmem + COL_ST + pcol, umma_desc(sdO + st * L::kTileB + kk * 2048, L::kSub, 1024), IDESC_ACC, (s > 0 || kk > 0));
-                }
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t pcol = (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-                    umma_ts(tmem + COL_DK, tmem + COL_DPT + pcol, umma_desc(sQ + st * L::kTileB + kk * 2048, L::kSub, 1024), IDESC_ACC, (s > 0 || kk > 0));
-                }
-                umma_commit(bar(E_RE0 + st));
+                issue_sd(u);
             }
-            if (ok) umma_commit(bar(E_ACC));
+        }
+    } else if (warp == 18) {
+        {
+            const int units = steps * 2;
+            const uint64_t dQm = umma_desc(sQ, L::kSub, 1024), dOm = umma_desc(sdO, L::kSub, 1024); // MN-major views
+            bool ok = true;
+            for (int u = 0; u < units && ok; ++u) {
+                ok = mbar_wait(bar(E_P0 + (u & 1)), (u >> 1) & 1, abort_flag, err, 24);
+                if (!ok) break;
+                tc_fence_after();
+                const int st = (u >> 1) & 1, hf = u & 1;
+                const uint32_t boff = st * L::kTileB + hf * 8192;
+                const uint64_t bo = umma_desc_at(dOm, boff), bq = umma_desc_at(dQm, boff);
+                const uint32_t a_p = tmem + COL_ST + hf * 64, a_s = tmem + COL_DPT + hf * 64;
+                if (u > 0) umma_ts_w<1>(tmem + COL_DV, a_p, bo, IDESC_ACC); else umma_ts_w<0>(tmem + COL_DV, a_p, bo, IDESC_ACC);
+#pragma unroll
+                for (int kk = 1; kk < 4; ++kk) umma_ts_w<1>(tmem + COL_DV, a_p + kk * 16, umma_desc_at(bo, kk * 2048), IDESC_ACC);
+                if (u > 0) umma_ts_w<1>(tmem + COL_DK, a_s, bq, IDESC_ACC); else umma_ts_w<0>(tmem + COL_DK, a_s, bq, IDESC_ACC);
+#pragma unroll
+                for (int kk = 1; kk < 4; ++kk) umma_ts_w<1>(tmem + COL_DK, a_s + kk * 16, umma_desc_at(bq, kk * 2048), IDESC_ACC);
+                umma_commit_w(bar(E_F0 + hf));
+                if (u & 1) umma_commit_w(bar(E_RE0 + st));
+            }
+            if (ok) umma_commit_w(bar(E_ACC));
         }
     } else {
         // ------------------------------------------------------------ element-wise: thread = key row
-        const int g = warp >> 2;                             // which 64 query columns
-        const int r = tid & 127;
+        const int cg = warp >> 2;                            // which 16 query columns of a half
+        const int r = (warp & 3) * 32 + lane;                // TMEM lane = key row of the tile
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const int n = n0 + r;
         // query rows that see key n: [qi_lo, qi_hi]
@@ -217,90 +247,95 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_sm100_kernel(const __grid_con
         if (wl >= 0) qi_hi = min(sq - 1, n + wl - diff);
         if (n >= sk) { qi_lo = 1; qi_hi = 0; }
         bool ok = true;
-        for (int s = 0; s < steps && ok; ++s) {
+        const int units = steps * 2;
+        // -LSE (log2 domain, lanes 0-15) / -delta (lanes 16-31) of the warp's 16 query columns, fetched one unit ahead
+        auto fetch_vec = [&](int u) -> float {
+            const int s = u >> 1;
             const int h = hk * G + s / nmb;
-            const int i0 = (mb_lo + s % nmb) * 128;
-            // Each warp stages the LSE (log2 domain) and delta of its 64 query columns in its own slice
-            // of shared memory: lanes load two columns each, then only a warp-level sync is needed.
-            float* vec = sVec + warp * 256 + (s & 1) * 128;          // [0,64) lse2, [64,128) delta
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                const int c = lane + 32 * t;
-                const int i = i0 + g * 64 + c;
-                float l2 = INFINITY, dl = 0.f;
-                if (i < sq) {
-                    const int64_t tok = (int64_t)q_off + i;
-                    l2 = a.lse[(a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + tok * a.lse_ss] * kLog2e;
-                    dl = a.delta[((a.cu_q ? tok : (int64_t)b * a.sq + i)) * a.hq + h];
-                }
-                vec[c] = l2;
-                vec[64 + c] = dl;
-            }
+            const int i = (mb_lo + s % nmb) * 128 + (u & 1) * 64 + cg * 16 + (lane & 15);
+            if (i >= sq) return lane < 16 ? -INFINITY : 0.f;
+            const int64_t tok = (int64_t)q_off + i;
+            return lane < 16 ? -a.lse[(a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + tok * a.lse_ss] * kLog2e
+                             : -a.delta[((a.cu_q ? tok : (int64_t)b * a.sq + i)) * a.hq + h];
+        };
+        float staged = fetch_vec(0);
+        for (int u = 0; u < units && ok; ++u) {
+            const int s = u >> 1, hf = u & 1;
+            const int i0 = (mb_lo + s % nmb) * 128 + hf * 64 + cg * 16;      // first query row of this thread's 16 columns
+            float* vec = sVec + warp * 64 + (u & 1) * 32;               // [0,16) lse2, [16,32) delta
+            vec[lane] = staged;
             __syncwarp();
-            ok = mbar_wait(bar(E_S), s & 1, abort_flag, err, 25);
+            if (u + 1 < units) staged = fetch_vec(u + 1);
+            ok = mbar_wait(bar(E_S0 + hf), (u >> 1) & 1, abort_flag, err, 25);
             if (!ok) break;
             tc_fence_after();
-            uint32_t pP[32], pS[32];
+            uint32_t sr[16], dr[16], pP[8], pS[8];
+            tmem_ld16(tmem + lane_base + COL_ST + hf * 64 + cg * 16, sr);
+            tmem_ld16(tmem + lane_base + COL_DPT + hf * 64 + cg * 16, dr);
+            tmem_wait_ld();
+            const bool inside = __all_sync(0xffffffffu, i0 >= qi_lo && i0 + 15 <= qi_hi);
+            const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
 #pragma unroll
-            for (int c4 = 0; c4 < 2; ++c4) {
-                uint32_t sr[32], dr[32];
-                tmem_ld32(tmem + lane_base + COL_ST + g * 64 + c4 * 32, sr);
-                tmem_ld32(tmem + lane_base + COL_DPT + g * 64 + c4 * 32, dr);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int lc = c4 * 32 + i;
-                    const int c = g * 64 + lc;
-                    const float2 l2 = *reinterpret_cast<const float2*>(vec + lc);
-                    const float2 dl = *reinterpret_cast<const float2*>(vec + 64 + lc);
-                    float p0 = ex2_approx(fmaf(__uint_as_float(sr[i]), a.scale_log2, -l2.x));
-                    float p1 = ex2_approx(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -l2.y));
-                    const int qi = i0 + c;
-                    p0 = (qi >= qi_lo && qi <= qi_hi) ? p0 : 0.f;
-                    p1 = (qi + 1 >= qi_lo && qi + 1 <= qi_hi) ? p1 : 0.f;
-                    const float d0 = p0 * (__uint_as_float(dr[i]) - dl.x);
-                    const float d1 = p1 * (__uint_as_float(dr[i + 1]) - dl.y);
-                    pP[c4 * 16 + i / 2] = Elem<T>::pack(p0, p1);
-                    pS[c4 * 16 + i / 2] = Elem<T>::pack(d0, d1);
+            for (int i = 0; i < 16; i += 4) {
+                const float4 nl = *reinterpret_cast<const float4*>(vec + i);           // -lse2
+                const float4 nd = *reinterpret_cast<const float4*>(vec + 16 + i);      // -delta
+                const float2 x01 = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, make_float2(nl.x, nl.y));
+                const float2 x23 = fma2(make_float2(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])), sc2, make_float2(nl.z, nl.w));
+                float2 p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
+                float2 p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
+                if (!inside) {
+                    const int qi = i0 + i;
+                    p01.x = (qi >= qi_lo && qi <= qi_hi) ? p01.x : 0.f;
+                    p01.y = (qi + 1 >= qi_lo && qi + 1 <= qi_hi) ? p01.y : 0.f;
+                    p23.x = (qi + 2 >= qi_lo && qi + 2 <= qi_hi) ? p23.x : 0.f;
+                    p23.y = (qi + 3 >= qi_lo && qi + 3 <= qi_hi) ? p23.y : 0.f;
                 }
+                const float2 d01 = mul2(p01, add2(make_float2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])), make_float2(nd.x, nd.y)));
+                const float2 d23 = mul2(p23, add2(make_float2(__uint_as_float(dr[i + 2]), __uint_as_float(dr[i + 3])), make_float2(nd.z, nd.w)));
+                pP[i / 2] = Elem<T>::pack(p01.x, p01.y);
+                pP[i / 2 + 1] = Elem<T>::pack(p23.x, p23.y);
+                pS[i / 2] = Elem<T>::pack(d01.x, d01.y);
+                pS[i / 2 + 1] = Elem<T>::pack(d23.x, d23.y);
             }
-            tmem_st32(tmem + lane_base + COL_ST + g * 64, pP);
-            tmem_st32(tmem + lane_base + COL_DPT + g * 64, pS);
+            tmem_st8(tmem + lane_base + COL_ST + hf * 64 + cg * 16, pP);
+            tmem_st8(tmem + lane_base + COL_DPT + hf * 64 + cg * 16, pS);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(E_P));
+            mbar_arrive(bar(E_P0 + hf));
         }
         if (ok) ok = mbar_wait(bar(E_ACC), 0, abort_flag, err, 26);
         if (ok) {
             tc_fence_after();
-            // warpgroup 0 writes dK (x scale), warpgroup 1 writes dV
-            T* row = g == 0 ? dkb + (int64_t)r * a.dk_ss : dvb + (int64_t)r * a.dv_ss;
-            const float sc = g == 0 ? a.scale : 1.f;
-            const uint32_t col = g == 0 ? COL_DK : COL_DV;
+            // warp groups 0,1 write the two halves of dK (x scale), groups 2,3 the halves of dV
+            const bool is_dk = cg < 2;
+            T* row = is_dk ? dkb + (int64_t)r * a.dk_ss : dvb + (int64_t)r * a.dv_ss;
+            const float sc = is_dk ? a.scale : 1.f;
+            const uint32_t col = is_dk ? COL_DK : COL_DV;
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < D / 64; ++c) {
+                const int cc = (cg & 1) * (D / 64) + c;
                 uint32_t acc[32];
-                tmem_ld32(tmem + lane_base + col + c * 32, acc);
+                tmem_ld32(tmem + lane_base + col + cc * 32, acc);
                 tmem_wait_ld();
-                if (r < krows) store_row_scaled<T>(row + c * 32, acc, sc);
+                if (r < krows) store_row_scaled<T>(row + cc * 32, acc, sc);
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+    if (warp == 16) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
 // ------------------------------------------------------------------------------------------------------
 // dQ
 // ------------------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(320, 1) bwd_dq_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
+__global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
     using L = BwdSm100Smem<D>;
     constexpr int NSUB = D / 64, KSTEPS = D / 16;
-    constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 128, COL_DQ = 256;
+    constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 128, COL_DQ = 256;     // S / dP: 2 x 64 columns
     constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
-    constexpr uint32_t IDESC_S = umma_idesc(FMT, 128, 128, 0, 0);
+    constexpr uint32_t IDESC_S = umma_idesc(FMT, 128, 64, 0, 0);
     constexpr uint32_t IDESC_ACC = umma_idesc(FMT, 128, D, 0, 1);
 
     extern __shared__ unsigned char smem_raw[];
@@ -342,11 +377,11 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_sm100_kernel(const __grid_const
         return;
     }
     if (tid == 0) {
-        for (int i = 0; i < E_COUNT; ++i) mbar_init(bar(i), i == E_P ? 256u : 1u);
+        for (int i = 0; i < E_COUNT; ++i) mbar_init(bar(i), (i == E_P0 || i == E_P1) ? 512u : 1u);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 8) { tmem_alloc(smem_addr(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    if (warp == 16) { tmem_alloc(smem_addr(tmem_slot), TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -354,7 +389,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_sm100_kernel(const __grid_const
     int* err = &g_bwd_sm100_error;
     const int bb = a.cu_q ? 0 : b;
 
-    if (warp == 8) {
+    if (warp == 16) {
         if (lane == 0) {
             tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tdo); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
             mbar_expect_tx(bar(E_FIX), 2 * L::kTileB);
@@ -378,40 +413,63 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_sm100_kernel(const __grid_const
                 }
             }
         }
-    } else if (warp == 9) {
-        if (lane == 0) {
+    } else if (warp == 17) {
+        {
+            const int units = ntiles * 2;
+            const uint64_t dQ0 = umma_desc(sQ, 16, 1024), dO0 = umma_desc(sdO, 16, 1024);
+            const uint64_t dKk = umma_desc(sK, 16, 1024), dVk = umma_desc(sV, 16, 1024);
+            auto issue_sd = [&](int u) {                    // S and dP against the 64 keys of half u
+                const int st = (u >> 1) & 1, hf = u & 1;
+                const uint32_t boff = st * L::kTileB + hf * 8192;
+                const uint64_t bk = umma_desc_at(dKk, boff), bv = umma_desc_at(dVk, boff);
+                const uint32_t d_s = tmem + COL_S + hf * 64, d_p = tmem + COL_DP + hf * 64;
+                umma_ss_w<0>(d_s, dQ0, bk, IDESC_S);
+#pragma unroll
+                for (int kk = 1; kk < KSTEPS; ++kk) {
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss_w<1>(d_s, umma_desc_at(dQ0, off), umma_desc_at(bk, off), IDESC_S);
+                }
+                umma_ss_w<0>(d_p, dO0, bv, IDESC_S);
+#pragma unroll
+                for (int kk = 1; kk < KSTEPS; ++kk) {
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss_w<1>(d_p, umma_desc_at(dO0, off), umma_desc_at(bv, off), IDESC_S);
+                }
+                umma_commit_w(bar(E_S0 + hf));
+            };
             bool ok = mbar_wait(bar(E_FIX), 0, abort_flag, err, 32);
-            for (int j = 0; j < ntiles && ok; ++j) {
-                const int st = j & 1, use = j >> 1;
-                ok = mbar_wait(bar(E_RF0 + st), use & 1, abort_flag, err, 33);
+            for (int u = 0; u < units && ok; ++u) {
+                const int j1 = u >> 1;
+                if (u >= 2) ok = mbar_wait(bar(E_F0 + (u & 1)), (j1 - 1) & 1, abort_flag, err, 37);
+                if (ok && (u & 1) == 0) ok = mbar_wait(bar(E_RF0 + (j1 & 1)), (j1 >> 1) & 1, abort_flag, err, 33);
                 if (!ok) break;
                 tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk) {       // S = Q K^T
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss(tmem + COL_S, umma_desc(sQ + off, 16, 1024), umma_desc(sK + st * L::kTileB + off, 16, 1024), IDESC_S, kk > 0);
-                }
-#pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk) {       // dP = dO V^T
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss(tmem + COL_DP, umma_desc(sdO + off, 16, 1024), umma_desc(sV + st * L::kTileB + off, 16, 1024), IDESC_S, kk > 0);
-                }
-                umma_commit(bar(E_S));
-                ok = mbar_wait(bar(E_P), j & 1, abort_flag, err, 34);
-                if (!ok) break;
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {            // dQ += dS K  (K = 128 keys)
-                    const uint32_t pcol = (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-                    umma_ts(tmem + COL_DQ, tmem + COL_DP + pcol, umma_desc(sK + st * L::kTileB + kk * 2048, L::kSub, 1024), IDESC_ACC, (j > 0 || kk > 0));
-                }
-                umma_commit(bar(E_RE0 + st));
+                issue_sd(u);
             }
-            if (ok) umma_commit(bar(E_ACC));
+        }
+    } else if (warp == 18) {
+        {
+            const int units = ntiles * 2;
+            const uint64_t dKm = umma_desc(sK, L::kSub, 1024);
+            bool ok = true;
+            for (int u = 0; u < units && ok; ++u) {
+                ok = mbar_wait(bar(E_P0 + (u & 1)), (u >> 1) & 1, abort_flag, err, 34);
+                if (!ok) break;
+                tc_fence_after();
+                const int st = (u >> 1) & 1, hf = u & 1;
+                const uint64_t bk = umma_desc_at(dKm, st * L::kTileB + hf * 8192);
+                const uint32_t a_s = tmem + COL_DP + hf * 64;
+                if (u > 0) umma_ts_w<1>(tmem + COL_DQ, a_s, bk, IDESC_ACC); else umma_ts_w<0>(tmem + COL_DQ, a_s, bk, IDESC_ACC);
+#pragma unroll
+                for (int kk = 1; kk < 4; ++kk) umma_ts_w<1>(tmem + COL_DQ, a_s + kk * 16, umma_desc_at(bk, kk * 2048), IDESC_ACC);
+                umma_commit_w(bar(E_F0 + hf));
+                if (u & 1) umma_commit_w(bar(E_RE0 + st));
+            }
+            if (ok) umma_commit_w(bar(E_ACC));
         }
     } else {
-        const int g = warp >> 2;
-        const int r = tid & 127;
+        const int cg = warp >> 2;                            // which 16 key columns of a half
+        const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const int qi = m0 + r;
         int klo = 1, khi = 0;
@@ -423,51 +481,52 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_sm100_kernel(const __grid_const
             dl = a.delta[((a.cu_q ? tok : (int64_t)b * a.sq + qi)) * a.hq + h];
         }
         bool ok = true;
-        for (int j = 0; j < ntiles && ok; ++j) {
-            const int n0 = (t_lo + j) * 128;
-            ok = mbar_wait(bar(E_S), j & 1, abort_flag, err, 35);
+        const int units = ntiles * 2;
+        for (int u = 0; u < units && ok; ++u) {
+            const int hf = u & 1;
+            const int c0 = (t_lo + (u >> 1)) * 128 + hf * 64 + cg * 16;     // first key of this thread's 16 columns
+            ok = mbar_wait(bar(E_S0 + hf), (u >> 1) & 1, abort_flag, err, 35);
             if (!ok) break;
             tc_fence_after();
-            uint32_t pS[32];
+            uint32_t sr[16], dr[16], pS[8];
+            tmem_ld16(tmem + lane_base + COL_S + hf * 64 + cg * 16, sr);
+            tmem_ld16(tmem + lane_base + COL_DP + hf * 64 + cg * 16, dr);
+            tmem_wait_ld();
+            const bool inside = __all_sync(0xffffffffu, c0 >= klo && c0 + 15 <= khi);
+            const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dl, -dl);
 #pragma unroll
-            for (int c4 = 0; c4 < 2; ++c4) {
-                uint32_t sr[32], dr[32];
-                tmem_ld32(tmem + lane_base + COL_S + g * 64 + c4 * 32, sr);
-                tmem_ld32(tmem + lane_base + COL_DP + g * 64 + c4 * 32, dr);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int col = n0 + g * 64 + c4 * 32 + i;
-                    float p0 = ex2_approx(fmaf(__uint_as_float(sr[i]), a.scale_log2, -lse2));
-                    float p1 = ex2_approx(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -lse2));
-                    p0 = (col >= klo && col <= khi) ? p0 : 0.f;
-                    p1 = (col + 1 >= klo && col + 1 <= khi) ? p1 : 0.f;
-                    pS[c4 * 16 + i / 2] = Elem<T>::pack(p0 * (__uint_as_float(dr[i]) - dl), p1 * (__uint_as_float(dr[i + 1]) - dl));
+            for (int i = 0; i < 16; i += 2) {
+                const float2 x = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, nl2);
+                float2 p = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+                if (!inside) {
+                    const int col = c0 + i;
+                    p.x = (col >= klo && col <= khi) ? p.x : 0.f;
+                    p.y = (col + 1 >= klo && col + 1 <= khi) ? p.y : 0.f;
                 }
+                const float2 ds = mul2(p, add2(make_float2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])), nd2));
+                pS[i / 2] = Elem<T>::pack(ds.x, ds.y);
             }
-            tmem_st32(tmem + lane_base + COL_DP + g * 64, pS);
+            tmem_st8(tmem + lane_base + COL_DP + hf * 64 + cg * 16, pS);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(E_P));
+            mbar_arrive(bar(E_P0 + hf));
         }
         if (ok) ok = mbar_wait(bar(E_ACC), 0, abort_flag, err, 36);
         if (ok) {
             tc_fence_after();
-            // each warpgroup writes half of the head dim of its row
+            // each group of four warps writes 32 columns of its row (groups beyond D / 32 have nothing to write)
             T* row = dqb + (int64_t)r * a.dq_ss;
-#pragma unroll
-            for (int c = 0; c < D / 64; ++c) {
-                const int cc = g * (D / 64) + c;
+            if (cg < D / 32) {
                 uint32_t acc[32];
-                tmem_ld32(tmem + lane_base + COL_DQ + cc * 32, acc);
+                tmem_ld32(tmem + lane_base + COL_DQ + cg * 32, acc);
                 tmem_wait_ld();
-                if (r < rows) store_row_scaled<T>(row + cc * 32, acc, a.scale);
+                if (r < rows) store_row_scaled<T>(row + cg * 32, acc, a.scale);
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+    if (warp == 16) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -534,9 +593,9 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
     if (int e = cuda_ok(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
     if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
     dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g2((p.sq + 127) / 128, p.hq, p.b);
-    k1<<<g1, 320, smem, st>>>(a);
+    k1<<<g1, 608, smem, st>>>(a);
     mark_kernel(st);
-    k2<<<g2, 320, smem, st>>>(a);
+    k2<<<g2, 608, smem, st>>>(a);
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "bwd_sm100 launch");
 }

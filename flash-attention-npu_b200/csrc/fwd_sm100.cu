@@ -432,23 +432,26 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
             }
         }
     } else if (warp == 9) {
-        if (lane == 0) {
+        {   // whole warp, one elected lane issues (see umma_ss_w)
+            // descriptors of the tile origins, built once; every MMA adds a compile-time offset
+            const uint64_t dQ0 = umma_desc(sQ, 16, 1024), dK0 = umma_desc(sK, 16, 1024), dV0 = umma_desc(sV, L::kSub, 1024);
             auto issue_qk = [&](int x, int st) {
                 const uint32_t d_s = tmem + x * 128;
+                const uint64_t aq = umma_desc_at(dQ0, x * L::kQ), bk = umma_desc_at(dK0, st * L::kKV);
+                umma_ss_w<0>(d_s, aq, bk, IDESC_QK);
 #pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk) {
-                    const uint64_t ad = umma_desc(sQ + x * L::kQ + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bd = umma_desc(sK + st * L::kKV + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
-                    umma_ss(d_s, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
+                for (int kk = 1; kk < KSTEPS; ++kk) {
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss_w<1>(d_s, umma_desc_at(aq, off), umma_desc_at(bk, off), IDESC_QK);
                 }
-                umma_commit(bar(C_SA + x));
+                umma_commit_w(bar(C_SA + x));
             };
             auto issue_pv = [&](int x, int st, int j) {
+                const uint64_t bv = umma_desc_at(dV0, st * L::kKV);
+                const uint32_t d_o = tmem + 256 + x * 128, a_p = tmem + x * 128;
+                if (j > 0) umma_ts_w<1>(d_o, a_p, bv, IDESC_PV); else umma_ts_w<0>(d_o, a_p, bv, IDESC_PV);
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint64_t bd = umma_desc(sV + st * L::kKV + kk * 2048, L::kSub, 1024);
-                    umma_ts(tmem + 256 + x * 128, tmem + x * 128 + kk * 8, bd, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 1; kk < 8; ++kk) umma_ts_w<1>(d_o, a_p + kk * 8, umma_desc_at(bv, kk * 2048), IDESC_PV);
             };
             bool ok = mbar_wait(bar(C_Q), 0, abort_flag, err, 3);
             if (ok) ok = mbar_wait(bar(C_KF0), 0, abort_flag, err, 4);
@@ -456,7 +459,7 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
                 tc_fence_after();
                 issue_qk(0, 0);
                 if (has_b) issue_qk(1, 0);
-                umma_commit(bar(C_KE0));
+                umma_commit_w(bar(C_KE0));
             }
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int st = j & 1, use = j >> 1;
@@ -473,7 +476,7 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
                     tc_fence_after();
                     issue_qk(0, st1);
                 } else {
-                    umma_commit(bar(C_OA));
+                    umma_commit_w(bar(C_OA));
                 }
                 if (has_b) {
                     ok = mbar_wait(bar(C_PB), j & 1, abort_flag, err, 8);
@@ -481,12 +484,12 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
                     tc_fence_after();
                     issue_pv(1, st, j);
                 }
-                umma_commit(bar(C_VE0 + st));
+                umma_commit_w(bar(C_VE0 + st));
                 if (more) {
                     if (has_b) issue_qk(1, st1);
-                    umma_commit(bar(C_KE0 + st1));
+                    umma_commit_w(bar(C_KE0 + st1));
                 } else if (has_b) {
-                    umma_commit(bar(C_OB));
+                    umma_commit_w(bar(C_OB));
                 }
             }
         }
