@@ -335,7 +335,7 @@ struct FwdSm100Smem2 {
 enum { C_Q = 0, C_KF0, C_KF1, C_KE0, C_KE1, C_VF0, C_VF1, C_VE0, C_VE1, C_SA, C_SB, C_PA, C_PB, C_OA, C_OB, C_COUNT };
 
 template <typename T, int D>
-__global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constant__ Sm100FwdArgs a) {
+__global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constant__ Sm100FwdArgs a) {
     using L = FwdSm100Smem2<D>;
     constexpr int NSUB = D / 64;
     constexpr int KSTEPS = D / 16;
@@ -405,6 +405,13 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
     const int qrow0 = (a.cu_q ? q_off : 0) + m0;
     const int qb = a.cu_q ? 0 : b;
 
+    // Register file split by warp group: the copy/MMA group (warps 8-11, of which 10 and 11 only
+    // exist to complete the group) keeps 48 registers a thread, the two softmax groups take 224.  The sum
+    // 128*48 + 256*224 must stay within what the CTA was launched with (384 threads * 168 registers): an
+    // increase beyond the CTA's pool would block forever.
+    static_assert(128 * 48 + 256 * 224 <= 384 * 168, "register split exceeds the CTA's allocation");
+    if (warp >= 8) {
+    reg_dealloc<48>();
     if (warp == 8) {
         if (lane == 0) {
             tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
@@ -438,20 +445,18 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
             auto issue_qk = [&](int x, int st) {
                 const uint32_t d_s = tmem + x * 128;
                 const uint64_t aq = umma_desc_at(dQ0, x * L::kQ), bk = umma_desc_at(dK0, st * L::kKV);
-                umma_ss_w<0>(d_s, aq, bk, IDESC_QK);
-#pragma unroll
-                for (int kk = 1; kk < KSTEPS; ++kk) {
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss_w<1>(d_s, umma_desc_at(aq, off), umma_desc_at(bk, off), IDESC_QK);
-                }
+                umma_ss_wo<0, 0, 0>(d_s, aq, bk, IDESC_QK);
+                static_for<1, KSTEPS>([&](auto kk) {
+                    constexpr uint32_t off = (kk.value >> 2) * L::kSub + (kk.value & 3) * 32;
+                    umma_ss_wo<1, off, off>(d_s, aq, bk, IDESC_QK);
+                });
                 umma_commit_w(bar(C_SA + x));
             };
             auto issue_pv = [&](int x, int st, int j) {
                 const uint64_t bv = umma_desc_at(dV0, st * L::kKV);
                 const uint32_t d_o = tmem + 256 + x * 128, a_p = tmem + x * 128;
-                if (j > 0) umma_ts_w<1>(d_o, a_p, bv, IDESC_PV); else umma_ts_w<0>(d_o, a_p, bv, IDESC_PV);
-#pragma unroll
-                for (int kk = 1; kk < 8; ++kk) umma_ts_w<1>(d_o, a_p + kk * 8, umma_desc_at(bv, kk * 2048), IDESC_PV);
+                if (j > 0) umma_ts_wo<1, 0, 0>(d_o, a_p, bv, IDESC_PV); else umma_ts_wo<0, 0, 0>(d_o, a_p, bv, IDESC_PV);
+                static_for<1, 8>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
             };
             bool ok = mbar_wait(bar(C_Q), 0, abort_flag, err, 3);
             if (ok) ok = mbar_wait(bar(C_KF0), 0, abort_flag, err, 4);
@@ -493,7 +498,10 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
                 }
             }
         }
-    } else if (warp < 4 || has_b) {
+    }
+    } else {
+    reg_alloc<224>();
+    if (warp < 4 || has_b) {
         // ---------------------------------------------------------------- softmax of tile x
         const int x = warp >> 2;
         const int r = tid & 127;
@@ -531,14 +539,15 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
                     }
                 }
             }
+            // four independent chains of three-input maxima
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(sreg[c][i]));
-                    mx1 = fmaxf(mx1, __uint_as_float(sreg[c][i + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(sreg[c][i + 2]));
-                    mx3 = fmaxf(mx3, __uint_as_float(sreg[c][i + 3]));
+                for (int i = 0; i < 32; i += 8) {
+                    mx0 = fmaxf(fmaxf(mx0, __uint_as_float(sreg[c][i])), __uint_as_float(sreg[c][i + 1]));
+                    mx1 = fmaxf(fmaxf(mx1, __uint_as_float(sreg[c][i + 2])), __uint_as_float(sreg[c][i + 3]));
+                    mx2 = fmaxf(fmaxf(mx2, __uint_as_float(sreg[c][i + 4])), __uint_as_float(sreg[c][i + 5]));
+                    mx3 = fmaxf(fmaxf(mx3, __uint_as_float(sreg[c][i + 6])), __uint_as_float(sreg[c][i + 7]));
                 }
             }
             const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;       // log2 domain
@@ -559,23 +568,28 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
                 }
             }
             const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-            float s0 = 0.f, s1 = 0.f;
+            const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(neg_m, neg_m);
+            float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
             for (int hlf = 0; hlf < 2; ++hlf) {
                 uint32_t preg[32];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float p0 = ex2_approx(fmaf(__uint_as_float(sreg[2 * hlf + c][i]), sc, neg_m));
-                        const float p1 = ex2_approx(fmaf(__uint_as_float(sreg[2 * hlf + c][i + 1]), sc, neg_m));
-                        s0 += p0;
-                        s1 += p1;
-                        preg[c * 16 + i / 2] = Elem<T>::pack(p0, p1);
+                    for (int i = 0; i < 32; i += 4) {
+                        const float2 xa = fma2(make_float2(__uint_as_float(sreg[2 * hlf + c][i]), __uint_as_float(sreg[2 * hlf + c][i + 1])), sc2, nm2);
+                        const float2 xb = fma2(make_float2(__uint_as_float(sreg[2 * hlf + c][i + 2]), __uint_as_float(sreg[2 * hlf + c][i + 3])), sc2, nm2);
+                        const float2 pa = make_float2(ex2_approx(xa.x), ex2_approx(xa.y));
+                        const float2 pb = make_float2(ex2_approx(xb.x), ex2_approx(xb.y));
+                        sum_a = add2(sum_a, pa);
+                        sum_b = add2(sum_b, pb);
+                        preg[c * 16 + i / 2] = Elem<T>::pack(pa.x, pa.y);
+                        preg[c * 16 + i / 2 + 1] = Elem<T>::pack(pb.x, pb.y);
                     }
                 }
                 tmem_st32(t_s + hlf * 32, preg);
             }
+            const float s0 = sum_a.x + sum_b.x, s1 = sum_a.y + sum_b.y;
             l_run += s0 + s1;
             tmem_wait_st();
             tc_fence_before();
@@ -605,6 +619,7 @@ __global__ void __launch_bounds__(320, 1) fwd_sm100_kernel2(const __grid_constan
             }
             if (r < rows && lbase) lbase[(int64_t)(x * 128 + r) * a.lse_ss] = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : INFINITY;
         }
+    }
     }
     tc_fence_before();
     __syncthreads();
@@ -676,7 +691,7 @@ static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
         const int smem = FwdSm100Smem2<D>::kBytes + 1024;
         if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
         dim3 grid((p.sq + 255) / 256, p.hq, p.b);
-        kern<<<grid, 320, smem, st>>>(a);
+        kern<<<grid, 384, smem, st>>>(a);
     } else {
         auto kern = fwd_sm100_kernel<T, D>;
         const int smem = FwdSm100Smem<D>::kBytes + 1024;

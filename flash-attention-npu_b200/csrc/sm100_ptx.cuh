@@ -1,6 +1,7 @@
 // Blackwell (sm_100a) building blocks as inline PTX: mbarriers with bounded waits, TMA tile
 // loads, tensor-memory allocation, tcgen05 MMA / commit / ld / st, UMMA descriptors.
 #pragma once
+#include <type_traits>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -162,6 +163,30 @@ __device__ __forceinline__ void umma_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint
         "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(ACC) : "memory");
 }
+// The same with the descriptors formed inside the statement from a base and a compile-time byte offset, so that
+// the compiler keeps one base in registers instead of one descriptor per K step.
+template <int ACC, uint32_t A_OFF, uint32_t B_OFF>
+__device__ __forceinline__ void umma_ss_wo(uint32_t d_tmem, uint64_t a_base, uint64_t b_base, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "add.u64 da, %1, %5;\n\t"
+        "add.u64 db, %2, %6;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_base), "l"(b_base), "r"(idesc), "n"(ACC), "n"(A_OFF >> 4), "n"(B_OFF >> 4) : "memory");
+}
+template <int ACC, uint32_t A_COL, uint32_t B_OFF>
+__device__ __forceinline__ void umma_ts_wo(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_base, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t.reg .b32 ta;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "add.u32 ta, %1, %5;\n\t"
+        "add.u64 db, %2, %6;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_base), "r"(idesc), "n"(ACC), "n"(A_COL), "n"(B_OFF >> 4) : "memory");
+}
 __device__ __forceinline__ void umma_commit_w(uint32_t bar) {
     asm volatile(
         "{\n\t.reg .pred q;\n\t"
@@ -223,6 +248,19 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Compile-time loop: f(std::integral_constant<int, I>) for I in [B, E).
+template <int B, int E, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+    if constexpr (B < E) {
+        f(std::integral_constant<int, B>{});
+        static_for<B + 1, E>(f);
+    }
+}
+
+// Warp-group register reallocation (all four warps of an aligned group execute it together).
+template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
