@@ -332,7 +332,10 @@ struct FwdSm100Smem2 {
     static constexpr int kBytes = oBar + 256;
 };
 
-enum { C_Q = 0, C_KF0, C_KF1, C_KE0, C_KE1, C_VF0, C_VF1, C_VE0, C_VE1, C_SA, C_SB, C_PA, C_PB, C_OA, C_OB, C_COUNT };
+#ifndef FA_FWD_POLY
+#define FA_FWD_POLY 2      // pairs of every 8 whose exponential runs on the FMA pipe
+#endif
+enum { C_Q = 0, C_KF0, C_KF1, C_KE0, C_KE1, C_VF0, C_VF1, C_VE0, C_VE1, C_SA, C_SB, C_PA, C_PB, C_PA2, C_PB2, C_OA, C_OB, C_COUNT };
 
 template <typename T, int D>
 __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constant__ Sm100FwdArgs a) {
@@ -389,7 +392,7 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     }
 
     if (tid == 0) {
-        for (int i = 0; i < C_COUNT; ++i) mbar_init(bar(i), (i == C_PA || i == C_PB) ? 128u : 1u);
+        for (int i = 0; i < C_COUNT; ++i) mbar_init(bar(i), (i >= C_PA && i <= C_PB2) ? 128u : 1u);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -452,11 +455,16 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                 });
                 umma_commit_w(bar(C_SA + x));
             };
-            auto issue_pv = [&](int x, int st, int j) {
+            // P·V of tile x in two halves of 64 keys: the second half waits for its own barrier
+            auto issue_pv = [&](int x, int st, int j) -> bool {
                 const uint64_t bv = umma_desc_at(dV0, st * L::kKV);
                 const uint32_t d_o = tmem + 256 + x * 128, a_p = tmem + x * 128;
                 if (j > 0) umma_ts_wo<1, 0, 0>(d_o, a_p, bv, IDESC_PV); else umma_ts_wo<0, 0, 0>(d_o, a_p, bv, IDESC_PV);
-                static_for<1, 8>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
+                static_for<1, 4>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
+                if (!mbar_wait(bar(C_PA2 + x), j & 1, abort_flag, err, 11)) return false;
+                tc_fence_after();
+                static_for<4, 8>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
+                return true;
             };
             bool ok = mbar_wait(bar(C_Q), 0, abort_flag, err, 3);
             if (ok) ok = mbar_wait(bar(C_KF0), 0, abort_flag, err, 4);
@@ -474,7 +482,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                 if (ok) ok = mbar_wait(bar(C_VF0 + st), use & 1, abort_flag, err, 6);
                 if (!ok) break;
                 tc_fence_after();
-                issue_pv(0, st, j);
+                ok = issue_pv(0, st, j);
+                if (!ok) break;
                 if (more) {
                     ok = mbar_wait(bar(C_KF0 + st1), use1 & 1, abort_flag, err, 7);
                     if (!ok) break;
@@ -487,7 +496,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                     ok = mbar_wait(bar(C_PB), j & 1, abort_flag, err, 8);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_pv(1, st, j);
+                    ok = issue_pv(1, st, j);
+                    if (!ok) break;
                 }
                 umma_commit_w(bar(C_VE0 + st));
                 if (more) {
@@ -525,29 +535,36 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
             tc_fence_after();
             uint32_t sreg[4][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
+            for (int c = 0; c < 2; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
             tmem_wait_ld();
+            // the second half of the row is in flight while the first half is reduced
+#pragma unroll
+            for (int c = 2; c < 4; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
             const bool full = n0 >= lo_l && n0 + 127 <= hi_f;
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-            if (!full) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+            for (int hh = 0; hh < 2; ++hh) {
+                if (hh == 1) tmem_wait_ld();
+                if (!full) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int col = n0 + c * 32 + i;
-                        if (col < klo || col > khi) sreg[c][i] = 0xff800000u;     // -inf
+                    for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int col = n0 + c * 32 + i;
+                            if (col < klo || col > khi) sreg[c][i] = 0xff800000u;     // -inf
+                        }
                     }
                 }
-            }
-            // four independent chains of three-input maxima
+                // four independent chains of three-input maxima
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+                for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    mx0 = fmaxf(fmaxf(mx0, __uint_as_float(sreg[c][i])), __uint_as_float(sreg[c][i + 1]));
-                    mx1 = fmaxf(fmaxf(mx1, __uint_as_float(sreg[c][i + 2])), __uint_as_float(sreg[c][i + 3]));
-                    mx2 = fmaxf(fmaxf(mx2, __uint_as_float(sreg[c][i + 4])), __uint_as_float(sreg[c][i + 5]));
-                    mx3 = fmaxf(fmaxf(mx3, __uint_as_float(sreg[c][i + 6])), __uint_as_float(sreg[c][i + 7]));
+                    for (int i = 0; i < 32; i += 8) {
+                        mx0 = fmaxf(fmaxf(mx0, __uint_as_float(sreg[c][i])), __uint_as_float(sreg[c][i + 1]));
+                        mx1 = fmaxf(fmaxf(mx1, __uint_as_float(sreg[c][i + 2])), __uint_as_float(sreg[c][i + 3]));
+                        mx2 = fmaxf(fmaxf(mx2, __uint_as_float(sreg[c][i + 4])), __uint_as_float(sreg[c][i + 5]));
+                        mx3 = fmaxf(fmaxf(mx3, __uint_as_float(sreg[c][i + 6])), __uint_as_float(sreg[c][i + 7]));
+                    }
                 }
             }
             const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;       // log2 domain
@@ -570,30 +587,36 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
             const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
             const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(neg_m, neg_m);
             float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+            // NPOLY of every 8 pairs take the polynomial 2^x, spread evenly between the special-function ones
+            auto exp_phase = [&](auto npoly_c) {
+                constexpr int NPOLY = decltype(npoly_c)::value;
 #pragma unroll
-            for (int hlf = 0; hlf < 2; ++hlf) {
-                uint32_t preg[32];
+                for (int hlf = 0; hlf < 2; ++hlf) {
+                    uint32_t preg[32];
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const float2 xa = fma2(make_float2(__uint_as_float(sreg[2 * hlf + c][i]), __uint_as_float(sreg[2 * hlf + c][i + 1])), sc2, nm2);
-                        const float2 xb = fma2(make_float2(__uint_as_float(sreg[2 * hlf + c][i + 2]), __uint_as_float(sreg[2 * hlf + c][i + 3])), sc2, nm2);
-                        const float2 pa = make_float2(ex2_approx(xa.x), ex2_approx(xa.y));
-                        const float2 pb = make_float2(ex2_approx(xb.x), ex2_approx(xb.y));
-                        sum_a = add2(sum_a, pa);
-                        sum_b = add2(sum_b, pb);
-                        preg[c * 16 + i / 2] = Elem<T>::pack(pa.x, pa.y);
-                        preg[c * 16 + i / 2 + 1] = Elem<T>::pack(pb.x, pb.y);
+                    for (int g = 0; g < 4; ++g) {
+                        const uint32_t* src = &sreg[2 * hlf + (g >> 1)][(g & 1) * 16];
+                        static_for<0, 8>([&](auto pi) {
+                            constexpr bool poly = (pi.value * NPOLY) % 8 < NPOLY;
+                            const float2 xv = fma2(make_float2(__uint_as_float(src[2 * pi.value]), __uint_as_float(src[2 * pi.value + 1])), sc2, nm2);
+                            float2 pv;
+                            if constexpr (poly) pv = ex2_poly2(xv);
+                            else pv = make_float2(ex2_approx(xv.x), ex2_approx(xv.y));
+                            if constexpr (pi.value & 1) sum_b = add2(sum_b, pv); else sum_a = add2(sum_a, pv);
+                            preg[g * 8 + pi.value] = Elem<T>::pack(pv.x, pv.y);
+                        });
                     }
+                    tmem_st32(t_s + hlf * 32, preg);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(bar((hlf ? C_PA2 : C_PA) + x));
                 }
-                tmem_st32(t_s + hlf * 32, preg);
-            }
+            };
+            // masked tiles keep the special-function path: it maps -inf to an exact zero
+            if (full) exp_phase(std::integral_constant<int, FA_FWD_POLY>{});
+            else exp_phase(std::integral_constant<int, 0>{});
             const float s0 = sum_a.x + sum_b.x, s1 = sum_a.y + sum_b.y;
             l_run += s0 + s1;
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(C_PA + x));
         }
         if (ok) ok = mbar_wait(bar(C_OA + x), 0, abort_flag, err, 10);
         if (ok) {

@@ -297,6 +297,24 @@ __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
     return d;
 }
 
+// 2^x for two values on the FMA pipe instead of the special-function unit: x is split into its nearest integer n
+// (adding 1.5*2^23 leaves n in the low mantissa bits) and f = x - n in [-0.5, 0.5]; a degree-4 polynomial gives 2^f
+// to 2.7e-6 relative, and n is added to the exponent field.  Inputs below -125 return about 2^-125.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+    const float2 big = make_float2(12582912.f, 12582912.f);
+    x.x = fmaxf(x.x, -125.f);
+    x.y = fmaxf(x.y, -125.f);
+    const float2 r = add2(x, big);
+    const float2 n = add2(r, make_float2(-12582912.f, -12582912.f));
+    const float2 fr = fma2(n, make_float2(-1.f, -1.f), x);
+    float2 q = fma2(fr, make_float2(0.00957401655614376f, 0.00957401655614376f), make_float2(0.055918190628290176f, 0.055918190628290176f));
+    q = fma2(q, fr, make_float2(0.2402464896440506f, 0.2402464896440506f));
+    q = fma2(q, fr, make_float2(0.6931217312812805f, 0.6931217312812805f));
+    q = fma2(q, fr, make_float2(0.9999992847442627f, 0.9999992847442627f));
+    return make_float2(__uint_as_float(__float_as_uint(q.x) + (__float_as_uint(r.x) << 23)),
+                       __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(r.y) << 23)));
+}
+
 }  // namespace sm100
 
 // (dim, head, row, batch) view with a [64 x 1 x box_rows x 1] box and 128-byte swizzle (fwd_sm100.cu)

@@ -8,7 +8,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libfa_b200.so")
+# FA_B200_LIB points the loader at another build of the same library (a debug or tuning build)
+LIB_PATH = os.environ.get("FA_B200_LIB") or os.path.join(_HERE, "lib", "libfa_b200.so")
 
 
 class FaTensor(C.Structure):
