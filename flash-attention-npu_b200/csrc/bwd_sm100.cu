@@ -532,37 +532,55 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
 // ------------------------------------------------------------------------------------------------------
 // host
 // ------------------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void bwd_delta_sm100_kernel(const fa_bwd_params p, float* delta) {
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+// delta[row] = sum_d O[row, d] * dO[row, d].  HBM-bound: D/8 lanes share a row with one 16-byte load each of O and
+// dO, and every thread keeps kU rows in flight.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) bwd_delta_sm100_kernel(const fa_bwd_params p, float* delta) {
+    constexpr int LPR = D / 8, RPW = 32 / LPR, kU = 4;
+    const int lane = threadIdx.x & 31, sub = lane / LPR, c = (lane % LPR) * 8;
     const int64_t toks = p.cu_seqlens_q ? p.total_q : (int64_t)p.b * p.sq;
-    if (row >= toks * p.hq) return;
-    const int lane = threadIdx.x & 31;
-    const int64_t tok = row / p.hq;
-    const int h = (int)(row % p.hq);
-    int64_t ooff, doff;
-    if (p.cu_seqlens_q) {
-        ooff = tok * p.o.stride_s + (int64_t)h * p.o.stride_h;
-        doff = tok * p.dout.stride_s + (int64_t)h * p.dout.stride_h;
-    } else {
-        const int64_t bb = tok / p.sq, i = tok % p.sq;
-        ooff = bb * p.o.stride_b + i * p.o.stride_s + (int64_t)h * p.o.stride_h;
-        doff = bb * p.dout.stride_b + i * p.dout.stride_s + (int64_t)h * p.dout.stride_h;
-    }
-    const T* o = reinterpret_cast<const T*>(p.o.ptr) + ooff;
-    const T* d = reinterpret_cast<const T*>(p.dout.ptr) + doff;
-    float acc = 0.f;
-    for (int c = lane * 8; c < p.dv_dim; c += 256) {
-        const uint4 ov = *reinterpret_cast<const uint4*>(o + c);
-        const uint4 dv = *reinterpret_cast<const uint4*>(d + c);
-        const T* oe = reinterpret_cast<const T*>(&ov);
-        const T* de = reinterpret_cast<const T*>(&dv);
+    const int64_t rows = toks * p.hq;
+    const int64_t warp_g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t step = (int64_t)gridDim.x * (blockDim.x >> 5) * (kU * RPW);
+    const T* o_base = reinterpret_cast<const T*>(p.o.ptr);
+    const T* d_base = reinterpret_cast<const T*>(p.dout.ptr);
+    const bool small = rows < (1ll << 31);
+    for (int64_t base = warp_g * (kU * RPW); base < rows; base += step) {
+        uint4 ov[kU], dv[kU];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc += Elem<T>::to_float(oe[e]) * Elem<T>::to_float(de[e]);
-    }
+        for (int u = 0; u < kU; ++u) {
+            const int64_t row = base + u * RPW + sub;
+            ov[u] = make_uint4(0, 0, 0, 0);
+            dv[u] = make_uint4(0, 0, 0, 0);
+            if (row < rows) {
+                int64_t tok, bb = 0, i;
+                int h;
+                if (small) { const uint32_t r32 = (uint32_t)row; tok = r32 / (uint32_t)p.hq; h = (int)(r32 % (uint32_t)p.hq); }
+                else { tok = row / p.hq; h = (int)(row % p.hq); }
+                i = tok;
+                if (!p.cu_seqlens_q) {
+                    if (small) { bb = (uint32_t)tok / (uint32_t)p.sq; i = (uint32_t)tok % (uint32_t)p.sq; }
+                    else { bb = tok / p.sq; i = tok % p.sq; }
+                }
+                const int64_t ooff = bb * p.o.stride_b + i * p.o.stride_s + (int64_t)h * p.o.stride_h;
+                const int64_t doff = bb * p.dout.stride_b + i * p.dout.stride_s + (int64_t)h * p.dout.stride_h;
+                ov[u] = __ldg(reinterpret_cast<const uint4*>(o_base + ooff + c));
+                dv[u] = __ldg(reinterpret_cast<const uint4*>(d_base + doff + c));
+            }
+        }
 #pragma unroll
-    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-    if (lane == 0) delta[row] = acc;
+        for (int u = 0; u < kU; ++u) {
+            const T* oe = reinterpret_cast<const T*>(&ov[u]);
+            const T* de = reinterpret_cast<const T*>(&dv[u]);
+            float acc = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc += Elem<T>::to_float(oe[e]) * Elem<T>::to_float(de[e]);
+#pragma unroll
+            for (int sft = LPR / 2; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+            const int64_t row = base + u * RPW + sub;
+            if (c == 0 && row < rows) delta[row] = acc;
+        }
+    }
 }
 
 bool bwd_sm100_supported(const fa_bwd_params& p) {
@@ -585,7 +603,12 @@ template <typename T, int D>
 static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* delta, cudaStream_t st) {
     const int64_t toks = p.cu_seqlens_q ? p.total_q : (int64_t)p.b * p.sq;
     const int64_t rows = toks * p.hq;
-    bwd_delta_sm100_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p, delta);
+    {
+        constexpr int kRowsPerBlock = 8 * 4 * (32 / (D / 8));      // warps x rows in flight x rows per warp pass
+        const int64_t want = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+        const unsigned blocks = (unsigned)(want < 148 * 16 ? (want < 1 ? 1 : want) : 148 * 16);
+        bwd_delta_sm100_kernel<T, D><<<blocks, 256, 0, st>>>(p, delta);
+    }
     mark_kernel(st);
     auto k1 = bwd_dkdv_sm100_kernel<T, D>;
     auto k2 = bwd_dq_sm100_kernel<T, D>;
