@@ -100,20 +100,20 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(inside)}
 
 
-def cpu_oracle_sample(heads=2):
-    """The CPU oracle on one batch entry and `heads` heads of the workload (forward fp32 math on bf16
+def cpu_oracle_sample(heads=2, batch=1):
+    """The CPU oracle on `batch` batch entries and `heads` heads of the workload (forward fp32 math on bf16
     inputs, backward in float64 like the reference golden).  Returns (TFLOP/s, seconds, cores, text)."""
     from oracle import attention_oracle as orc
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     g = torch.Generator().manual_seed(0)
-    q, k, v, do = (torch.randn(1, S, heads, D, generator=g).bfloat16() for _ in range(4))
+    q, k, v, do = (torch.randn(batch, S, heads, D, generator=g).bfloat16() for _ in range(4))
     t0 = time.perf_counter()
     out, lse = orc.attention_fwd(q, k, v, SCALE, causal=True)
     orc.attention_bwd(q, k, v, do, lse, SCALE, causal=True, head_chunk=1)
     dt = time.perf_counter() - t0
-    flops = STEP_FLOPS * heads / (B * H)
-    return flops / dt / 1e12, dt, cores, f"1 of {B} batch entries x {heads} of {H} heads of the workload, fwd + bwd"
+    flops = STEP_FLOPS * heads * batch / (B * H)
+    return flops / dt / 1e12, dt, cores, f"{batch} of {B} batch entries x {heads} of {H} heads of the workload, fwd + bwd"
 
 
 def run_reference(args, rank):
@@ -268,12 +268,22 @@ def main():
     h2d = sum(t.numel() * 2 for t in host)
     d2h = sum(t.numel() * 2 for t in (out_h, gq_h, gk_h, gv_h))
 
-    decode = None
+    decode = varlen = mla = None
     if rank == 0 and not args.no_decode:
+        # side measurements of the other single-GPU configurations; none may take the headline down
         try:
             decode = paged_decode_side_measurement(dev)
-        except Exception as exc:  # the side measurement must not take the headline down
+        except Exception as exc:
             decode = {"error": str(exc)[:200]}
+        try:
+            varlen = varlen_side_measurement(dev)
+        except Exception as exc:
+            varlen = {"error": str(exc)[:200]}
+        try:
+            mla = mla_side_measurement(dev)
+        except Exception as exc:
+            mla = {"error": str(exc)[:200]}
+        torch.cuda.empty_cache()
 
     if rank != 0:
         if world > 1:
@@ -314,8 +324,12 @@ def main():
     }
     if decode is not None:
         line["paged_decode"] = decode
+    if varlen is not None:
+        line["varlen_fwd"] = varlen
+    if mla is not None:
+        line["mla_decode"] = mla
     if not args.no_cpu and world == 1:
-        v_cpu, dt, cores, sample = cpu_oracle_sample(2)
+        v_cpu, dt, cores, sample = cpu_oracle_sample(H, 2)      # 10-30 s of host work
         line["cpu_baseline"] = {"value": v_cpu, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
                                 "seconds": dt}
     else:
@@ -376,6 +390,80 @@ def paged_decode_side_measurement(dev, iters=10):
             "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": bytes_, "kernel": kern,
             "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8000": gbs / 8000.0,
             "cache_gb": pool * page * hkv * d * 2 * 2 / 1e9}
+
+
+def _time_calls(call, iters, warm=3):
+    for _ in range(warm):
+        call()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        call()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def varlen_side_measurement(dev, iters=10):
+    """BASELINE configuration 3 (packed forward, 16 sequences with lengths U[256,8192], Hq32 Hkv8 D128,
+    causal): forward TFLOP/s over the unmasked half of every sequence's score matrix."""
+    import flash_attn_npu as fa
+    import fa_b200_capi as capi
+    g = torch.Generator().manual_seed(3)
+    hq, hkv, d = 32, 8, 128
+    lens = torch.randint(256, 8193, (16,), generator=g)
+    cu = torch.zeros(17, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens, 0)
+    total, mx = int(cu[-1]), int(lens.max())
+    q = torch.randn(total, hq, d, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(total, hkv, d, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(total, hkv, d, device=dev, dtype=torch.bfloat16)
+    cu_d = cu.to(dev)
+    ms = _time_calls(lambda: fa.flash_attn_varlen_func(q, k, v, cu_d, cu_d, mx, mx, causal=True), iters)
+    flops = float(sum(4.0 * hq * int(n) * int(n) * d / 2.0 for n in lens))
+    peaks = measured_peaks()
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"workload": "config3: flash_attn_varlen_func fwd bf16 16 seqs L~U[256,8192] Hq32 Hkv8 D128 causal",
+            "ms": ms, "value": tf, "unit": "TFLOP/s", "flops": flops, "tokens": total, "kernel": capi.last_kernel(),
+            "frac_of_measured_bf16": tf / peaks["bf16_tflops"], "frac_of_nominal_2250": tf / 2250.0}
+
+
+def mla_side_measurement(dev, iters=10):
+    """BASELINE configuration 5 (latent-attention decode, B64 Sq1 Hq128 against one latent head: 512 int8 +
+    fp32 scale + 64 bf16 positional values per cached token, page 256, lengths U[4096,131072]): achieved HBM
+    GB/s over 644 B per cached token plus q / out / table."""
+    import flash_attn_npu_3 as fa3
+    import fa_b200_capi as capi
+    g = torch.Generator().manual_seed(5)
+    b, hq, dl, dr, page = 64, 128, 512, 64, 256
+    lens = torch.randint(4096, 131073, (b,), generator=g, dtype=torch.int32)
+    nblk = (lens + page - 1) // page
+    pool = int(nblk.sum())
+    perm = torch.randperm(pool, generator=g).int()
+    table = torch.zeros(b, int(nblk.max()), dtype=torch.int32)
+    off = 0
+    for i in range(b):
+        n = int(nblk[i])
+        table[i, :n] = perm[off:off + n]
+        off += n
+    lat = torch.randint(-127, 128, (pool, page, dl), device=dev, dtype=torch.int8)
+    scales = torch.rand(pool, page, device=dev, dtype=torch.float32) * 0.02 + 0.001
+    rope = torch.randn(pool, page, dr, device=dev, dtype=torch.bfloat16)
+    qn = torch.randn(b, 1, hq, dl, device=dev, dtype=torch.bfloat16)
+    qr = torch.randn(b, 1, hq, dr, device=dev, dtype=torch.bfloat16)
+    lens_d, table_d = lens.to(dev), table.to(dev)
+    ms = _time_calls(lambda: fa3.flash_attn_mla_with_kvcache(qn, qr, lat, scales, rope, lens_d, table_d), iters)
+    tokens = int(lens.sum())
+    bytes_ = tokens * (dl + dr * 2 + 4) + b * hq * (dl + dr) * 2 + b * hq * dl * 2 + table.numel() * 4
+    flops = 2.0 * tokens * hq * (dl + dr + dl)
+    peaks = measured_peaks()
+    gbs = bytes_ / (ms * 1e-3) / 1e9
+    return {"workload": "config5: int8 latent decode B64 Sq1 Hq128 Hkv1 (512 int8 + 64 bf16) page256 L~U[4096,131072]",
+            "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": bytes_, "kernel": capi.last_kernel(),
+            "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8000": gbs / 8000.0,
+            "tflops": flops / (ms * 1e-3) / 1e12, "tensor_time_bound_ms": flops / (peaks["bf16_tflops"] * 1e12) * 1e3,
+            "hbm_time_bound_ms": bytes_ / (peaks["hbm_gbs"] * 1e9) * 1e3}
 
 
 if __name__ == "__main__":

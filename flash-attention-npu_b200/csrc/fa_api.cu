@@ -289,5 +289,8 @@ void fa_set_kernel_events(void** events, int count) {
 }
 int fa_kernel_events_used(void) { return g_event_idx; }
 void fa_set_kernel_policy(int policy) { g_policy = policy; }
+}  // extern "C"
+namespace fa { int kernel_policy() { return g_policy; } }
+extern "C" {
 
 }  // extern "C"

@@ -48,6 +48,13 @@ int launch_fwd_combine(const fa_fwd_params& p, int nsplit, const float* o_part, 
 int combine_flat(const fa_combine_params& c);
 int combine_flat_keep(const fa_combine_params& c);
 int launch_bwd_generic(const fa_bwd_params& p);
+// 0 = automatic kernel choice, 1 = generic kernels only (fa_set_kernel_policy)
+int kernel_policy();
+// int8 latent decode on tcgen05 (mla_sm100.cu)
+bool mla_sm100_supported(const fa_mla_params& p);
+int launch_mla_sm100(const fa_mla_params& p, int nsplit, int tokens_per_split, float* o_part, float* lse_part,
+                     int final_direct, cudaStream_t st);
+int mla_sm100_error_flag(bool clear);
 int launch_bwd_sm100(const fa_bwd_params& p);
 bool bwd_sm100_supported(const fa_bwd_params& p);
 size_t bwd_generic_workspace(const fa_bwd_params& p);

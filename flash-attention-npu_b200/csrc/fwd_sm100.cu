@@ -754,7 +754,8 @@ int sm100_error_flag(bool clear) {
     cudaMemcpyFromSymbol(&v, g_fwd_sm100_error, sizeof(int));
     if (clear) { int z = 0; cudaMemcpyToSymbol(g_fwd_sm100_error, &z, sizeof(int)); }
     const int w = bwd_sm100_error_flag(clear);
-    return v ? v : w;
+    const int m = mla_sm100_error_flag(clear);
+    return v ? v : (w ? w : m);
 }
 
 }  // namespace fa

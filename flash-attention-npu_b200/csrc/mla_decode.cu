@@ -303,13 +303,17 @@ int fa_mla_decode(const fa_mla_params* pp) {
         }
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
-    const int smem = 3 * kMlaTile * kMlaPitch;
-    if (int e = cuda_ok(cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-    dim3 grid(a.nsplit, (p.hq + kMlaHeadsPerCta - 1) / kMlaHeadsPerCta, p.b);
-    note_kernel("mla_int8_decode");
-    mla_decode_kernel<<<grid, 256, smem, st>>>(a);
-    mark_kernel(st);
-    if (int e = cuda_ok(cudaGetLastError(), "mla_decode launch")) return e;
+    if (kernel_policy() == 0 && mla_sm100_supported(p)) {
+        if (int e = launch_mla_sm100(p, a.nsplit, a.tokens_per_split, a.o_part, a.lse_part, a.final_direct, st)) return e;
+    } else {
+        const int smem = 3 * kMlaTile * kMlaPitch;
+        if (int e = cuda_ok(cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+        dim3 grid(a.nsplit, (p.hq + kMlaHeadsPerCta - 1) / kMlaHeadsPerCta, p.b);
+        note_kernel("mla_int8_decode");
+        mla_decode_kernel<<<grid, 256, smem, st>>>(a);
+        mark_kernel(st);
+        if (int e = cuda_ok(cudaGetLastError(), "mla_decode launch")) return e;
+    }
     if (a.nsplit > 1) {
         fa_combine_params c = {};
         c.o_partial = a.o_part; c.lse_partial = a.lse_part;
