@@ -232,7 +232,9 @@ static void plan_mla(const fa_mla_params& p, int& nsplit, int& tps, int max_len)
     long n = 1;
     if (p.num_splits > 1) n = p.num_splits;
     else if (p.num_splits == 0) {
-        const long by_bal = (max_len + 2047) / 2048;
+        // the tcgen05 kernel stages all of Q (144 KB) per CTA, so its splits are longer
+        const long per_split = (kernel_policy() == 0 && mla_sm100_supported(p)) ? 8192 : 2048;
+        const long by_bal = (max_len + per_split - 1) / per_split;
         const long base = 2L * (p.b > 0 ? p.b : 1);
         const long by_occ = (2L * sm_count() + base - 1) / base;
         const long cap = (max_len + 255) / 256;

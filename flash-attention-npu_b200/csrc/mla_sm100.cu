@@ -5,12 +5,12 @@
 //
 // A 128 x 512 fp32 output accumulator fills the whole tensor memory of an SM, so a CTA owns one HALF of the
 // output columns (256 TMEM columns) and both halves compute the scores; what is left holds two 64-column score
-// buffers.  CTA = (KV split, output half, sequence x head tile).  13 warps:
+// buffers.  CTA = (KV split, output half, sequence x head tile).  16 warps:
 //   warps 0-3   softmax: thread = head row; S from TMEM, P (bf16) back into the same columns, epilogue
 //   warps 4-11  producers: int8 rows -> registers -> (x - 0) * scale -> bf16 -> swizzled shared memory in the
 //               UMMA layout, one tile of 64 tokens at a time; the same bytes are the K operand of Q K^T and the
 //               V operand of P V
-//   warp 12     issues the MMAs, owns the tensor memory
+//   warp 12     issues the MMAs, owns the tensor memory (warps 13-15 idle: register reallocation works on groups of 4)
 // Shared memory holds Q (128 x 576 bf16 = 144 KB) and ONE dequantised tile (64 x 576 bf16 = 72 KB).  The tile is
 // split into an "early" group (the 256 latent columns of the OTHER half + rope) that only Q K^T reads, and a
 // "late" group (the CTA's own 256 columns) that P V reads too: the early group of tile j+1 is refilled and
@@ -41,7 +41,7 @@ constexpr int kKSub = kTile * 128;              // bytes of one [64 tokens x 64 
 constexpr int kSmemQ = 9 * kQSub, kSmemK = 9 * kKSub;
 constexpr int kSmemBar = kSmemQ + kSmemK;
 constexpr int kSmemBytes = kSmemBar + 256 + 1024;
-constexpr int kThreads = 13 * 32;
+constexpr int kThreads = 16 * 32;               // warps 13-15 only complete the last warp group
 enum { M_KF_E = 0, M_KF_L, M_KE_E, M_KE_L, M_S0, M_S1, M_P0, M_P1, M_O, M_COUNT };
 
 struct MlaSm100Args {
@@ -156,7 +156,12 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sm100_kernel(const __grid_con
     int* err = &g_mla_sm100_error;
     const int own0 = half * 4, oth0 = (1 - half) * 4;                      // first sub-tile of the own / other half
 
-    if (warp == 12) {
+    // Register file split by warp group (the CTA starts with 128 a thread): 96 for the MMA group and for the two
+    // producer groups, 224 for the softmax group; 128*96 + 256*96 + 128*224 = 512*128.
+    static_assert(128 * 96 + 256 * 96 + 128 * 224 <= 512 * 128, "register split exceeds the CTA's allocation");
+    if (warp >= 12) {
+        reg_dealloc<96>();
+        if (warp == 12) {
         // ------------------------------------------------------------------ MMA issue (whole warp, one elected lane)
         const uint64_t dQ = umma_desc(sQ, 16, 1024), dK = umma_desc(sK, 16, 1024);
         const uint64_t dV = umma_desc(sK + own0 * kKSub, kKSub, 1024);     // MN-major: four 64-column groups kKSub apart
@@ -202,7 +207,9 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sm100_kernel(const __grid_con
             umma_commit_w(bar(M_KE_L));
         }
         if (ok) umma_commit_w(bar(M_O));
+        }
     } else if (warp >= 4) {
+        reg_dealloc<96>();
         // ------------------------------------------------------------------ producers: dequantise into shared memory
         const int pw = warp - 4;
         const int cl = lane & 15;                                         // 16-byte chunk of a 256-value half row
@@ -279,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sm100_kernel(const __grid_con
         for (int j = 0; j < ntiles && ok; ++j) {
 #pragma unroll
             for (int r = 0; r < 4; ++r) sc[r] = sc_next[r];
-            if (j > 0) ok = mbar_wait(bar(M_KE_E), (j - 1) & 1, abort_flag, err, 25);
+            if (j > 0) ok = mbar_wait_relaxed(bar(M_KE_E), (j - 1) & 1, abort_flag, err, 25);
             if (!ok) break;
             store_group(oth0, regE);
             store_rope();
@@ -291,13 +298,14 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sm100_kernel(const __grid_con
                 load_group(j + 1, oth0 * 64, regE, true);
                 load_rope(j + 1);
             }
-            if (j > 0) ok = mbar_wait(bar(M_KE_L), (j - 1) & 1, abort_flag, err, 26);
+            if (j > 0) ok = mbar_wait_relaxed(bar(M_KE_L), (j - 1) & 1, abort_flag, err, 26);
             if (!ok) break;
             store_group(own0, regL);
             publish(M_KF_L);
             if (j + 1 < ntiles) load_group(j + 1, own0 * 64, regL, false);
         }
     } else {
+        reg_alloc<224>();
         // ------------------------------------------------------------------ softmax: thread = head row
         const int r = tid;                                                 // 0..127
         const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
