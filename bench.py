@@ -148,12 +148,17 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode side measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "decode", "mla"],
+                    help="run two calls of one kernel on a small case (for a profiler capture) and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.profile_case:
+        profile_case(args.profile_case)
         return
     args.warmup = max(args.warmup, 3)
 
@@ -390,6 +395,59 @@ def paged_decode_side_measurement(dev, iters=10):
             "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": bytes_, "kernel": kern,
             "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8000": gbs / 8000.0,
             "cache_gb": pool * page * hkv * d * 2 * 2 / 1e9}
+
+
+def profile_case(name):
+    """Two calls of one kernel family on a case small enough for a full profiler capture (a few hundred MB on the
+    device, inputs still larger than L2 where the kernel is memory-bound)."""
+    import fa_b200_capi as capi
+    import flash_attn_npu as fa
+    import flash_attn_npu_3 as fa3
+    from flash_attn_npu import flash_attn_npu as ext
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(11)
+    if name in ("fwd", "bwd"):
+        b, s, h, d = 2, 4096, 32, 128
+        q, k, v, do = (torch.randn(b, s, h, d, device=dev).bfloat16() for _ in range(4))
+        for _ in range(2):
+            out, lse, _, _ = ext.fwd(q, k, v, None, None, 0.0, d ** -0.5, True, -1, -1, 0.0, False, None)
+            if name == "bwd":
+                ext.bwd(do, q, k, v, out, lse, None, None, None, None, 0.0, d ** -0.5, True, -1, -1, 0.0, False, None, None)
+    else:
+        page = 256
+        b = 16
+        lo, hi = (1024, 32769) if name == "decode" else (4096, 65537)
+        lens = torch.randint(lo, hi, (b,), generator=g, dtype=torch.int32)
+        nblk = (lens + page) // page
+        pool = int(nblk.sum())
+        perm = torch.randperm(pool, generator=g).int()
+        table = torch.zeros(b, int(nblk.max()), dtype=torch.int32)
+        off = 0
+        for i in range(b):
+            n = int(nblk[i])
+            table[i, :n] = perm[off:off + n]
+            off += n
+        lens_d, table_d = lens.to(dev), table.to(dev)
+        if name == "decode":
+            hq, hkv, d = 32, 8, 128
+            kc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
+            vc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
+            q = torch.randn(b, 1, hq, d, device=dev, dtype=torch.bfloat16)
+            print("cached tokens", int(lens.sum()), "algorithmic bytes", int(lens.sum()) * hkv * d * 4)
+            for _ in range(2):
+                fa.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=lens_d, block_table=table_d, causal=True)
+        else:
+            hq, dl, dr = 128, 512, 64
+            lat = torch.randint(-127, 128, (pool, page, dl), device=dev, dtype=torch.int8)
+            scales = torch.rand(pool, page, device=dev, dtype=torch.float32) * 0.02 + 0.001
+            rope = torch.randn(pool, page, dr, device=dev, dtype=torch.bfloat16)
+            qn = torch.randn(b, 1, hq, dl, device=dev, dtype=torch.bfloat16)
+            qr = torch.randn(b, 1, hq, dr, device=dev, dtype=torch.bfloat16)
+            print("cached tokens", int(lens.sum()), "algorithmic bytes", int(lens.sum()) * (dl + 2 * dr + 4))
+            for _ in range(2):
+                fa3.flash_attn_mla_with_kvcache(qn, qr, lat, scales, rope, lens_d, table_d)
+    torch.cuda.synchronize()
+    print("profile case", name, "kernel", capi.last_kernel(), "error flag", capi.lib.fa_debug_get(2))
 
 
 def _time_calls(call, iters, warm=3):
