@@ -10,6 +10,7 @@ namespace fa {
 static thread_local char g_err[512] = "";
 static thread_local const char* g_kernel = "";
 static int g_policy = 0;
+static int g_mla_variant = 0;     // 0: CTA-pair latent decode, 1: single-CTA kernel (fa_debug_set key 5)
 // optional per-kernel timing: the caller lends CUDA events, one is recorded after every launch
 static thread_local cudaEvent_t* g_events = nullptr;
 static thread_local int g_nevents = 0, g_event_idx = 0;
@@ -276,6 +277,7 @@ void fa_debug_set(int key, int value) {
     if (key == 1) fa::fwd_sm100_set_p_in_tmem(value);
     if (key == 3) { fa::sm100_error_flag(true); fa::decode_error_flag(true); }
     if (key == 4) fa::decode_set_use_tma(value);
+    if (key == 5) g_mla_variant = value;
 }
 int fa_debug_get(int key) {
     if (key != 2) return 0;
@@ -290,7 +292,7 @@ void fa_set_kernel_events(void** events, int count) {
 int fa_kernel_events_used(void) { return g_event_idx; }
 void fa_set_kernel_policy(int policy) { g_policy = policy; }
 }  // extern "C"
-namespace fa { int kernel_policy() { return g_policy; } }
+namespace fa { int kernel_policy() { return g_policy; } int mla_variant() { return g_mla_variant; } }
 extern "C" {
 
 }  // extern "C"

@@ -50,11 +50,18 @@ int combine_flat_keep(const fa_combine_params& c);
 int launch_bwd_generic(const fa_bwd_params& p);
 // 0 = automatic kernel choice, 1 = generic kernels only (fa_set_kernel_policy)
 int kernel_policy();
+// 0 = CTA-pair latent-decode kernel preferred, 1 = single-CTA kernel (fa_debug_set key 5)
+int mla_variant();
 // int8 latent decode on tcgen05 (mla_sm100.cu)
 bool mla_sm100_supported(const fa_mla_params& p);
 int launch_mla_sm100(const fa_mla_params& p, int nsplit, int tokens_per_split, float* o_part, float* lse_part,
                      int final_direct, cudaStream_t st);
 int mla_sm100_error_flag(bool clear);
+// the same over a pair of CTAs that split the score dimensions (mla_sm100_pair.cu)
+bool mla_pair_supported(const fa_mla_params& p);
+int launch_mla_pair(const fa_mla_params& p, int nsplit, int tokens_per_split, float* o_part, float* lse_part,
+                    int final_direct, cudaStream_t st);
+int mla_pair_error_flag(bool clear);
 int launch_bwd_sm100(const fa_bwd_params& p);
 bool bwd_sm100_supported(const fa_bwd_params& p);
 size_t bwd_generic_workspace(const fa_bwd_params& p);

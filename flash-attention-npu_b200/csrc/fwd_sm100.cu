@@ -755,7 +755,8 @@ int sm100_error_flag(bool clear) {
     if (clear) { int z = 0; cudaMemcpyToSymbol(g_fwd_sm100_error, &z, sizeof(int)); }
     const int w = bwd_sm100_error_flag(clear);
     const int m = mla_sm100_error_flag(clear);
-    return v ? v : (w ? w : m);
+    const int m2 = mla_pair_error_flag(clear);
+    return v ? v : (w ? w : (m ? m : m2));
 }
 
 }  // namespace fa

@@ -305,7 +305,9 @@ int fa_mla_decode(const fa_mla_params* pp) {
         }
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
-    if (kernel_policy() == 0 && mla_sm100_supported(p)) {
+    if (kernel_policy() == 0 && mla_variant() == 0 && mla_pair_supported(p)) {
+        if (int e = launch_mla_pair(p, a.nsplit, a.tokens_per_split, a.o_part, a.lse_part, a.final_direct, st)) return e;
+    } else if (kernel_policy() == 0 && mla_sm100_supported(p)) {
         if (int e = launch_mla_sm100(p, a.nsplit, a.tokens_per_split, a.o_part, a.lse_part, a.final_direct, st)) return e;
     } else {
         const int smem = 3 * kMlaTile * kMlaPitch;
