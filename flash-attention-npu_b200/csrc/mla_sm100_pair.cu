@@ -198,45 +198,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
         const int sub_l = cl >> 2, cp = cl & 3;
         const int32_t* btab = p.block_table + (int64_t)b * p.block_table_stride;
         const int rrow = (tid - 128) >> 2, rch = (tid - 128) & 3;         // rope: 64 rows x 8 chunks, two per thread
-        uint4 regN[4], regR[2];
-        float sc[4];
+        // two tiles of operands live in registers: a tile's loads are issued two iterations before they are stored, so
+        // that HBM latency (longer than one tile's work) stays off the critical path
+        uint4 regN[2][4], regR[2][2];
+        float sc[2][4];
         auto tile_row = [&](int j) -> int64_t {                           // first cache row of tile j (inside one page)
             const int t0 = t_begin + j * kTile;
             const int jj = t0 < t_end ? t0 : t_begin;
             return (int64_t)__ldg(btab + jj / p.page_size) * p.page_size + jj % p.page_size;
         };
-        int64_t slot_next = tile_row(1);
-        auto load_tile = [&](int j, int64_t slot0) {
+        auto load_tile = [&](auto par, int j, int64_t slot0) {
+            constexpr int P = decltype(par)::value;
             const int t0 = t_begin + j * kTile;
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const int row = r * 16 + krow;
                 const bool live = t0 + row < t_end;
-                regN[r] = make_uint4(0, 0, 0, 0);                      // rows past the end become zero keys and values
-                if (live) regN[r] = __ldg(reinterpret_cast<const uint4*>(p.latent + (slot0 + row) * kLat + rank * 256 + cl * 16));
-                sc[r] = live ? __ldg(p.scales + slot0 + row) : 0.f;
+                regN[P][r] = make_uint4(0, 0, 0, 0);                   // rows past the end become zero keys and values
+                if (live) regN[P][r] = __ldg(reinterpret_cast<const uint4*>(p.latent + (slot0 + row) * kLat + rank * 256 + cl * 16));
+                sc[P][r] = live ? __ldg(p.scales + slot0 + row) : 0.f;
             }
             if (rank == 0) {
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
-                    regR[i] = make_uint4(0, 0, 0, 0);
+                    regR[P][i] = make_uint4(0, 0, 0, 0);
                     if (t0 + rrow < t_end)
-                        regR[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.rope) + (slot0 + rrow) * kRope + (rch * 2 + i) * 8));
+                        regR[P][i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.rope) + (slot0 + rrow) * kRope + (rch * 2 + i) * 8));
                 }
             }
         };
-        load_tile(0, tile_row(0));
+        int64_t row_next = tile_row(2);                                    // page-table entries are fetched one tile earlier still
         bool ok = true;
-        for (int j = 0; j < ntiles && ok; ++j) {
-            const int s = j & 1;
-            if (j >= 2) ok = mbar_wait_relaxed(bar(P_KE0 + s), ((j >> 1) - 1) & 1, abort_flag, err, 33);
-            if (!ok) break;
-            unsigned char* kbuf = sgen + kOffK + s * kKBuf;
+        auto body = [&](auto par, int j) {
+            constexpr int P = decltype(par)::value;                        // = j & 1: register set and tile buffer
+            if (j >= 2) ok = mbar_wait_relaxed(bar(P_KE0 + P), ((j >> 1) - 1) & 1, abort_flag, err, 33);
+            if (!ok) return;
+            unsigned char* kbuf = sgen + kOffK + P * kKBuf;
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const int row = r * 16 + krow;
                 uint4 lo, hi;
-                dequant16(regN[r], sc[r], lo, hi);
+                dequant16(regN[P][r], sc[P][r], lo, hi);
                 unsigned char* base = kbuf + sub_l * kKSub + row * 128;
                 const int c0 = (2 * cp) ^ (row & 7), c1 = (2 * cp + 1) ^ (row & 7);
                 // the two sub-tiles a quarter warp touches store their even / odd chunks in opposite order
@@ -252,17 +254,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     const int ch = rch * 2 + i;
-                    *reinterpret_cast<uint4*>(kbuf + 4 * kKSub + rrow * 128 + ((ch ^ (rrow & 7)) << 4)) = regR[i];
+                    *reinterpret_cast<uint4*>(kbuf + 4 * kKSub + rrow * 128 + ((ch ^ (rrow & 7)) << 4)) = regR[P][i];
                 }
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(P_KF0 + s));
-            if (j + 1 < ntiles) {
-                const int64_t slot0 = slot_next;
-                slot_next = tile_row(j + 2);
-                load_tile(j + 1, slot0);
+            if (lane == 0) mbar_arrive(bar(P_KF0 + P));
+            if (j + 2 < ntiles) {
+                const int64_t slot0 = row_next;
+                row_next = tile_row(j + 3);
+                load_tile(par, j + 2, slot0);
             }
+        };
+        load_tile(std::integral_constant<int, 0>{}, 0, tile_row(0));
+        if (ntiles > 1) load_tile(std::integral_constant<int, 1>{}, 1, tile_row(1));
+        for (int j = 0; j < ntiles && ok; j += 2) {
+            body(std::integral_constant<int, 0>{}, j);
+            if (ok && j + 1 < ntiles) body(std::integral_constant<int, 1>{}, j + 1);
         }
         }
     } else {
@@ -310,7 +318,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
                     d[3] = __float_as_uint(__uint_as_float(d[3]) + v.w);
                 }
             }
-            mbar_arrive_remote(map_to_cta(bar(P_RC0 + s), peer));          // the peer may overwrite my buffer s again
+            // the values read above have been used, so the buffer may be overwritten: no release needed
+            mbar_arrive_remote_relaxed(map_to_cta(bar(P_RC0 + s), peer));
             const int valid = t_end - (t_begin + j * kTile);               // tokens of this tile that exist
             if (valid < kTile) {
 #pragma unroll
