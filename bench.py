@@ -38,6 +38,11 @@ STEP_FLOPS = FWD_FLOPS + BWD_FLOPS
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
+# DRAM bytes of one dK/dV launch at B2 S4096 H32 D128 causal from the committed ncu capture (271.1 MB read + 108.6 MB
+# written); the traffic grows in proportion to the batch
+DKDV_TRAFFIC_B2 = 379.7e6
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -331,12 +336,14 @@ def main():
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "kernels_ms": {n: t for n, t, _ in parts},
         "roofline": {"bound": "tensor", "kernel": dom[0], "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                     "frac": achieved / peak, "traffic": None,
+                     "frac": achieved / peak, "traffic": DKDV_TRAFFIC_B2 * (B / 2.0) if dom[0] == "bwd:dk_dv" else None,
+                     "traffic_source": "ncu dram__bytes_read+write of the B2 case of the same kernel "
+                                       "(profiles/bwd_sm100_kernels_B2_S4096_H32_D128_causal.md) scaled by batch",
                      "peak_source": peaks["_source"] + (" sustained" if sustained else " burst") + " cuBLAS bf16",
                      "frac_of_nominal_2250": achieved / 2250.0,
                      "fwd_frac": FWD_FLOPS / (fwd_ms * 1e-3) / 1e12 / peak},
         "e2e": {"value": STEP_FLOPS * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms},
         "gpu_launches": launches,
         "clocks": clocks,
     }
