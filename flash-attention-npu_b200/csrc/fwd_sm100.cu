@@ -652,6 +652,389 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Persistent variant of the kernel above: one CTA per SM walks a static list of (query block pair, head, batch)
+// items, heaviest query blocks first.  All barriers keep running across items (their parities come from running
+// counts of tiles and items), so the copy warp already loads Q, K and V of the next item and the MMA warp already
+// multiplies its first Q K^T while the softmax warps still write the previous item's output; only the first P V of
+// an item waits until the accumulator has been read out (C_OFA / C_OFB), and the Q buffer is reloaded once the
+// last Q K^T of the previous item has completed (C_QE).
+enum { C3_QE = C_COUNT, C3_OFA, C3_OFB, C3_COUNT };
+
+template <typename T, int D>
+__global__ void __launch_bounds__(384, 1) fwd_sm100_kernel3(const __grid_constant__ Sm100FwdArgs a, const int mblocks, const int items) {
+    using L = FwdSm100Smem2<D>;
+    constexpr int NSUB = D / 64;
+    constexpr int KSTEPS = D / 16;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
+    constexpr uint32_t IDESC_QK = umma_idesc(FMT, 128, 128, 0, 0);
+    constexpr uint32_t IDESC_PV = umma_idesc(FMT, 128, D, 0, 1);
+    constexpr float kRescaleThreshold = 8.f;
+    static_assert(8 * C3_COUNT + 16 <= 256, "barrier area");
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
+    const uint32_t sQ = sbase + L::oQ, sK = sbase + L::oK, sV = sbase + L::oV;
+    const uint32_t bars = sbase + L::oBar;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * C3_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * C3_COUNT + 8);
+    auto bar = [&](int i) { return bars + 8u * i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (g_fwd_sm100_error) return;
+    const int wl = a.wl, wr = a.causal ? 0 : a.wr;
+    const int heads_batch = a.hq * a.b;
+
+    struct Item {
+        int b, h, hk, m0, sq, sk, q_off, k_off, rows_cta, t_lo, ntiles;
+        bool has_b, live;
+    };
+    // items are sorted heaviest first; successive rounds hand them to the CTAs in alternating direction, which
+    // keeps the per-CTA totals within about 1 % of each other for causal masks
+    auto item_of = [&](int rnd) {
+        const int c = (rnd & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+        return rnd * (int)gridDim.x + c;
+    };
+    auto decode = [&](int t) {
+        Item it;
+        const int mblk = mblocks - 1 - t / heads_batch, rem = t % heads_batch;
+        it.h = rem % a.hq;
+        it.b = rem / a.hq;
+        it.hk = it.h / (a.hq / a.hkv);
+        it.q_off = 0; it.k_off = 0; it.sq = a.sq; it.sk = a.sk;
+        if (a.cu_q) {
+            it.q_off = a.cu_q[it.b]; it.sq = a.cu_q[it.b + 1] - it.q_off;
+            it.k_off = a.cu_k[it.b]; it.sk = a.cu_k[it.b + 1] - it.k_off;
+        }
+        it.m0 = mblk * 256;
+        it.live = it.m0 < it.sq;
+        it.rows_cta = min(256, it.sq - it.m0);
+        it.has_b = it.rows_cta > 128;
+        it.t_lo = 0; it.ntiles = 0;
+        if (it.live) {
+            int lo_first, hi_first, lo_last, hi_last;
+            window_bounds(it.m0, it.sq, it.sk, wl, wr, lo_first, hi_first);
+            window_bounds(it.m0 + it.rows_cta - 1, it.sq, it.sk, wl, wr, lo_last, hi_last);
+            int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
+            if (it.sk <= 0 || lo_first >= it.sk) { t_lo = 0; t_hi = 0; }
+            it.t_lo = t_lo;
+            it.ntiles = max(0, t_hi - t_lo);
+        }
+        return it;
+    };
+
+    if (tid == 0) {
+        for (int i = 0; i < C3_COUNT; ++i)
+            mbar_init(bar(i), ((i >= C_PA && i <= C_PB2) || i == C3_OFA || i == C3_OFB) ? 128u : 1u);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    int* err = &g_fwd_sm100_error;
+
+    static_assert(128 * 48 + 256 * 224 <= 384 * 168, "register split exceeds the CTA's allocation");
+    if (warp >= 8) {
+    reg_dealloc<48>();
+    if (warp == 8) {
+        if (lane == 0) {
+            tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
+            int gt = 0, ni = 0;                       // tiles and items (with keys) so far
+            bool ok = true;
+            for (int rnd = 0; rnd * (int)gridDim.x < items && ok; ++rnd) {
+                const int t = item_of(rnd);
+                if (t >= items) continue;
+                const Item it = decode(t);
+                if (!it.live || it.ntiles == 0) continue;
+                const int qrow0 = (a.cu_q ? it.q_off : 0) + it.m0, qb = a.cu_q ? 0 : it.b;
+                if (ni > 0) ok = mbar_wait(bar(C3_QE), (ni - 1) & 1, abort_flag, err, 12);
+                if (!ok) break;
+                mbar_expect_tx(bar(C_Q), it.has_b ? 2 * L::kQ : L::kQ);
+#pragma unroll
+                for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, it.h, qrow0, qb);
+                if (it.has_b) {
+#pragma unroll
+                    for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + L::kQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, it.h, qrow0 + 128, qb);
+                }
+                for (int j = 0; j < it.ntiles && ok; ++j) {
+                    const int st = (gt + j) & 1, use = (gt + j) >> 1;
+                    const int krow = (a.cu_q ? it.k_off : 0) + (it.t_lo + j) * 128;
+                    if (use > 0) ok = mbar_wait(bar(C_KE0 + st), (use - 1) & 1, abort_flag, err, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(C_KF0 + st), L::kKV);
+#pragma unroll
+                    for (int s = 0; s < NSUB; ++s) tma_load_4d(sK + st * L::kKV + s * L::kSub, &a.tk, bar(C_KF0 + st), s * 64, it.hk, krow, qb);
+                    if (use > 0) ok = mbar_wait(bar(C_VE0 + st), (use - 1) & 1, abort_flag, err, 2);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(C_VF0 + st), L::kKV);
+#pragma unroll
+                    for (int s = 0; s < NSUB; ++s) tma_load_4d(sV + st * L::kKV + s * L::kSub, &a.tv, bar(C_VF0 + st), s * 64, it.hk, krow, qb);
+                }
+                gt += it.ntiles;
+                ++ni;
+            }
+        }
+    } else if (warp == 9) {
+        const uint64_t dQ0 = umma_desc(sQ, 16, 1024), dK0 = umma_desc(sK, 16, 1024), dV0 = umma_desc(sV, L::kSub, 1024);
+        auto issue_qk = [&](int x, int st) {
+            const uint32_t d_s = tmem + x * 128;
+            const uint64_t aq = umma_desc_at(dQ0, x * L::kQ), bk = umma_desc_at(dK0, st * L::kKV);
+            umma_ss_wo<0, 0, 0>(d_s, aq, bk, IDESC_QK);
+            static_for<1, KSTEPS>([&](auto kk) {
+                constexpr uint32_t off = (kk.value >> 2) * L::kSub + (kk.value & 3) * 32;
+                umma_ss_wo<1, off, off>(d_s, aq, bk, IDESC_QK);
+            });
+            umma_commit_w(bar(C_SA + x));
+        };
+        // P V of tile x in two halves of 64 keys; `pp` = parity of the tile's P barriers
+        auto issue_pv = [&](int x, int st, bool first, int pp) -> bool {
+            const uint64_t bv = umma_desc_at(dV0, st * L::kKV);
+            const uint32_t d_o = tmem + 256 + x * 128, a_p = tmem + x * 128;
+            if (!first) umma_ts_wo<1, 0, 0>(d_o, a_p, bv, IDESC_PV); else umma_ts_wo<0, 0, 0>(d_o, a_p, bv, IDESC_PV);
+            static_for<1, 4>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
+            if (!mbar_wait(bar(C_PA2 + x), pp, abort_flag, err, 11)) return false;
+            tc_fence_after();
+            static_for<4, 8>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
+            return true;
+        };
+        int gt = 0, gtb = 0, ni = 0, nib = 0;         // tiles / items so far, all and those with a second query tile
+        bool ok = true;
+        for (int rnd = 0; rnd * (int)gridDim.x < items && ok; ++rnd) {
+            const int t = item_of(rnd);
+            if (t >= items) continue;
+            const Item it = decode(t);
+            if (!it.live || it.ntiles == 0) continue;
+            const int ntiles = it.ntiles;
+            const bool has_b = it.has_b;
+            ok = mbar_wait(bar(C_Q), ni & 1, abort_flag, err, 3);
+            if (ok) ok = mbar_wait(bar(C_KF0 + (gt & 1)), (gt >> 1) & 1, abort_flag, err, 4);
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(0, gt & 1);
+            if (has_b) issue_qk(1, gt & 1);
+            umma_commit_w(bar(C_KE0 + (gt & 1)));
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int st = (gt + j) & 1, use = (gt + j) >> 1;
+                const bool more = j + 1 < ntiles;
+                const int st1 = (gt + j + 1) & 1, use1 = (gt + j + 1) >> 1;
+                if (!more) umma_commit_w(bar(C3_QE));                 // every Q K^T of this item has been issued
+                ok = mbar_wait(bar(C_PA), (gt + j) & 1, abort_flag, err, 5);
+                if (ok) ok = mbar_wait(bar(C_VF0 + st), use & 1, abort_flag, err, 6);
+                if (ok && j == 0 && ni > 0) ok = mbar_wait(bar(C3_OFA), (ni - 1) & 1, abort_flag, err, 13);
+                if (!ok) break;
+                tc_fence_after();
+                ok = issue_pv(0, st, j == 0, (gt + j) & 1);
+                if (!ok) break;
+                if (more) {
+                    ok = mbar_wait(bar(C_KF0 + st1), use1 & 1, abort_flag, err, 7);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(0, st1);
+                } else {
+                    umma_commit_w(bar(C_OA));
+                }
+                if (has_b) {
+                    ok = mbar_wait(bar(C_PB), (gtb + j) & 1, abort_flag, err, 8);
+                    if (ok && j == 0 && nib > 0) ok = mbar_wait(bar(C3_OFB), (nib - 1) & 1, abort_flag, err, 14);
+                    if (!ok) break;
+                    tc_fence_after();
+                    ok = issue_pv(1, st, j == 0, (gtb + j) & 1);
+                    if (!ok) break;
+                }
+                umma_commit_w(bar(C_VE0 + st));
+                if (more) {
+                    if (has_b) issue_qk(1, st1);
+                    umma_commit_w(bar(C_KE0 + st1));
+                } else if (has_b) {
+                    umma_commit_w(bar(C_OB));
+                }
+            }
+            gt += ntiles;
+            ++ni;
+            if (has_b) { gtb += ntiles; ++nib; }
+        }
+    }
+    } else {
+    reg_alloc<224>();
+    {
+        int gt = 0, ni = 0;                           // tiles / items this softmax group has handled
+        for (int rnd = 0; rnd * (int)gridDim.x < items; ++rnd) {
+            const int t = item_of(rnd);
+            if (t >= items) continue;
+            const Item it = decode(t);
+            if (!it.live) continue;
+            const int b = it.b, h = it.h, m0 = it.m0, sq = it.sq, sk = it.sk, q_off = it.q_off;
+            const int rows_cta = it.rows_cta, t_lo = it.t_lo, ntiles = it.ntiles;
+            T* obase = reinterpret_cast<T*>(a.o) + (a.cu_q ? 0 : (int64_t)b * a.o_sb) + (int64_t)(q_off + m0) * a.o_ss + (int64_t)h * a.o_sh;
+            float* lbase = a.lse ? a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + (int64_t)(q_off + m0) * a.lse_ss : nullptr;
+            if (ntiles == 0) {                        // no visible key for any row of the item
+                if (tid < rows_cta) {
+                    uint4 z = make_uint4(0, 0, 0, 0);
+                    T* orow = obase + (int64_t)tid * a.o_ss;
+#pragma unroll
+                    for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
+                    if (lbase) lbase[(int64_t)tid * a.lse_ss] = INFINITY;
+                }
+                continue;
+            }
+            if (warp >= 4 && !it.has_b) continue;     // the second query tile does not exist
+            {
+            const int x = warp >> 2;
+            const int r = tid & 127;
+            const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+            const uint32_t t_s = tmem + lane_base + x * 128;
+            const uint32_t t_o = tmem + lane_base + 256 + x * 128;
+            const int rows = min(128, rows_cta - x * 128);
+            const int qi = m0 + x * 128 + r;
+            int klo = 1, khi = 0;
+            if (r < rows) window_bounds(qi, sq, sk, wl, wr, klo, khi);
+            int lo_l, hi_f, tmp;
+            window_bounds(m0 + x * 128, sq, sk, wl, wr, tmp, hi_f);
+            window_bounds(m0 + x * 128 + rows - 1, sq, sk, wl, wr, lo_l, tmp);
+            float m_used = -INFINITY, l_run = 0.f;
+            const float sc = a.scale_log2;
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int n0 = (t_lo + j) * 128;
+                ok = mbar_wait(bar(C_SA + x), (gt + j) & 1, abort_flag, err, 9);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t sreg[4][32];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
+                tmem_wait_ld();
+                // the second half of the row is in flight while the first half is reduced
+#pragma unroll
+                for (int c = 2; c < 4; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
+                const bool full = n0 >= lo_l && n0 + 127 <= hi_f;
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    if (hh == 1) tmem_wait_ld();
+                    if (!full) {
+#pragma unroll
+                        for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const int col = n0 + c * 32 + i;
+                                if (col < klo || col > khi) sreg[c][i] = 0xff800000u;     // -inf
+                            }
+                        }
+                    }
+                    // four independent chains of three-input maxima
+#pragma unroll
+                    for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            mx0 = fmaxf(fmaxf(mx0, __uint_as_float(sreg[c][i])), __uint_as_float(sreg[c][i + 1]));
+                            mx1 = fmaxf(fmaxf(mx1, __uint_as_float(sreg[c][i + 2])), __uint_as_float(sreg[c][i + 3]));
+                            mx2 = fmaxf(fmaxf(mx2, __uint_as_float(sreg[c][i + 4])), __uint_as_float(sreg[c][i + 5]));
+                            mx3 = fmaxf(fmaxf(mx3, __uint_as_float(sreg[c][i + 6])), __uint_as_float(sreg[c][i + 7]));
+                        }
+                    }
+                }
+                const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;       // log2 domain
+                if (m_used == -INFINITY) m_used = m_new;
+                if (j > 0 && __any_sync(0xffffffffu, m_new > m_used + kRescaleThreshold)) {
+                    const float m_next = fmaxf(m_used, m_new);
+                    const float alpha = m_used == -INFINITY ? 1.f : ex2_approx(m_used - m_next);
+                    m_used = m_next;
+                    l_run *= alpha;
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t oreg[32];
+                        tmem_ld32(t_o + c * 32, oreg);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                        tmem_st32(t_o + c * 32, oreg);
+                    }
+                }
+                const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+                const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(neg_m, neg_m);
+                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+                // NPOLY of every 8 pairs take the polynomial 2^x, spread evenly between the special-function ones
+                auto exp_phase = [&](auto npoly_c) {
+                    constexpr int NPOLY = decltype(npoly_c)::value;
+#pragma unroll
+                    for (int hlf = 0; hlf < 2; ++hlf) {
+                        uint32_t preg[32];
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const uint32_t* src = &sreg[2 * hlf + (g >> 1)][(g & 1) * 16];
+                            static_for<0, 8>([&](auto pi) {
+                                constexpr bool poly = (pi.value * NPOLY) % 8 < NPOLY;
+                                const float2 xv = fma2(make_float2(__uint_as_float(src[2 * pi.value]), __uint_as_float(src[2 * pi.value + 1])), sc2, nm2);
+                                float2 pv;
+                                if constexpr (poly) pv = ex2_poly2(xv);
+                                else pv = make_float2(ex2_approx(xv.x), ex2_approx(xv.y));
+                                if constexpr (pi.value & 1) sum_b = add2(sum_b, pv); else sum_a = add2(sum_a, pv);
+                                preg[g * 8 + pi.value] = Elem<T>::pack(pv.x, pv.y);
+                            });
+                        }
+                        tmem_st32(t_s + hlf * 32, preg);
+                        tmem_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(bar((hlf ? C_PA2 : C_PA) + x));
+                    }
+                };
+                // masked tiles keep the special-function path: it maps -inf to an exact zero
+                if (full) exp_phase(std::integral_constant<int, FA_FWD_POLY>{});
+                else exp_phase(std::integral_constant<int, 0>{});
+                const float s0 = sum_a.x + sum_b.x, s1 = sum_a.y + sum_b.y;
+                l_run += s0 + s1;
+            }
+            if (ok) ok = mbar_wait(bar(C_OA + x), ni & 1, abort_flag, err, 10);
+            if (ok) {
+                tc_fence_after();
+                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+                T* orow = obase + (int64_t)(x * 128 + r) * a.o_ss;
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t oreg[32];
+                    tmem_ld32(t_o + c * 32, oreg);
+                    tmem_wait_ld();
+                    if (r < rows) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 pk;
+                            pk.x = Elem<T>::pack(__uint_as_float(oreg[8 * v + 0]) * inv, __uint_as_float(oreg[8 * v + 1]) * inv);
+                            pk.y = Elem<T>::pack(__uint_as_float(oreg[8 * v + 2]) * inv, __uint_as_float(oreg[8 * v + 3]) * inv);
+                            pk.z = Elem<T>::pack(__uint_as_float(oreg[8 * v + 4]) * inv, __uint_as_float(oreg[8 * v + 5]) * inv);
+                            pk.w = Elem<T>::pack(__uint_as_float(oreg[8 * v + 6]) * inv, __uint_as_float(oreg[8 * v + 7]) * inv);
+                            reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
+                        }
+                    }
+                }
+                if (r < rows && lbase) lbase[(int64_t)(x * 128 + r) * a.lse_ss] = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : INFINITY;
+
+                    // the accumulator has been read: the next item's first P V may overwrite it
+                    tc_fence_before();
+                    mbar_arrive(bar(C3_OFA + x));
+                }
+                if (!ok) break;
+            }
+            gt += ntiles;
+            ++ni;
+        }
+    }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -687,7 +1070,7 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
 }
 
 // 0: one query tile per CTA, P through shared memory; 1: same with P in tensor memory;
-// 2: two query tiles per CTA, P in tensor memory (default)
+// 2: two query tiles per CTA, P in tensor memory; 3: the same as persistent CTAs over a static item list
 static int g_variant = 2;
 void fwd_sm100_set_p_in_tmem(int v) { g_variant = v; }
 
@@ -709,7 +1092,16 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
 template <typename T, int D>
 static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
-    if (g_variant == 2) {
+    if (g_variant == 3) {
+        auto kern = fwd_sm100_kernel3<T, D>;
+        const int smem = FwdSm100Smem2<D>::kBytes + 1024;
+        if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+        const int mblocks = (p.sq + 255) / 256;
+        const long long items = (long long)mblocks * p.hq * p.b;
+        if (items > 0x7fffffffLL) return fail(FA_ERR_BAD_SHAPE, "too many work items");
+        const int ctas = (int)(items < sm_count() ? items : sm_count());
+        kern<<<ctas, 384, smem, st>>>(a, mblocks, (int)items);
+    } else if (g_variant == 2) {
         auto kern = fwd_sm100_kernel2<T, D>;
         const int smem = FwdSm100Smem2<D>::kBytes + 1024;
         if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
@@ -744,7 +1136,7 @@ int launch_fwd_sm100(const fa_fwd_params& p) {
     a.scale_log2 = p.scale * kLog2e;
     a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
     a.p_in_tmem = g_variant == 1;
-    note_kernel(g_variant == 2 ? "sm100_tcgen05_2q" : g_variant == 1 ? "sm100_tcgen05_ts" : "sm100_tcgen05");
+    note_kernel(g_variant == 3 ? "sm100_tcgen05_2q_persistent" : g_variant == 2 ? "sm100_tcgen05_2q" : g_variant == 1 ? "sm100_tcgen05_ts" : "sm100_tcgen05");
     if (p.dtype == FA_F16) return p.d == 64 ? launch_sm100_t<__half, 64>(p, a) : launch_sm100_t<__half, 128>(p, a);
     return p.d == 64 ? launch_sm100_t<__nv_bfloat16, 64>(p, a) : launch_sm100_t<__nv_bfloat16, 128>(p, a);
 }

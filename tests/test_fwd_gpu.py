@@ -187,3 +187,44 @@ def test_errors_mirror_the_reference():
         m.flash_attn_func(big, big, big)
     with pytest.raises(RuntimeError, match="softcap"):
         m.flash_attn_func(q, q, q, softcap=-1.0)
+
+
+@pytest.mark.parametrize("variant,name", [(0, "sm100_tcgen05"), (1, "sm100_tcgen05_ts"), (2, "sm100_tcgen05_2q"),
+                                          (3, "sm100_tcgen05_2q_persistent")])
+def test_tcgen05_forward_variants(variant, name):
+    """Every tcgen05 forward variant (one or two query tiles per CTA, P through shared or tensor memory, persistent
+    CTAs) against the oracle, on a dense GQA case with a ragged last tile and on a packed batch with empty and
+    one-row sequences; the persistent variant has more work items than the GPU has SMs."""
+    import fa_b200_capi as capi
+    capi.lib.fa_debug_set(1, variant)
+    try:
+        dt, b, h, hkv, sq, sk, d = torch.bfloat16, 3, 64, 8, 300, 777, 128
+        q = (torch.rand(b, sq, h, d) * 10 - 5).to(dt)
+        k = (torch.rand(b, sk, hkv, d) * 10 - 5).to(dt)
+        v = (torch.rand(b, sk, hkv, d) * 10 - 5).to(dt)
+        scale = d ** -0.5
+        for causal, window in ((True, (-1, -1)), (False, (100, 50))):
+            (lp_o, lp_l), (f_o, f_l) = fwd_refs(q, k, v, scale, causal, window, 0.0)
+            out, lse = run_dense(2, q, k, v, scale, causal, window, 0.0)
+            assert capi.last_kernel() == name
+            assert_within("out", out, lp_o, f_o)
+            assert_lse(lse, f_l)
+        lq, lk, hh, hk2, d2 = [300, 1, 0, 700, 64], [300, 555, 40, 700, 64], 8, 2, 64
+        q = (torch.rand(sum(lq), hh, d2) * 10 - 5).to(torch.float16)
+        k = (torch.rand(sum(lk), hk2, d2) * 10 - 5).to(torch.float16)
+        v = (torch.rand(sum(lk), hk2, d2) * 10 - 5).to(torch.float16)
+        cu_q = torch.tensor([0] + list(torch.tensor(lq).cumsum(0)), dtype=torch.int32)
+        cu_k = torch.tensor([0] + list(torch.tensor(lk).cumsum(0)), dtype=torch.int32)
+        lp_o, lp_l = orc.attention_varlen_fwd(q, k, v, cu_q, cu_k, d2 ** -0.5, True, (-1, -1), 0.0)
+        f_o, f_l = orc.attention_varlen_fwd(q.float(), k.float(), v.float(), cu_q, cu_k, d2 ** -0.5, True, (-1, -1), 0.0,
+                                            data_type=torch.float32)
+        m = _api(2)
+        out, lse, _ = m.flash_attn_varlen_func(q.cuda(), k.cuda(), v.cuda(), cu_q.cuda(), cu_k.cuda(), max(lq), max(lk),
+                                               softmax_scale=d2 ** -0.5, causal=True, return_attn_probs=True)
+        torch.cuda.synchronize()
+        assert capi.last_kernel() == name
+        assert capi.lib.fa_debug_get(2) == 0
+        assert_within("out", out.cpu(), lp_o, f_o)
+        assert_lse(lse.cpu(), f_l)
+    finally:
+        capi.lib.fa_debug_set(1, 2)
