@@ -329,7 +329,7 @@ struct FwdSm100Smem2 {
     static constexpr int oK = oQ + 2 * kQ;                  // 2 stages
     static constexpr int oV = oK + 2 * kKV;                 // 2 stages
     static constexpr int oBar = oV + 2 * kKV;
-    static constexpr int kBytes = oBar + 256;
+    static constexpr int kBytes = oBar + 320;        // barriers, flags and the persistent kernel's four 16-byte slots
 };
 
 #ifndef FA_FWD_POLY
@@ -653,16 +653,19 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Persistent variant of the kernel above: one CTA per SM walks a static list of (query block pair, head, batch)
-// items, heaviest query blocks first.  All barriers keep running across items (their parities come from running
-// counts of tiles and items), so the copy warp already loads Q, K and V of the next item and the MMA warp already
-// multiplies its first Q K^T while the softmax warps still write the previous item's output; only the first P V of
-// an item waits until the accumulator has been read out (C_OFA / C_OFB), and the Q buffer is reloaded once the
-// last Q K^T of the previous item has completed (C_QE).
-enum { C3_QE = C_COUNT, C3_OFA, C3_OFB, C3_COUNT };
+// Persistent variant of the kernel above.  It is launched with the same grid, but a CTA that has issued the loads
+// of its item asks the hardware for the next CTA of the grid that has not started yet and runs that CTA's item
+// itself (the hardware keeps the launch order, so the query blocks of a head still run together and share K/V in
+// L2).  All barriers keep running across items (their parities come from running counts of tiles and items), so the
+// copy warp already loads Q, K and V of the next item and the MMA warp already multiplies its first Q K^T while the
+// softmax warps still write the previous item's output; only the first P V of an item waits until the accumulator
+// has been read out (C3_OFA / C3_OFB), and the Q buffer is reloaded once the last Q K^T of the previous item has
+// completed (C3_QE).  The answers of the hardware arrive in a ring of four 16-byte slots, each with its barrier
+// (C3_IT0..3): the copy warp is never more than two items ahead of the slowest warp, so four slots suffice.
+enum { C3_QE = C_COUNT, C3_OFA, C3_OFB, C3_IT0, C3_IT1, C3_IT2, C3_IT3, C3_COUNT };
 
 template <typename T, int D>
-__global__ void __launch_bounds__(384, 1) fwd_sm100_kernel3(const __grid_constant__ Sm100FwdArgs a, const int mblocks, const int items) {
+__global__ void __launch_bounds__(384, 1) fwd_sm100_kernel3(const __grid_constant__ Sm100FwdArgs a) {
     using L = FwdSm100Smem2<D>;
     constexpr int NSUB = D / 64;
     constexpr int KSTEPS = D / 16;
@@ -671,7 +674,7 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel3(const __grid_constan
     constexpr uint32_t IDESC_QK = umma_idesc(FMT, 128, 128, 0, 0);
     constexpr uint32_t IDESC_PV = umma_idesc(FMT, 128, D, 0, 1);
     constexpr float kRescaleThreshold = 8.f;
-    static_assert(8 * C3_COUNT + 16 <= 256, "barrier area");
+    static_assert(8 * C3_COUNT + 16 + 64 <= L::kBytes - L::oBar && (8 * C3_COUNT + 16) % 16 == 0, "barrier area");
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
@@ -680,28 +683,29 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel3(const __grid_constan
     const uint32_t bars = sbase + L::oBar;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * C3_COUNT);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * C3_COUNT + 8);
+    const uint32_t slots = bars + 8u * C3_COUNT + 16u;                   // four 16-byte answers of the work-stealing requests
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (g_fwd_sm100_error) return;
     const int wl = a.wl, wr = a.causal ? 0 : a.wr;
-    const int heads_batch = a.hq * a.b;
 
     struct Item {
         int b, h, hk, m0, sq, sk, q_off, k_off, rows_cta, t_lo, ntiles;
         bool has_b, live;
     };
-    // items are sorted heaviest first; successive rounds hand them to the CTAs in alternating direction, which
-    // keeps the per-CTA totals within about 1 % of each other for causal masks
-    auto item_of = [&](int rnd) {
-        const int c = (rnd & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
-        return rnd * (int)gridDim.x + c;
+    // k-th item of this CTA: its own block index first, then whatever the hardware handed over; false = no work left
+    auto item_at = [&](int k, int& bx, int& by, int& bz) -> bool {
+        if (k == 0) { bx = blockIdx.x; by = blockIdx.y; bz = blockIdx.z; return true; }
+        const int idx = (k - 1) & 3;
+        if (!mbar_wait(bar(C3_IT0 + idx), ((k - 1) >> 2) & 1, abort_flag, &g_fwd_sm100_error, 15)) return false;
+        return next_cta_decode(slots + idx * 16, bx, by, bz);
     };
-    auto decode = [&](int t) {
+    auto decode = [&](int bx, int by, int bz) {
         Item it;
-        const int mblk = mblocks - 1 - t / heads_batch, rem = t % heads_batch;
-        it.h = rem % a.hq;
-        it.b = rem / a.hq;
+        const int mblk = (int)gridDim.x - 1 - bx;
+        it.h = by;
+        it.b = bz;
         it.hk = it.h / (a.hq / a.hkv);
         it.q_off = 0; it.k_off = 0; it.sq = a.sq; it.sk = a.sk;
         if (a.cu_q) {
@@ -749,10 +753,13 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel3(const __grid_constan
             tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
             int gt = 0, ni = 0;                       // tiles and items (with keys) so far
             bool ok = true;
-            for (int rnd = 0; rnd * (int)gridDim.x < items && ok; ++rnd) {
-                const int t = item_of(rnd);
-                if (t >= items) continue;
-                const Item it = decode(t);
+            for (int k = 0; ok; ++k) {
+                int bx, by, bz;
+                if (!item_at(k, bx, by, bz)) break;
+                // ask for item k + 1 now: its answer is there long before anyone needs it
+                mbar_expect_tx(bar(C3_IT0 + (k & 3)), 16);
+                next_cta_request(slots + (k & 3) * 16, bar(C3_IT0 + (k & 3)));
+                const Item it = decode(bx, by, bz);
                 if (!it.live || it.ntiles == 0) continue;
                 const int qrow0 = (a.cu_q ? it.q_off : 0) + it.m0, qb = a.cu_q ? 0 : it.b;
                 if (ni > 0) ok = mbar_wait(bar(C3_QE), (ni - 1) & 1, abort_flag, err, 12);
@@ -807,10 +814,10 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel3(const __grid_constan
         };
         int gt = 0, gtb = 0, ni = 0, nib = 0;         // tiles / items so far, all and those with a second query tile
         bool ok = true;
-        for (int rnd = 0; rnd * (int)gridDim.x < items && ok; ++rnd) {
-            const int t = item_of(rnd);
-            if (t >= items) continue;
-            const Item it = decode(t);
+        for (int k = 0; ok; ++k) {
+            int bx, by, bz;
+            if (!item_at(k, bx, by, bz)) break;
+            const Item it = decode(bx, by, bz);
             if (!it.live || it.ntiles == 0) continue;
             const int ntiles = it.ntiles;
             const bool has_b = it.has_b;
@@ -866,10 +873,10 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel3(const __grid_constan
     reg_alloc<224>();
     {
         int gt = 0, ni = 0;                           // tiles / items this softmax group has handled
-        for (int rnd = 0; rnd * (int)gridDim.x < items; ++rnd) {
-            const int t = item_of(rnd);
-            if (t >= items) continue;
-            const Item it = decode(t);
+        for (int k = 0;; ++k) {
+            int bx, by, bz;
+            if (!item_at(k, bx, by, bz)) break;
+            const Item it = decode(bx, by, bz);
             if (!it.live) continue;
             const int b = it.b, h = it.h, m0 = it.m0, sq = it.sq, sk = it.sk, q_off = it.q_off;
             const int rows_cta = it.rows_cta, t_lo = it.t_lo, ntiles = it.ntiles;
@@ -1096,11 +1103,8 @@ static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
         auto kern = fwd_sm100_kernel3<T, D>;
         const int smem = FwdSm100Smem2<D>::kBytes + 1024;
         if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-        const int mblocks = (p.sq + 255) / 256;
-        const long long items = (long long)mblocks * p.hq * p.b;
-        if (items > 0x7fffffffLL) return fail(FA_ERR_BAD_SHAPE, "too many work items");
-        const int ctas = (int)(items < sm_count() ? items : sm_count());
-        kern<<<ctas, 384, smem, st>>>(a, mblocks, (int)items);
+        dim3 grid((p.sq + 255) / 256, p.hq, p.b);
+        kern<<<grid, 384, smem, st>>>(a);
     } else if (g_variant == 2) {
         auto kern = fwd_sm100_kernel2<T, D>;
         const int smem = FwdSm100Smem2<D>::kBytes + 1024;

@@ -132,6 +132,28 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// ---- work stealing for persistent CTAs: a running CTA asks the hardware for the next not yet started CTA of its
+// grid and runs that CTA's work itself (the asked-for CTA is then never launched) -----------------------------------
+// The 16-byte answer arrives in shared memory at `slot` and completes 16 bytes on `bar`.
+__device__ __forceinline__ void next_cta_request(uint32_t slot, uint32_t bar) {
+    asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+                 ::"r"(slot), "r"(bar) : "memory");
+}
+// Decode an answer read back from `slot`: returns false when no CTA was left to take over.
+__device__ __forceinline__ bool next_cta_decode(uint32_t slot, int& x, int& y, int& z) {
+    uint32_t ok, cx, cy, cz;
+    asm volatile(
+        "{\n\t.reg .b128 resp;\n\t.reg .pred p;\n\t.reg .b32 dummy;\n\t"
+        "ld.shared.b128 resp, [%4];\n\t"
+        "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, resp;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "mov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
+        "@p clusterlaunchcontrol.query_cancel.get_first_ctaid.v4.b32.b128 {%1, %2, %3, dummy}, resp;\n\t}"
+        : "=r"(ok), "=r"(cx), "=r"(cy), "=r"(cz) : "r"(slot) : "memory");
+    x = (int)cx; y = (int)cy; z = (int)cz;
+    return ok != 0;
+}
+
 // ---- fences -----------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
