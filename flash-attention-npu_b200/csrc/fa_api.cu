@@ -15,6 +15,7 @@ static int g_mla_variant = 0;     // 0: CTA-pair latent decode, 1: single-CTA ke
 static thread_local cudaEvent_t* g_events = nullptr;
 static thread_local int g_nevents = 0, g_event_idx = 0;
 
+bool kernel_events_active() { return g_events != nullptr; }
 void mark_kernel(cudaStream_t st) {
     if (g_events && g_event_idx < g_nevents) cudaEventRecord(g_events[g_event_idx++], st);
 }
@@ -278,6 +279,7 @@ void fa_debug_set(int key, int value) {
     if (key == 3) { fa::sm100_error_flag(true); fa::decode_error_flag(true); }
     if (key == 4) fa::decode_set_use_tma(value);
     if (key == 5) g_mla_variant = value;
+    if (key == 6) fa::bwd_sm100_set_overlap(value);
 }
 int fa_debug_get(int key) {
     if (key != 2) return 0;

@@ -63,6 +63,10 @@ int launch_mla_pair(const fa_mla_params& p, int nsplit, int tokens_per_split, fl
                     int final_direct, cudaStream_t st);
 int mla_pair_error_flag(bool clear);
 int launch_bwd_sm100(const fa_bwd_params& p);
+// 1 (default): the dQ kernel runs on an internal stream beside the dK/dV kernel (fa_debug_set key 6)
+void bwd_sm100_set_overlap(int v);
+// true while the caller has lent per-kernel timing events to this thread
+bool kernel_events_active();
 bool bwd_sm100_supported(const fa_bwd_params& p);
 size_t bwd_generic_workspace(const fa_bwd_params& p);
 size_t bwd_sm100_workspace(const fa_bwd_params& p);
