@@ -68,6 +68,8 @@ struct BwdSm100Smem {
 };
 
 enum { E_FIX = 0, E_RF0, E_RF1, E_RE0, E_RE1, E_S0, E_S1, E_P0, E_P1, E_F0, E_F1, E_ACC, E_COUNT };
+// barriers of the dQ kernel: three score buffers
+enum { G_FIX = 0, G_RF0, G_RF1, G_RE0, G_RE1, G_S0, G_S1, G_S2, G_P0, G_P1, G_P2, G_F0, G_F1, G_F2, G_ACC, G_COUNT };
 
 template <typename T>
 __device__ __forceinline__ void store_row_scaled(T* dst, const uint32_t (&r)[32], float s) {
@@ -334,7 +336,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
     using L = BwdSm100Smem<D>;
     constexpr int NSUB = D / 64, KSTEPS = D / 16;
-    constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 128, COL_DQ = 256;     // S / dP: 2 x 64 columns
+    constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 192, COL_DQ = 384;     // S / dP: 3 x 64 columns each
     constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
     constexpr uint32_t IDESC_S = umma_idesc(FMT, 128, 64, 0, 0);
     constexpr uint32_t IDESC_ACC = umma_idesc(FMT, 128, D, 0, 1);
@@ -344,8 +346,8 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
     unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
     const uint32_t sQ = sbase + L::oFix0, sdO = sbase + L::oFix1, sK = sbase + L::oRing0, sV = sbase + L::oRing1;
     const uint32_t bars = sbase + L::oBar;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * E_COUNT);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * E_COUNT + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * G_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * G_COUNT + 8);
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -378,7 +380,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
         return;
     }
     if (tid == 0) {
-        for (int i = 0; i < E_COUNT; ++i) mbar_init(bar(i), (i == E_P0 || i == E_P1) ? 512u : 1u);
+        for (int i = 0; i < G_COUNT; ++i) mbar_init(bar(i), (i >= G_P0 && i <= G_P2) ? 512u : 1u);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -393,24 +395,24 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
     if (warp == 16) {
         if (lane == 0) {
             tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tdo); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
-            mbar_expect_tx(bar(E_FIX), 2 * L::kTileB);
+            mbar_expect_tx(bar(G_FIX), 2 * L::kTileB);
             const int qrow = (a.cu_q ? q_off : 0) + m0;
 #pragma unroll
             for (int s = 0; s < NSUB; ++s) {
-                tma_load_4d(sQ + s * L::kSub, &a.tq, bar(E_FIX), s * 64, h, qrow, bb);
-                tma_load_4d(sdO + s * L::kSub, &a.tdo, bar(E_FIX), s * 64, h, qrow, bb);
+                tma_load_4d(sQ + s * L::kSub, &a.tq, bar(G_FIX), s * 64, h, qrow, bb);
+                tma_load_4d(sdO + s * L::kSub, &a.tdo, bar(G_FIX), s * 64, h, qrow, bb);
             }
             bool ok = true;
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int st = j & 1, use = j >> 1;
                 const int krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128;
-                if (use > 0) ok = mbar_wait(bar(E_RE0 + st), (use - 1) & 1, abort_flag, err, 31);
+                if (use > 0) ok = mbar_wait(bar(G_RE0 + st), (use - 1) & 1, abort_flag, err, 31);
                 if (!ok) break;
-                mbar_expect_tx(bar(E_RF0 + st), 2 * L::kTileB);
+                mbar_expect_tx(bar(G_RF0 + st), 2 * L::kTileB);
 #pragma unroll
                 for (int c = 0; c < NSUB; ++c) {
-                    tma_load_4d(sK + st * L::kTileB + c * L::kSub, &a.tk, bar(E_RF0 + st), c * 64, hk, krow, bb);
-                    tma_load_4d(sV + st * L::kTileB + c * L::kSub, &a.tv, bar(E_RF0 + st), c * 64, hk, krow, bb);
+                    tma_load_4d(sK + st * L::kTileB + c * L::kSub, &a.tk, bar(G_RF0 + st), c * 64, hk, krow, bb);
+                    tma_load_4d(sV + st * L::kTileB + c * L::kSub, &a.tv, bar(G_RF0 + st), c * 64, hk, krow, bb);
                 }
             }
         }
@@ -419,11 +421,11 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
             const int units = ntiles * 2;
             const uint64_t dQ0 = umma_desc(sQ, 16, 1024), dO0 = umma_desc(sdO, 16, 1024);
             const uint64_t dKk = umma_desc(sK, 16, 1024), dVk = umma_desc(sV, 16, 1024);
-            auto issue_sd = [&](int u) {                    // S and dP against the 64 keys of half u
+            auto issue_sd = [&](int u, int bi) {            // S and dP against the 64 keys of half u, into buffer bi
                 const int st = (u >> 1) & 1, hf = u & 1;
                 const uint32_t boff = st * L::kTileB + hf * 8192;
                 const uint64_t bk = umma_desc_at(dKk, boff), bv = umma_desc_at(dVk, boff);
-                const uint32_t d_s = tmem + COL_S + hf * 64, d_p = tmem + COL_DP + hf * 64;
+                const uint32_t d_s = tmem + COL_S + bi * 64, d_p = tmem + COL_DP + bi * 64;
                 umma_ss_w<0>(d_s, dQ0, bk, IDESC_S);
 #pragma unroll
                 for (int kk = 1; kk < KSTEPS; ++kk) {
@@ -436,16 +438,19 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
                     const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
                     umma_ss_w<1>(d_p, umma_desc_at(dO0, off), umma_desc_at(bv, off), IDESC_S);
                 }
-                umma_commit_w(bar(E_S0 + hf));
+                umma_commit_w(bar(G_S0 + bi));
             };
-            bool ok = mbar_wait(bar(E_FIX), 0, abort_flag, err, 32);
-            for (int u = 0; u < units && ok; ++u) {
+            bool ok = mbar_wait(bar(G_FIX), 0, abort_flag, err, 32);
+            // three score buffers rotate: the MMAs of unit u + 2 are issued while the element-wise warps work on unit
+            // u + 1 and the dQ MMA of unit u is still pending
+            for (int u = 0, bi = 0, rnd = 0; u < units && ok; ++u) {
                 const int j1 = u >> 1;
-                if (u >= 2) ok = mbar_wait(bar(E_F0 + (u & 1)), (j1 - 1) & 1, abort_flag, err, 37);
-                if (ok && (u & 1) == 0) ok = mbar_wait(bar(E_RF0 + (j1 & 1)), (j1 >> 1) & 1, abort_flag, err, 33);
+                if (u >= 3) ok = mbar_wait(bar(G_F0 + bi), (rnd - 1) & 1, abort_flag, err, 37);
+                if (ok && (u & 1) == 0) ok = mbar_wait(bar(G_RF0 + (j1 & 1)), (j1 >> 1) & 1, abort_flag, err, 33);
                 if (!ok) break;
                 tc_fence_after();
-                issue_sd(u);
+                issue_sd(u, bi);
+                if (++bi == 3) { bi = 0; ++rnd; }
             }
         }
     } else if (warp == 18) {
@@ -453,20 +458,21 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
             const int units = ntiles * 2;
             const uint64_t dKm = umma_desc(sK, L::kSub, 1024);
             bool ok = true;
-            for (int u = 0; u < units && ok; ++u) {
-                ok = mbar_wait(bar(E_P0 + (u & 1)), (u >> 1) & 1, abort_flag, err, 34);
+            for (int u = 0, bi = 0, rnd = 0; u < units && ok; ++u) {
+                ok = mbar_wait(bar(G_P0 + bi), rnd & 1, abort_flag, err, 34);
                 if (!ok) break;
                 tc_fence_after();
                 const int st = (u >> 1) & 1, hf = u & 1;
                 const uint64_t bk = umma_desc_at(dKm, st * L::kTileB + hf * 8192);
-                const uint32_t a_s = tmem + COL_DP + hf * 64;
+                const uint32_t a_s = tmem + COL_DP + bi * 64;
                 if (u > 0) umma_ts_w<1>(tmem + COL_DQ, a_s, bk, IDESC_ACC); else umma_ts_w<0>(tmem + COL_DQ, a_s, bk, IDESC_ACC);
 #pragma unroll
                 for (int kk = 1; kk < 4; ++kk) umma_ts_w<1>(tmem + COL_DQ, a_s + kk * 16, umma_desc_at(bk, kk * 2048), IDESC_ACC);
-                umma_commit_w(bar(E_F0 + hf));
-                if (u & 1) umma_commit_w(bar(E_RE0 + st));
+                umma_commit_w(bar(G_F0 + bi));
+                if (u & 1) umma_commit_w(bar(G_RE0 + st));
+                if (++bi == 3) { bi = 0; ++rnd; }
             }
-            if (ok) umma_commit_w(bar(E_ACC));
+            if (ok) umma_commit_w(bar(G_ACC));
         }
     } else {
         const int cg = warp >> 2;                            // which 16 key columns of a half
@@ -483,15 +489,15 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
         }
         bool ok = true;
         const int units = ntiles * 2;
-        for (int u = 0; u < units && ok; ++u) {
+        for (int u = 0, bi = 0, rnd = 0; u < units && ok; ++u) {
             const int hf = u & 1;
             const int c0 = (t_lo + (u >> 1)) * 128 + hf * 64 + cg * 16;     // first key of this thread's 16 columns
-            ok = mbar_wait(bar(E_S0 + hf), (u >> 1) & 1, abort_flag, err, 35);
+            ok = mbar_wait(bar(G_S0 + bi), rnd & 1, abort_flag, err, 35);
             if (!ok) break;
             tc_fence_after();
             uint32_t sr[16], dr[16], pS[8];
-            tmem_ld16(tmem + lane_base + COL_S + hf * 64 + cg * 16, sr);
-            tmem_ld16(tmem + lane_base + COL_DP + hf * 64 + cg * 16, dr);
+            tmem_ld16(tmem + lane_base + COL_S + bi * 64 + cg * 16, sr);
+            tmem_ld16(tmem + lane_base + COL_DP + bi * 64 + cg * 16, dr);
             tmem_wait_ld();
             const bool inside = __all_sync(0xffffffffu, c0 >= klo && c0 + 15 <= khi);
             const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dl, -dl);
@@ -507,12 +513,13 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
                 const float2 ds = mul2(p, add2(make_float2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])), nd2));
                 pS[i / 2] = Elem<T>::pack(ds.x, ds.y);
             }
-            tmem_st8(tmem + lane_base + COL_DP + hf * 64 + cg * 16, pS);
+            tmem_st8(tmem + lane_base + COL_DP + bi * 64 + cg * 16, pS);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(E_P0 + hf));
+            mbar_arrive(bar(G_P0 + bi));
+            if (++bi == 3) { bi = 0; ++rnd; }
         }
-        if (ok) ok = mbar_wait(bar(E_ACC), 0, abort_flag, err, 36);
+        if (ok) ok = mbar_wait(bar(G_ACC), 0, abort_flag, err, 36);
         if (ok) {
             tc_fence_after();
             // each group of four warps writes 32 columns of its row (groups beyond D / 32 have nothing to write)
