@@ -3,9 +3,9 @@
 //
 // The 576 score dimensions are split over the pair: CTA 0 holds latent dims [0,256) and the 64 rope dims, CTA 1
 // latent dims [256,512).  Each CTA stages only its part of Q (80 KB) and of every dequantised 64-token tile
-// (40 KB, two buffers), computes PARTIAL scores S_r = Q_r K_r^T in tensor memory, and the softmax threads exchange
-// the partials through distributed shared memory: each writes its 128 x 64 fp32 partial into the peer's receive
-// buffer, both add own + peer (the same fp32 sum in both CTAs) and run the same online softmax.  P V then uses the
+// (40 KB, two buffers), computes PARTIAL scores S_r = Q_r K_r^T in tensor memory, and the softmax warps exchange
+// the partials through distributed shared memory: each warp bulk-copies its 32 x 64 fp32 partial into the peer
+// warp's receive buffer, both add own + peer (the same fp32 sum in both CTAs) and run the same online softmax.  P V then uses the
 // CTA's own 256 latent columns as V, so each CTA owns one half of the output and nothing is computed twice.
 //
 //   warps 0-3   softmax + exchange: thread = head row; epilogue
@@ -38,14 +38,16 @@ constexpr int kQSub = 128 * 128;                // bytes of one [128 heads x 64 
 constexpr int kKSub = kTile * 128;              // bytes of one [64 tokens x 64 dims] K sub-tile
 constexpr int kSubs = 5;                        // 4 latent sub-tiles + rope (CTA 0 only)
 constexpr int kKBuf = kSubs * kKSub;            // one tile buffer
-constexpr int kRecvBuf = 128 * kTile * 4;       // one receive buffer of partial scores
-constexpr int kOffK = kSubs * kQSub, kOffRecv = kOffK + 2 * kKBuf, kOffBar = kOffRecv + 2 * kRecvBuf;
+constexpr int kXchg = 32 * kTile * 4;            // partial scores of one softmax warp (32 rows x 64 tokens, fp32)
+constexpr int kOffK = kSubs * kQSub, kOffRecv = kOffK + 2 * kKBuf, kOffBar = kOffRecv + 4 * 2 * kXchg;      // per softmax warp: a send buffer and a receive buffer
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
 constexpr int kThreads = 16 * 32;
 static_assert(kSmemBytes <= 232448, "shared memory budget");
-// KF/KE: tile buffer full / free; S: partial scores complete; P: probabilities written; RF: peer's partial has
-// arrived in my receive buffer; RC: the peer has consumed what I wrote into its receive buffer; O: all MMAs done
-enum { P_KF0 = 0, P_KF1, P_KE0, P_KE1, P_S0, P_S1, P_P0, P_P1, P_RF0, P_RF1, P_RC0, P_RC1, P_O, P_COUNT };
+// KF/KE: tile buffer full / free; S: partial scores complete; P: probabilities written; RF (one per softmax warp):
+// the peer warp's partial has landed in my receive buffer; RC: the peer warp has read what I copied into its receive
+// buffer; O: all MMAs done
+enum { P_KF0 = 0, P_KF1, P_KE0, P_KE1, P_S0, P_S1, P_P0, P_P1, P_RF0, P_RF1, P_RF2, P_RF3, P_RC0, P_RC1, P_RC2, P_RC3,
+       P_O, P_COUNT };
 
 struct MlaPairArgs {
     fa_mla_params p;
@@ -67,7 +69,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
     extern __shared__ unsigned char smem_raw[];
     const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
     unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
-    const uint32_t sQ = sbase, sK = sbase + kOffK, sRecv = sbase + kOffRecv, bars = sbase + kOffBar;
+    const uint32_t sQ = sbase, sK = sbase + kOffK, bars = sbase + kOffBar;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + kOffBar + 8 * P_COUNT);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + kOffBar + 8 * P_COUNT + 8);
     auto bar = [&](int i) { return bars + 8u * i; };
@@ -109,8 +111,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
         mbar_init(bar(P_KE0), 1); mbar_init(bar(P_KE1), 1);
         mbar_init(bar(P_S0), 1); mbar_init(bar(P_S1), 1);
         mbar_init(bar(P_P0), 128); mbar_init(bar(P_P1), 128);
-        mbar_init(bar(P_RF0), 128); mbar_init(bar(P_RF1), 128);
-        mbar_init(bar(P_RC0), 128); mbar_init(bar(P_RC1), 128);
+        for (int w = 0; w < 4; ++w) { mbar_init(bar(P_RF0 + w), 1); mbar_init(bar(P_RC0 + w), 1); }
         mbar_init(bar(P_O), 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -293,33 +294,45 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
             tmem_ld32(t_s, sreg[0]);
             tmem_ld32(t_s + 32, sreg[1]);
             tmem_wait_ld();
-            // my partial scores go into the peer's receive buffer s, once it has read what I put there two tiles ago;
-            // layout [16-byte chunk][row] so that a warp writes and reads 512 contiguous bytes
-            if (j >= 2) ok = mbar_wait_cluster(bar(P_RC0 + s), ((j >> 1) - 1) & 1, abort_flag, err, 35);
-            if (!ok) break;
-            const uint32_t peer_recv = map_to_cta(sRecv + s * kRecvBuf, peer);
-#pragma unroll
-            for (int c = 0; c < 16; ++c)
-                st_cluster_v4(peer_recv + (c * 128 + r) * 16,
-                              make_float4(__uint_as_float(sreg[c >> 3][(c & 7) * 4]), __uint_as_float(sreg[c >> 3][(c & 7) * 4 + 1]),
-                                          __uint_as_float(sreg[c >> 3][(c & 7) * 4 + 2]), __uint_as_float(sreg[c >> 3][(c & 7) * 4 + 3])));
-            mbar_arrive_remote(map_to_cta(bar(P_RF0 + s), peer));
-            ok = mbar_wait_cluster(bar(P_RF0 + s), (j >> 1) & 1, abort_flag, err, 36);
-            if (!ok) break;
+            // Exchange, warp by warp: my 32 x 64 partial goes to my send buffer ([16-byte chunk][lane], so that the
+            // warp writes 512 contiguous bytes), one bulk copy moves it into the peer warp's receive buffer and counts
+            // its bytes on the peer's barrier; the peer's partial arrives the same way and is added to mine.
             {
-                const float4* mine = reinterpret_cast<const float4*>(sgen + kOffRecv + s * kRecvBuf);
+                unsigned char* send = sgen + kOffRecv + warp * 2 * kXchg;
+                const unsigned char* recv = send + kXchg;
+                if (lane == 0) {
+                    mbar_expect_tx(bar(P_RF0 + warp), kXchg);            // the peer's copy of this tile
+                    bulk_copy_wait_read();                                 // my copy of the previous tile has left the send buffer
+                }
+                __syncwarp();
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    reinterpret_cast<uint4*>(send)[c * 32 + lane] =
+                        make_uint4(sreg[c >> 3][(c & 7) * 4], sreg[c >> 3][(c & 7) * 4 + 1], sreg[c >> 3][(c & 7) * 4 + 2], sreg[c >> 3][(c & 7) * 4 + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    // the peer warp has read what I sent for the previous tile
+                    if (j >= 1) ok = mbar_wait_cluster(bar(P_RC0 + warp), (j - 1) & 1, abort_flag, err, 35);
+                    if (ok) bulk_copy_to_peer(map_to_cta(smem_addr(recv), peer), smem_addr(send), kXchg, map_to_cta(bar(P_RF0 + warp), peer));
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                ok = mbar_wait_cluster(bar(P_RF0 + warp), j & 1, abort_flag, err, 36);
+                if (!ok) break;
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const float4 v = mine[c * 128 + r];
+                    const float4 v = reinterpret_cast<const float4*>(recv)[c * 32 + lane];
                     uint32_t* d = &sreg[c >> 3][(c & 7) * 4];
                     d[0] = __float_as_uint(__uint_as_float(d[0]) + v.x);
                     d[1] = __float_as_uint(__uint_as_float(d[1]) + v.y);
                     d[2] = __float_as_uint(__uint_as_float(d[2]) + v.z);
                     d[3] = __float_as_uint(__uint_as_float(d[3]) + v.w);
                 }
+                __syncwarp();
+                // the values read above have been used, so the peer may overwrite my receive buffer: no release needed
+                if (lane == 0) mbar_arrive_remote_relaxed(map_to_cta(bar(P_RC0 + warp), peer));
             }
-            // the values read above have been used, so the buffer may be overwritten: no release needed
-            mbar_arrive_remote_relaxed(map_to_cta(bar(P_RC0 + s), peer));
             const int valid = t_end - (t_begin + j * kTile);               // tokens of this tile that exist
             if (valid < kTile) {
 #pragma unroll
