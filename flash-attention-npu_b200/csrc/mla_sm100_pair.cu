@@ -2,8 +2,9 @@
 // (KV split, sequence, tile of 128 heads).  No counterpart in the reference.
 //
 // The 576 score dimensions are split over the pair: CTA 0 holds latent dims [0,256) and the 64 rope dims, CTA 1
-// latent dims [256,512).  Each CTA stages only its part of Q (80 KB) and of every dequantised 64-token tile
-// (40 KB, two buffers), computes PARTIAL scores S_r = Q_r K_r^T in tensor memory, and the softmax warps exchange
+// latent dims [256,512).  Each CTA keeps its latent part of Q in tensor memory (128 columns: the A operand of the
+// score MMAs, so that only K is read from shared memory), stages its part of every dequantised 64-token tile (40 KB,
+// three buffers), computes PARTIAL scores S_r = Q_r K_r^T in tensor memory, and the softmax warps exchange
 // the partials through distributed shared memory: each warp bulk-copies its 32 x 64 fp32 partial into the peer
 // warp's receive buffer, both add own + peer (the same fp32 sum in both CTAs) and run the same online softmax.  P V then uses the
 // CTA's own 256 latent columns as V, so each CTA owns one half of the output and nothing is computed twice.
@@ -11,7 +12,7 @@
 //   warps 0-3   softmax + exchange: thread = head row; epilogue
 //   warps 4-11  producers: int8 rows -> registers -> * scale -> bf16 -> swizzled shared memory (UMMA layout)
 //   warp 12     issues the MMAs, owns the tensor memory (warps 13-15 only complete the last warp group)
-// Tensor memory: O half (256 columns) + two 64-column score buffers.
+// Tensor memory: O half (256 columns) + two 64-column score buffers + Q (128 columns).
 #include "fa_utils.cuh"
 #include "fa_internal.h"
 #include "sm100_ptx.cuh"
@@ -39,14 +40,15 @@ constexpr int kKSub = kTile * 128;              // bytes of one [64 tokens x 64 
 constexpr int kSubs = 5;                        // 4 latent sub-tiles + rope (CTA 0 only)
 constexpr int kKBuf = kSubs * kKSub;            // one tile buffer
 constexpr int kXchg = 32 * kTile * 4;            // partial scores of one softmax warp (32 rows x 64 tokens, fp32)
-constexpr int kOffK = kSubs * kQSub, kOffRecv = kOffK + 2 * kKBuf, kOffBar = kOffRecv + 4 * 2 * kXchg;      // per softmax warp: a send buffer and a receive buffer
+constexpr int kKBufs = 3;                        // tile buffers in flight
+constexpr int kOffK = kQSub, kOffRecv = kOffK + kKBufs * kKBuf, kOffBar = kOffRecv + 4 * 2 * kXchg;      // per softmax warp: a send buffer and a receive buffer
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
 constexpr int kThreads = 16 * 32;
 static_assert(kSmemBytes <= 232448, "shared memory budget");
-// KF/KE: tile buffer full / free; S: partial scores complete; P: probabilities written; RF (one per softmax warp):
+// KF/KE: tile buffer full / free; QT: the latent part of Q is in tensor memory; S: partial scores complete; P: probabilities written; RF (one per softmax warp):
 // the peer warp's partial has landed in my receive buffer; RC: the peer warp has read what I copied into its receive
 // buffer; O: all MMAs done
-enum { P_KF0 = 0, P_KF1, P_KE0, P_KE1, P_S0, P_S1, P_P0, P_P1, P_RF0, P_RF1, P_RF2, P_RF3, P_RC0, P_RC1, P_RC2, P_RC3,
+enum { P_KF0 = 0, P_KF1, P_KF2, P_KE0, P_KE1, P_KE2, P_QT, P_S0, P_S1, P_P0, P_P1, P_RF0, P_RF1, P_RF2, P_RF3, P_RC0, P_RC1, P_RC2, P_RC3,
        P_O, P_COUNT };
 
 struct MlaPairArgs {
@@ -69,7 +71,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
     extern __shared__ unsigned char smem_raw[];
     const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
     unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
-    const uint32_t sQ = sbase, sK = sbase + kOffK, bars = sbase + kOffBar;
+    const uint32_t sQ = sbase, sK = sbase + kOffK, bars = sbase + kOffBar;      // sQ: the rope part of Q only
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + kOffBar + 8 * P_COUNT);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + kOffBar + 8 * P_COUNT + 8);
     auto bar = [&](int i) { return bars + 8u * i; };
@@ -85,7 +87,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
     const int t_end = min(re, t_begin + a.tokens_per_split);
     const int ntiles = t_end > t_begin ? (t_end - t_begin + kTile - 1) / kTile : 0;
     const int64_t rows_all = (int64_t)p.b * p.hq;
-    const int nsub = rank == 0 ? 5 : 4;                                   // sub-tiles of 64 dims this CTA multiplies
 
     if (ntiles == 0) {                           // nothing cached in this split's range: both CTAs of the pair leave
         const int h = head0 + tid;
@@ -107,8 +108,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
     }
 
     if (tid == 0) {
-        mbar_init(bar(P_KF0), 8); mbar_init(bar(P_KF1), 8);
-        mbar_init(bar(P_KE0), 1); mbar_init(bar(P_KE1), 1);
+        for (int i = 0; i < kKBufs; ++i) { mbar_init(bar(P_KF0 + i), 8); mbar_init(bar(P_KE0 + i), 1); }
+        mbar_init(bar(P_QT), 128);
         mbar_init(bar(P_S0), 1); mbar_init(bar(P_S1), 1);
         mbar_init(bar(P_P0), 128); mbar_init(bar(P_P1), 128);
         for (int w = 0; w < 4; ++w) { mbar_init(bar(P_RF0 + w), 1); mbar_init(bar(P_RC0 + w), 1); }
@@ -120,20 +121,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
         tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
-    // ---- this CTA's part of Q: four latent sub-tiles (+ rope on rank 0), K-major [128 x 64], 128-byte swizzle -----
-    {
-        const T* qn = reinterpret_cast<const T*>(p.q_nope) + (int64_t)b * p.q_nope_stride_b + rank * 256;
+    // ---- Q: the rope part (rank 0) goes to shared memory as one K-major [128 x 64] sub-tile with 128-byte swizzle;
+    // the latent part goes to tensor memory (below, by the softmax warps)
+    if (rank == 0) {
         const T* qr = reinterpret_cast<const T*>(p.q_rope) + (int64_t)b * p.q_rope_stride_b;
-        const int chunks = nsub * 8;
-        for (int idx = tid; idx < 128 * chunks; idx += kThreads) {
-            const int r = idx / chunks, c = idx % chunks;
+        for (int idx = tid; idx < 128 * 8; idx += kThreads) {
+            const int r = idx >> 3, ch = idx & 7;
             const int h = head0 + r;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (h < p.hq)
-                v = __ldg(reinterpret_cast<const uint4*>(c < 32 ? qn + (int64_t)h * p.q_nope_stride_h + c * 8
-                                                                 : qr + (int64_t)h * p.q_rope_stride_h + (c - 32) * 8));
-            const int sub = c >> 3, ch = c & 7;
-            *reinterpret_cast<uint4*>(sgen + sub * kQSub + r * 128 + ((ch ^ (r & 7)) << 4)) = v;
+            if (h < p.hq) v = __ldg(reinterpret_cast<const uint4*>(qr + (int64_t)h * p.q_rope_stride_h + ch * 8));
+            *reinterpret_cast<uint4*>(sgen + r * 128 + ((ch ^ (r & 7)) << 4)) = v;
         }
     }
     fence_proxy_async_smem();
@@ -151,37 +148,45 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
         reg_dealloc<96>();
         if (warp == 12 && !dead) {
             // -------------------------------------------------------------- MMA issue (whole warp, one elected lane)
-            const uint64_t dQ = umma_desc(sQ, 16, 1024);
+            // latent part of the scores: A = Q from tensor memory (columns 384..511, two elements a column), B = the tile
+            // buffer; rope part (rank 0): both operands from shared memory
+            const uint64_t dQr = umma_desc(sQ, 16, 1024);
+            bool ok = mbar_wait(bar(P_QT), 0, abort_flag, err, 30);
             auto qk = [&](int j) -> bool {
-                const int s = j & 1;
-                if (!mbar_wait(bar(P_KF0 + s), (j >> 1) & 1, abort_flag, err, 31)) return false;
+                const int s = j & 1, kb = j % kKBufs;
+                if (!mbar_wait(bar(P_KF0 + kb), (j / kKBufs) & 1, abort_flag, err, 31)) return false;
                 tc_fence_after();
                 const uint32_t d_s = tmem + 256 + s * 64;
-                const uint64_t dK = umma_desc(sK + s * kKBuf, 16, 1024);
-                for (int sub = 0; sub < nsub; ++sub) {
-                    const uint64_t aq = umma_desc_at(dQ, sub * kQSub), bk = umma_desc_at(dK, sub * kKSub);
-                    if (sub == 0) umma_ss_wo<0, 0, 0>(d_s, aq, bk, IDESC_QK); else umma_ss_wo<1, 0, 0>(d_s, aq, bk, IDESC_QK);
-                    umma_ss_wo<1, 32, 32>(d_s, aq, bk, IDESC_QK);
-                    umma_ss_wo<1, 64, 64>(d_s, aq, bk, IDESC_QK);
-                    umma_ss_wo<1, 96, 96>(d_s, aq, bk, IDESC_QK);
+                const uint64_t dK = umma_desc(sK + kb * kKBuf, 16, 1024);
+                umma_ts_wo<0, 0, 0>(d_s, tmem + 384, dK, IDESC_QK);
+                static_for<1, 16>([&](auto kk) {
+                    constexpr uint32_t off = (kk.value >> 2) * kKSub + (kk.value & 3) * 32;
+                    umma_ts_wo<1, kk.value * 8, off>(d_s, tmem + 384, dK, IDESC_QK);
+                });
+                if (rank == 0) {
+                    const uint64_t bk = umma_desc_at(dK, 4 * kKSub);
+                    umma_ss_wo<1, 0, 0>(d_s, dQr, bk, IDESC_QK);
+                    umma_ss_wo<1, 32, 32>(d_s, dQr, bk, IDESC_QK);
+                    umma_ss_wo<1, 64, 64>(d_s, dQr, bk, IDESC_QK);
+                    umma_ss_wo<1, 96, 96>(d_s, dQr, bk, IDESC_QK);
                 }
                 umma_commit_w(bar(P_S0 + s));
                 return true;
             };
             auto pv = [&](int j) -> bool {
-                const int s = j & 1;
+                const int s = j & 1, kb = j % kKBufs;
                 if (!mbar_wait(bar(P_P0 + s), (j >> 1) & 1, abort_flag, err, 32)) return false;
                 tc_fence_after();
                 const uint32_t a_p = tmem + 256 + s * 64;
-                const uint64_t dV = umma_desc(sK + s * kKBuf, kKSub, 1024);   // MN-major: four 64-column groups kKSub apart
+                const uint64_t dV = umma_desc(sK + kb * kKBuf, kKSub, 1024);  // MN-major: four 64-column groups kKSub apart
                 if (j > 0) umma_ts_wo<1, 0, 0>(tmem, a_p, dV, IDESC_PV); else umma_ts_wo<0, 0, 0>(tmem, a_p, dV, IDESC_PV);
                 umma_ts_wo<1, 8, 2048>(tmem, a_p, dV, IDESC_PV);
                 umma_ts_wo<1, 16, 4096>(tmem, a_p, dV, IDESC_PV);
                 umma_ts_wo<1, 24, 6144>(tmem, a_p, dV, IDESC_PV);
-                umma_commit_w(bar(P_KE0 + s));
+                umma_commit_w(bar(P_KE0 + kb));
                 return true;
             };
-            bool ok = qk(0);
+            if (ok) ok = qk(0);
             for (int j = 1; j < ntiles && ok; ++j) {
                 ok = qk(j);                       // the scores of tile j run while the softmax of tile j - 1 is busy
                 if (ok) ok = pv(j - 1);
@@ -231,10 +236,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
         int64_t row_next = tile_row(2);                                    // page-table entries are fetched one tile earlier still
         bool ok = true;
         auto body = [&](auto par, int j) {
-            constexpr int P = decltype(par)::value;                        // = j & 1: register set and tile buffer
-            if (j >= 2) ok = mbar_wait_relaxed(bar(P_KE0 + P), ((j >> 1) - 1) & 1, abort_flag, err, 33);
+            constexpr int P = decltype(par)::value;                        // = j & 1: register set
+            const int kb = j % kKBufs;                                     // tile buffer
+            if (j >= kKBufs) ok = mbar_wait_relaxed(bar(P_KE0 + kb), (j / kKBufs - 1) & 1, abort_flag, err, 33);
             if (!ok) return;
-            unsigned char* kbuf = sgen + kOffK + P * kKBuf;
+            unsigned char* kbuf = sgen + kOffK + kb * kKBuf;
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const int row = r * 16 + krow;
@@ -260,7 +266,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(P_KF0 + P));
+            if (lane == 0) mbar_arrive(bar(P_KF0 + kb));
             if (j + 2 < ntiles) {
                 const int64_t slot0 = row_next;
                 row_next = tile_row(j + 3);
@@ -284,6 +290,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
         float m_used = -INFINITY, l_run = 0.f;
         const float scl = a.scale_log2;
         bool ok = true;
+        {   // this head's 256 latent query values -> tensor-memory columns 384..511 (the raw pairs of bf16 values)
+            const int h = head0 + r;
+            const T* qn = reinterpret_cast<const T*>(p.q_nope) + (int64_t)b * p.q_nope_stride_b + (int64_t)h * p.q_nope_stride_h + rank * 256;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t w[32];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (h < p.hq) v = __ldg(reinterpret_cast<const uint4*>(qn + c * 64 + i * 8));
+                    w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+                }
+                tmem_st32(tmem + lane_base + 384 + c * 32, w);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(P_QT));
+        }
         for (int j = 0; j < ntiles && ok; ++j) {
             const int s = j & 1;
             const uint32_t t_s = tmem + lane_base + 256 + s * 64;
@@ -358,7 +382,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
             // The exponent base moves only when the row maximum outgrows it by 2^8.  P V of tile j - 1 was issued
             // after the scores of tile j, so its completion is awaited before the accumulator is rescaled.
             if (j > 0 && __any_sync(0xffffffffu, m_new > m_used + kRescaleThreshold)) {
-                ok = mbar_wait(bar(P_KE0 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, err, 37);
+                ok = mbar_wait(bar(P_KE0 + (j - 1) % kKBufs), ((j - 1) / kKBufs) & 1, abort_flag, err, 37);
                 if (!ok) break;
                 tc_fence_after();
                 const float m_next = fmaxf(m_used, m_new);
