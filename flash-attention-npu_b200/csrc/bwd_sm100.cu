@@ -68,8 +68,9 @@ struct BwdSm100Smem {
 };
 
 enum { E_FIX = 0, E_RF0, E_RF1, E_RE0, E_RE1, E_S0, E_S1, E_P0, E_P1, E_F0, E_F1, E_ACC, E_COUNT };
-// barriers of the dQ kernel: three score buffers
-enum { G_FIX = 0, G_RF0, G_RF1, G_RE0, G_RE1, G_S0, G_S1, G_S2, G_P0, G_P1, G_P2, G_F0, G_F1, G_F2, G_ACC, G_COUNT };
+// barriers of the dQ kernel: KF/KE, VF/VE K and V stage full / free; S scores done; SA scores read; DP dP done; DS dS stored
+enum { G_FIX = 0, G_KF0, G_KF1, G_KF2, G_KE0, G_KE1, G_KE2, G_VF0, G_VF1, G_VE0, G_VE1, G_S0, G_S1, G_SA0, G_SA1, G_DP, G_DS,
+       G_ACC, G_COUNT };
 
 template <typename T>
 __device__ __forceinline__ void store_row_scaled(T* dst, const uint32_t (&r)[32], float s) {
@@ -336,18 +337,23 @@ template <typename T, int D>
 __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
     using L = BwdSm100Smem<D>;
     constexpr int NSUB = D / 64, KSTEPS = D / 16;
-    constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 192, COL_DQ = 384;     // S / dP: 3 x 64 columns each
+    // One unit = one 128-key tile.  S has two buffers (the scores of the next tile are multiplied while this tile is in
+    // the element-wise stage), dP one (dS is written over it and read by the dQ MMA), dQ accumulates.
+    constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_DP = 256, COL_DQ = 384;
     constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
-    constexpr uint32_t IDESC_S = umma_idesc(FMT, 128, 64, 0, 0);
+    constexpr uint32_t IDESC_S = umma_idesc(FMT, 128, 128, 0, 0);
     constexpr uint32_t IDESC_ACC = umma_idesc(FMT, 128, D, 0, 1);
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
     unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
-    const uint32_t sQ = sbase + L::oFix0, sdO = sbase + L::oFix1, sK = sbase + L::oRing0, sV = sbase + L::oRing1;
-    const uint32_t bars = sbase + L::oBar;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * G_COUNT);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * G_COUNT + 8);
+    // Q | dO | three K stages | two V stages: the scores of tile t + 1 are multiplied before dQ of tile t - 1 has
+    // released its K, so K needs one stage more than V
+    constexpr int oK = 2 * L::kTileB, oV = 5 * L::kTileB, oBarQ = 7 * L::kTileB;
+    const uint32_t sQ = sbase, sdO = sbase + L::kTileB, sK = sbase + oK, sV = sbase + oV;
+    const uint32_t bars = sbase + oBarQ;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + oBarQ + 8 * G_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + oBarQ + 8 * G_COUNT + 8);
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -380,7 +386,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
         return;
     }
     if (tid == 0) {
-        for (int i = 0; i < G_COUNT; ++i) mbar_init(bar(i), (i >= G_P0 && i <= G_P2) ? 512u : 1u);
+        for (int i = 0; i < G_COUNT; ++i) mbar_init(bar(i), (i == G_SA0 || i == G_SA1 || i == G_DS) ? 512u : 1u);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -404,78 +410,79 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
             }
             bool ok = true;
             for (int j = 0; j < ntiles && ok; ++j) {
-                const int st = j & 1, use = j >> 1;
+                const int ks = j % 3, vs = j & 1;
                 const int krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128;
-                if (use > 0) ok = mbar_wait(bar(G_RE0 + st), (use - 1) & 1, abort_flag, err, 31);
+                if (j >= 3) ok = mbar_wait(bar(G_KE0 + ks), (j / 3 - 1) & 1, abort_flag, err, 31);
                 if (!ok) break;
-                mbar_expect_tx(bar(G_RF0 + st), 2 * L::kTileB);
+                mbar_expect_tx(bar(G_KF0 + ks), L::kTileB);
 #pragma unroll
-                for (int c = 0; c < NSUB; ++c) {
-                    tma_load_4d(sK + st * L::kTileB + c * L::kSub, &a.tk, bar(G_RF0 + st), c * 64, hk, krow, bb);
-                    tma_load_4d(sV + st * L::kTileB + c * L::kSub, &a.tv, bar(G_RF0 + st), c * 64, hk, krow, bb);
-                }
+                for (int c = 0; c < NSUB; ++c) tma_load_4d(sK + ks * L::kTileB + c * L::kSub, &a.tk, bar(G_KF0 + ks), c * 64, hk, krow, bb);
+                if (j >= 2) ok = mbar_wait(bar(G_VE0 + vs), ((j >> 1) - 1) & 1, abort_flag, err, 39);
+                if (!ok) break;
+                mbar_expect_tx(bar(G_VF0 + vs), L::kTileB);
+#pragma unroll
+                for (int c = 0; c < NSUB; ++c) tma_load_4d(sV + vs * L::kTileB + c * L::kSub, &a.tv, bar(G_VF0 + vs), c * 64, hk, krow, bb);
             }
         }
     } else if (warp == 17) {
         {
-            const int units = ntiles * 2;
             const uint64_t dQ0 = umma_desc(sQ, 16, 1024), dO0 = umma_desc(sdO, 16, 1024);
             const uint64_t dKk = umma_desc(sK, 16, 1024), dVk = umma_desc(sV, 16, 1024);
-            auto issue_sd = [&](int u, int bi) {            // S and dP against the 64 keys of half u, into buffer bi
-                const int st = (u >> 1) & 1, hf = u & 1;
-                const uint32_t boff = st * L::kTileB + hf * 8192;
-                const uint64_t bk = umma_desc_at(dKk, boff), bv = umma_desc_at(dVk, boff);
-                const uint32_t d_s = tmem + COL_S + bi * 64, d_p = tmem + COL_DP + bi * 64;
-                umma_ss_w<0>(d_s, dQ0, bk, IDESC_S);
+            const uint64_t dKm = umma_desc(sK, L::kSub, 1024);
+            // [128 queries x 128 keys] = A (Q or dO, K-major) x B (K or V tile of stage st, K-major)
+            auto issue_scores = [&](uint32_t d_t, uint64_t a0, uint64_t b0, int stage) {
+                const uint64_t bt = umma_desc_at(b0, stage * L::kTileB);
+                umma_ss_w<0>(d_t, a0, bt, IDESC_S);
 #pragma unroll
                 for (int kk = 1; kk < KSTEPS; ++kk) {
                     const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss_w<1>(d_s, umma_desc_at(dQ0, off), umma_desc_at(bk, off), IDESC_S);
+                    umma_ss_w<1>(d_t, umma_desc_at(a0, off), umma_desc_at(bt, off), IDESC_S);
                 }
-                umma_ss_w<0>(d_p, dO0, bv, IDESC_S);
-#pragma unroll
-                for (int kk = 1; kk < KSTEPS; ++kk) {
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss_w<1>(d_p, umma_desc_at(dO0, off), umma_desc_at(bv, off), IDESC_S);
-                }
-                umma_commit_w(bar(G_S0 + bi));
             };
             bool ok = mbar_wait(bar(G_FIX), 0, abort_flag, err, 32);
-            // three score buffers rotate: the MMAs of unit u + 2 are issued while the element-wise warps work on unit
-            // u + 1 and the dQ MMA of unit u is still pending
-            for (int u = 0, bi = 0, rnd = 0; u < units && ok; ++u) {
-                const int j1 = u >> 1;
-                if (u >= 3) ok = mbar_wait(bar(G_F0 + bi), (rnd - 1) & 1, abort_flag, err, 37);
-                if (ok && (u & 1) == 0) ok = mbar_wait(bar(G_RF0 + (j1 & 1)), (j1 >> 1) & 1, abort_flag, err, 33);
-                if (!ok) break;
+            if (ok) ok = mbar_wait(bar(G_KF0), 0, abort_flag, err, 33);
+            if (ok) {
                 tc_fence_after();
-                issue_sd(u, bi);
-                if (++bi == 3) { bi = 0; ++rnd; }
+                issue_scores(tmem + COL_S, dQ0, dKk, 0);
+                umma_commit_w(bar(G_S0));
             }
-        }
-    } else if (warp == 18) {
-        {
-            const int units = ntiles * 2;
-            const uint64_t dKm = umma_desc(sK, L::kSub, 1024);
-            bool ok = true;
-            for (int u = 0, bi = 0, rnd = 0; u < units && ok; ++u) {
-                ok = mbar_wait(bar(G_P0 + bi), rnd & 1, abort_flag, err, 34);
+            // Order on the (in-order) tensor pipe: dP(t), S(t+1), dQ(t).  dP(t) follows dQ(t-1) in program order, so dS
+            // of the previous tile has been consumed before dP overwrites its columns.
+            for (int t = 0; t < ntiles && ok; ++t) {
+                const int ks = t % 3, vs = t & 1;
+                ok = mbar_wait(bar(G_VF0 + vs), (t >> 1) & 1, abort_flag, err, 40);
                 if (!ok) break;
                 tc_fence_after();
-                const int st = (u >> 1) & 1, hf = u & 1;
-                const uint64_t bk = umma_desc_at(dKm, st * L::kTileB + hf * 8192);
-                const uint32_t a_s = tmem + COL_DP + bi * 64;
-                if (u > 0) umma_ts_w<1>(tmem + COL_DQ, a_s, bk, IDESC_ACC); else umma_ts_w<0>(tmem + COL_DQ, a_s, bk, IDESC_ACC);
+                issue_scores(tmem + COL_DP, dO0, dVk, vs);
+                umma_commit_w(bar(G_DP));
+                umma_commit_w(bar(G_VE0 + vs));              // V of this tile is not read again
+                if (t + 1 < ntiles) {
+                    const int s1 = (t + 1) & 1, k1 = (t + 1) % 3;
+                    ok = mbar_wait(bar(G_KF0 + k1), ((t + 1) / 3) & 1, abort_flag, err, 33);
+                    // the element-wise warps have read the scores that lived in this buffer two tiles ago
+                    if (ok && t >= 1) ok = mbar_wait(bar(G_SA0 + s1), ((t - 1) >> 1) & 1, abort_flag, err, 37);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_scores(tmem + COL_S + s1 * 128, dQ0, dKk, k1);
+                    umma_commit_w(bar(G_S0 + s1));
+                }
+                ok = mbar_wait(bar(G_DS), t & 1, abort_flag, err, 34);
+                if (!ok) break;
+                tc_fence_after();
+                // dQ += dS (tensor memory, 16 keys in 8 columns at a stride of 16) x K tile read key-major
+                const uint64_t bk = umma_desc_at(dKm, ks * L::kTileB);
+                if (t > 0) umma_ts_w<1>(tmem + COL_DQ, tmem + COL_DP, bk, IDESC_ACC); else umma_ts_w<0>(tmem + COL_DQ, tmem + COL_DP, bk, IDESC_ACC);
 #pragma unroll
-                for (int kk = 1; kk < 4; ++kk) umma_ts_w<1>(tmem + COL_DQ, a_s + kk * 16, umma_desc_at(bk, kk * 2048), IDESC_ACC);
-                umma_commit_w(bar(G_F0 + bi));
-                if (u & 1) umma_commit_w(bar(G_RE0 + st));
-                if (++bi == 3) { bi = 0; ++rnd; }
+                for (int kk = 1; kk < 8; ++kk) umma_ts_w<1>(tmem + COL_DQ, tmem + COL_DP + kk * 16, umma_desc_at(bk, kk * 2048), IDESC_ACC);
+                umma_commit_w(bar(G_KE0 + ks));
             }
             if (ok) umma_commit_w(bar(G_ACC));
         }
+    } else if (warp == 18) {
+        // spare warp of the last group
     } else {
-        const int cg = warp >> 2;                            // which 16 key columns of a half
+        // element-wise warps: thread = (query row, 32 of the tile's 128 key columns)
+        const int cg = warp >> 2;
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const int qi = m0 + r;
@@ -487,37 +494,58 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
             lse2 = a.lse[(a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + tok * a.lse_ss] * kLog2e;
             dl = a.delta[((a.cu_q ? tok : (int64_t)b * a.sq + qi)) * a.hq + h];
         }
+        const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dl, -dl);
         bool ok = true;
-        const int units = ntiles * 2;
-        for (int u = 0, bi = 0, rnd = 0; u < units && ok; ++u) {
-            const int hf = u & 1;
-            const int c0 = (t_lo + (u >> 1)) * 128 + hf * 64 + cg * 16;     // first key of this thread's 16 columns
-            ok = mbar_wait(bar(G_S0 + bi), rnd & 1, abort_flag, err, 35);
-            if (!ok) break;
+        uint32_t pr[32];                                     // P of the tile in flight (fp32 bits)
+        // phase A: P = exp2(S * c - LSE) of tile t into registers
+        auto phase_a = [&](int t) {
+            const int sb = t & 1;
+            const int c0 = (t_lo + t) * 128 + cg * 32;      // first key of this thread's 32 columns
+            ok = mbar_wait(bar(G_S0 + sb), (t >> 1) & 1, abort_flag, err, 35);
+            if (!ok) return;
             tc_fence_after();
-            uint32_t sr[16], dr[16], pS[8];
-            tmem_ld16(tmem + lane_base + COL_S + bi * 64 + cg * 16, sr);
-            tmem_ld16(tmem + lane_base + COL_DP + bi * 64 + cg * 16, dr);
+            tmem_ld32(tmem + lane_base + COL_S + sb * 128 + cg * 32, pr);
             tmem_wait_ld();
-            const bool inside = __all_sync(0xffffffffu, c0 >= klo && c0 + 15 <= khi);
-            const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dl, -dl);
+            tc_fence_before();
+            mbar_arrive(bar(G_SA0 + sb));                    // the score buffer may be overwritten
+            const bool inside = __all_sync(0xffffffffu, c0 >= klo && c0 + 31 <= khi);
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-                const float2 x = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, nl2);
+            for (int i = 0; i < 32; i += 2) {
+                const float2 x = fma2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), sc2, nl2);
                 float2 p = make_float2(ex2_approx(x.x), ex2_approx(x.y));
                 if (!inside) {
                     const int col = c0 + i;
                     p.x = (col >= klo && col <= khi) ? p.x : 0.f;
                     p.y = (col + 1 >= klo && col + 1 <= khi) ? p.y : 0.f;
                 }
-                const float2 ds = mul2(p, add2(make_float2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])), nd2));
-                pS[i / 2] = Elem<T>::pack(ds.x, ds.y);
+                pr[i] = __float_as_uint(p.x);
+                pr[i + 1] = __float_as_uint(p.y);
             }
-            tmem_st8(tmem + lane_base + COL_DP + bi * 64 + cg * 16, pS);
+        };
+        phase_a(0);
+        for (int t = 0; t < ntiles && ok; ++t) {
+            // phase B: dS = P * (dP - delta), rounded, over dP's own columns
+            ok = mbar_wait(bar(G_DP), t & 1, abort_flag, err, 38);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t dr[32], lo8[8], hi8[8];
+            tmem_ld32(tmem + lane_base + COL_DP + cg * 32, dr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float2 ds = mul2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])),
+                                       add2(make_float2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])), nd2));
+                const uint32_t w = Elem<T>::pack(ds.x, ds.y);
+                if (i < 16) lo8[i / 2] = w; else hi8[(i - 16) / 2] = w;
+            }
+            // each group of 16 keys (one K step of the dQ MMA) sits in 8 columns at a stride of 16, inside the columns
+            // this thread has just read
+            tmem_st8(tmem + lane_base + COL_DP + cg * 32, lo8);
+            tmem_st8(tmem + lane_base + COL_DP + cg * 32 + 16, hi8);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(G_P0 + bi));
-            if (++bi == 3) { bi = 0; ++rnd; }
+            mbar_arrive(bar(G_DS));
+            if (t + 1 < ntiles) phase_a(t + 1);
         }
         if (ok) ok = mbar_wait(bar(G_ACC), 0, abort_flag, err, 36);
         if (ok) {
@@ -639,7 +667,8 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
     auto k2 = bwd_dq_sm100_kernel<T, D>;
     const int smem = BwdSm100Smem<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-    if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+    const int smem_dq = 7 * BwdSm100Smem<D>::kTileB + 256 + 1024;     // Q, dO, three K stages, two V stages, barriers
+    if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq), "cudaFuncSetAttribute")) return e;
     dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g2((p.sq + 127) / 128, p.hq, p.b);
     // dK/dV and dQ are independent of each other (both need only delta): the dQ kernel goes to an internal stream
     // that is forked from and joined back into the caller's stream, so that its CTAs fill the SMs the last wave of
@@ -659,7 +688,7 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
     }
     k1<<<g1, 608, smem, st>>>(a);
     mark_kernel(st);
-    k2<<<g2, 608, smem, side ? side : st>>>(a);
+    k2<<<g2, 608, smem_dq, side ? side : st>>>(a);
     mark_kernel(st);
     if (side) {
         cudaEventRecord(join, side);
