@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(128) decode_splitkv_kernel(const DecodeArgs a)
 
 
 // -------------------------------------------------------------------------------------------------------
-// The same kernel with the cache tiles brought in by TMA (cp.async.bulk.tensor, no multicast).
+// The same kernel with the cache tiles brought in by TMA (cp.async.bulk.tensor, each copy to one CTA).
 // 16-byte cp.async copies are tracked by the SM's load/store unit, which caps the bytes a warp can keep in
 // flight far below what HBM3e needs; a bulk tensor copy of a (32 tokens x 64 dims) box is one request.
 // Lane 0 of each warp arms the stage's mbarrier and issues the boxes, addressed by

@@ -44,7 +44,7 @@ constexpr int kKBufs = 3;                        // tile buffers in flight
 constexpr int kOffK = kQSub, kOffRecv = kOffK + kKBufs * kKBuf, kOffBar = kOffRecv + 4 * 2 * kXchg;      // per softmax warp: a send buffer and a receive buffer
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
 constexpr int kThreads = 16 * 32;
-static_assert(kSmemBytes <= 232448, "shared memory budget");
+static_assert(kSmemBytes <= 232448, "shared memory limit of a CTA");
 // KF/KE: tile buffer full / free; QT: the latent part of Q is in tensor memory; S: partial scores complete; P: probabilities written; RF (one per softmax warp):
 // the peer warp's partial has landed in my receive buffer; RC: the peer warp has read what I copied into its receive
 // buffer; O: all MMAs done
