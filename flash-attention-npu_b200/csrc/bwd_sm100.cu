@@ -15,13 +15,15 @@
 // :1447-1480, fag_epilogue_post.hpp:149-200): P and dS rounded before the second GEMMs, dQ and dK
 // multiplied by the softmax scale at the end.
 //
-// A 128 x 128 score tile is processed as two 64-column halves that ping-pong between two TMEM buffers:
-// while the element-wise warps turn half u into P / dS, the tensor core already computes the scores of
-// half u+1 and then consumes half u.  Tensor memory: S0 S1 | dP0 dP1 (64 columns each) | acc | acc (128
-// each).  Warps 0-15 do the element-wise work (thread = TMEM lane, each group of four warps takes 16 of the
-// 64 score columns of a half: four warps per scheduler hide the TMEM and exp latencies), warp 16 is the
-// TMA producer, warp 17 issues the score MMAs and warp 18 the accumulating MMAs (one issuing thread alone
-// could not keep the tensor pipe fed).  All waits are bounded.
+// Both kernels work on whole 128 x 128 score tiles (N = 128 score MMAs; 64-column halves cost ~50 cycles a K step
+// instead of 32).  dK/dV: tensor memory holds S^T | dP^T | dK | dV (128 columns each), nothing is double-buffered,
+// and the overlap comes from the order on the in-order tensor pipe: S^T(s) dP^T(s) | dV(s) S^T(s+1) | dK(s)
+// dP^T(s+1) | ...  -- P^T lies over S^T and dS^T over dP^T, so the next scores simply follow the MMA that reads
+// what they overwrite, and the exponentials of block s+1 run while dK(s) and dP^T(s+1) are multiplied.  dQ: S has
+// two buffers, dP one, dQ accumulates; order dP(t) S(t+1) dQ(t); K has three shared-memory stages (S(t+1) is
+// multiplied before dQ(t-1) has released its K), V two.  Warps 0-15 do the element-wise work (thread = TMEM lane,
+// each group of four warps takes 32 of a tile's 128 score columns) in two phases, exponentials then dS; warp 16 is
+// the TMA producer, warp 17 issues all MMAs.  All waits are bounded.
 #include "fa_utils.cuh"
 #include "fa_internal.h"
 #include "sm100_ptx.cuh"
@@ -62,8 +64,8 @@ struct BwdSm100Smem {
     static constexpr int oFix1 = oFix0 + kTileB;            // V (dkdv) or dO (dq)
     static constexpr int oRing0 = oFix1 + kTileB;           // 2 stages: Q (dkdv) or K (dq)
     static constexpr int oRing1 = oRing0 + 2 * kTileB;      // 2 stages: dO (dkdv) or V (dq)
-    static constexpr int oVec = oRing1 + 2 * kTileB;        // per warp: 2 stages x (16 lse2 + 16 delta) floats
-    static constexpr int oBar = oVec + 16 * 64 * 4;
+    static constexpr int oVec = oRing1 + 2 * kTileB;        // per warp: 2 stages x (32 lse2 + 32 delta) floats
+    static constexpr int oBar = oVec + 16 * 128 * 4;
     static constexpr int kBytes = oBar + 256;
 };
 
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
     constexpr int NSUB = D / 64, KSTEPS = D / 16;
     constexpr uint32_t TMEM_COLS = 512, COL_ST = 0, COL_DPT = 128, COL_DK = 256, COL_DV = 384;   // ST/DPT: 2 x 64
     constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
-    constexpr uint32_t IDESC_ST = umma_idesc(FMT, 128, 64, 0, 0);
+    constexpr uint32_t IDESC_ST = umma_idesc(FMT, 128, 128, 0, 0);
     constexpr uint32_t IDESC_ACC = umma_idesc(FMT, 128, D, 0, 1);
 
     extern __shared__ unsigned char smem_raw[];
@@ -142,7 +144,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
     }
 
     if (tid == 0) {
-        for (int i = 0; i < E_COUNT; ++i) mbar_init(bar(i), (i == E_P0 || i == E_P1) ? 512u : 1u);
+        for (int i = 0; i < E_COUNT; ++i) mbar_init(bar(i), (i == E_P0 || i == E_P1) ? 512u : 1u);   // P0: P^T stored, P1: dS^T stored
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -181,67 +183,68 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
         }
     } else if (warp == 17) {
         {
-            const int units = steps * 2;
+            // One unit = one 128-query block.  E_S0: S^T done, E_S1: dP^T done, E_P0: P^T stored, E_P1: dS^T stored.
+            // Order on the in-order tensor pipe: S^T(s) dP^T(s) | dV(s) S^T(s+1) | dK(s) dP^T(s+1) | ...: P^T lies over
+            // S^T and dS^T over dP^T, so the next scores follow the MMA that read what they overwrite; the exponentials
+            // of block s + 1 run while dK(s) and dP^T(s + 1) are multiplied.
             const uint64_t dK0 = umma_desc(sK, 16, 1024), dV0 = umma_desc(sV, 16, 1024);
             const uint64_t dQk = umma_desc(sQ, 16, 1024), dOk = umma_desc(sdO, 16, 1024);           // K-major views
-            auto issue_sd = [&](int u) {                    // S^T and dP^T of half u into buffer u & 1
-                const int st = (u >> 1) & 1, hf = u & 1;
-                const uint32_t boff = st * L::kTileB + hf * 8192;
-                const uint64_t bq = umma_desc_at(dQk, boff), bo = umma_desc_at(dOk, boff);
-                const uint32_t d_s = tmem + COL_ST + hf * 64, d_p = tmem + COL_DPT + hf * 64;
-                umma_ss_w<0>(d_s, dK0, bq, IDESC_ST);
-#pragma unroll
-                for (int kk = 1; kk < KSTEPS; ++kk) {
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss_w<1>(d_s, umma_desc_at(dK0, off), umma_desc_at(bq, off), IDESC_ST);
-                }
-                umma_ss_w<0>(d_p, dV0, bo, IDESC_ST);
-#pragma unroll
-                for (int kk = 1; kk < KSTEPS; ++kk) {
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss_w<1>(d_p, umma_desc_at(dV0, off), umma_desc_at(bo, off), IDESC_ST);
-                }
-                umma_commit_w(bar(E_S0 + hf));
-            };
-            // this warp: score MMAs.  Half u may overwrite its TMEM buffer once the accumulating MMAs of half u-2
-            // (issued by warp 18) have read it.
-            bool ok = mbar_wait(bar(E_FIX), 0, abort_flag, err, 22);
-            for (int u = 0; u < units && ok; ++u) {
-                const int s1 = u >> 1;
-                if (u >= 2) ok = mbar_wait(bar(E_F0 + (u & 1)), (s1 - 1) & 1, abort_flag, err, 27);
-                if (ok && (u & 1) == 0) ok = mbar_wait(bar(E_RF0 + (s1 & 1)), (s1 >> 1) & 1, abort_flag, err, 23);
-                if (!ok) break;
-                tc_fence_after();
-                issue_sd(u);
-            }
-        }
-    } else if (warp == 18) {
-        {
-            const int units = steps * 2;
             const uint64_t dQm = umma_desc(sQ, L::kSub, 1024), dOm = umma_desc(sdO, L::kSub, 1024); // MN-major views
-            bool ok = true;
-            for (int u = 0; u < units && ok; ++u) {
-                ok = mbar_wait(bar(E_P0 + (u & 1)), (u >> 1) & 1, abort_flag, err, 24);
+            auto issue_scores = [&](uint32_t d_t, uint64_t a0, uint64_t b0, int st) {
+                const uint64_t bt = umma_desc_at(b0, st * L::kTileB);
+                umma_ss_w<0>(d_t, a0, bt, IDESC_ST);
+#pragma unroll
+                for (int kk = 1; kk < KSTEPS; ++kk) {
+                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+                    umma_ss_w<1>(d_t, umma_desc_at(a0, off), umma_desc_at(bt, off), IDESC_ST);
+                }
+            };
+            // acc += A (tensor memory: 16 queries in 8 columns at a stride of 16) x B (query-major tile of stage st)
+            auto issue_acc = [&](uint32_t d_t, uint32_t a_t, uint64_t b0, int st, bool first) {
+                const uint64_t bt = umma_desc_at(b0, st * L::kTileB);
+                if (!first) umma_ts_w<1>(d_t, a_t, bt, IDESC_ACC); else umma_ts_w<0>(d_t, a_t, bt, IDESC_ACC);
+#pragma unroll
+                for (int kk = 1; kk < 8; ++kk) umma_ts_w<1>(d_t, a_t + kk * 16, umma_desc_at(bt, kk * 2048), IDESC_ACC);
+            };
+            bool ok = mbar_wait(bar(E_FIX), 0, abort_flag, err, 22);
+            if (ok) ok = mbar_wait(bar(E_RF0), 0, abort_flag, err, 23);
+            if (ok) {
+                tc_fence_after();
+                issue_scores(tmem + COL_ST, dK0, dQk, 0);
+                umma_commit_w(bar(E_S0));
+                issue_scores(tmem + COL_DPT, dV0, dOk, 0);
+                umma_commit_w(bar(E_S1));
+            }
+            for (int s = 0; s < steps && ok; ++s) {
+                const int st = s & 1, s1 = (s + 1) & 1;
+                ok = mbar_wait(bar(E_P0), s & 1, abort_flag, err, 24);
                 if (!ok) break;
                 tc_fence_after();
-                const int st = (u >> 1) & 1, hf = u & 1;
-                const uint32_t boff = st * L::kTileB + hf * 8192;
-                const uint64_t bo = umma_desc_at(dOm, boff), bq = umma_desc_at(dQm, boff);
-                const uint32_t a_p = tmem + COL_ST + hf * 64, a_s = tmem + COL_DPT + hf * 64;
-                if (u > 0) umma_ts_w<1>(tmem + COL_DV, a_p, bo, IDESC_ACC); else umma_ts_w<0>(tmem + COL_DV, a_p, bo, IDESC_ACC);
-#pragma unroll
-                for (int kk = 1; kk < 4; ++kk) umma_ts_w<1>(tmem + COL_DV, a_p + kk * 16, umma_desc_at(bo, kk * 2048), IDESC_ACC);
-                if (u > 0) umma_ts_w<1>(tmem + COL_DK, a_s, bq, IDESC_ACC); else umma_ts_w<0>(tmem + COL_DK, a_s, bq, IDESC_ACC);
-#pragma unroll
-                for (int kk = 1; kk < 4; ++kk) umma_ts_w<1>(tmem + COL_DK, a_s + kk * 16, umma_desc_at(bq, kk * 2048), IDESC_ACC);
-                umma_commit_w(bar(E_F0 + hf));
-                if (u & 1) umma_commit_w(bar(E_RE0 + st));
+                issue_acc(tmem + COL_DV, tmem + COL_ST, dOm, st, s == 0);
+                if (s + 1 < steps) {
+                    ok = mbar_wait(bar(E_RF0 + s1), ((s + 1) >> 1) & 1, abort_flag, err, 23);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_scores(tmem + COL_ST, dK0, dQk, s1);
+                    umma_commit_w(bar(E_S0));
+                }
+                ok = mbar_wait(bar(E_P1), s & 1, abort_flag, err, 27);
+                if (!ok) break;
+                tc_fence_after();
+                issue_acc(tmem + COL_DK, tmem + COL_DPT, dQm, st, s == 0);
+                umma_commit_w(bar(E_RE0 + st));
+                if (s + 1 < steps) {
+                    issue_scores(tmem + COL_DPT, dV0, dOk, s1);
+                    umma_commit_w(bar(E_S1));
+                }
             }
             if (ok) umma_commit_w(bar(E_ACC));
         }
+    } else if (warp == 18) {
+        // spare warp of the last group
     } else {
-        // ------------------------------------------------------------ element-wise: thread = key row
-        const int cg = warp >> 2;                            // which 16 query columns of a half
+        // ------------------------------------------------------------ element-wise: thread = (key row, 32 query columns)
+        const int cg = warp >> 2;
         const int r = (warp & 3) * 32 + lane;                // TMEM lane = key row of the tile
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const int n = n0 + r;
@@ -251,40 +254,40 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
         if (wl >= 0) qi_hi = min(sq - 1, n + wl - diff);
         if (n >= sk) { qi_lo = 1; qi_hi = 0; }
         bool ok = true;
-        const int units = steps * 2;
-        // -LSE (log2 domain, lanes 0-15) / -delta (lanes 16-31) of the warp's 16 query columns, fetched one unit ahead
-        auto fetch_vec = [&](int u) -> float {
-            const int s = u >> 1;
+        // -LSE (log2 domain) and -delta of the warp's 32 query columns, one per lane, fetched one step ahead
+        auto fetch_vec = [&](int s, float& nl, float& nd) {
             const int h = hk * G + s / nmb;
-            const int i = (mb_lo + s % nmb) * 128 + (u & 1) * 64 + cg * 16 + (lane & 15);
-            if (i >= sq) return lane < 16 ? -INFINITY : 0.f;
-            const int64_t tok = (int64_t)q_off + i;
-            return lane < 16 ? -a.lse[(a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + tok * a.lse_ss] * kLog2e
-                             : -a.delta[((a.cu_q ? tok : (int64_t)b * a.sq + i)) * a.hq + h];
+            const int i = (mb_lo + s % nmb) * 128 + cg * 32 + lane;
+            nl = -INFINITY; nd = 0.f;
+            if (i < sq) {
+                const int64_t tok = (int64_t)q_off + i;
+                nl = -a.lse[(a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + tok * a.lse_ss] * kLog2e;
+                nd = -a.delta[((a.cu_q ? tok : (int64_t)b * a.sq + i)) * a.hq + h];
+            }
         };
-        float staged = fetch_vec(0);
-        for (int u = 0; u < units && ok; ++u) {
-            const int s = u >> 1, hf = u & 1;
-            const int i0 = (mb_lo + s % nmb) * 128 + hf * 64 + cg * 16;      // first query row of this thread's 16 columns
-            float* vec = sVec + warp * 64 + (u & 1) * 32;               // [0,16) lse2, [16,32) delta
-            vec[lane] = staged;
+        float st_l, st_d;
+        fetch_vec(0, st_l, st_d);
+        const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
+        for (int s = 0; s < steps && ok; ++s) {
+            const int i0 = (mb_lo + s % nmb) * 128 + cg * 32;           // first query row of this thread's 32 columns
+            float* vec = sVec + warp * 128 + (s & 1) * 64;              // [0,32) -lse2, [32,64) -delta
+            vec[lane] = st_l;
+            vec[32 + lane] = st_d;
             __syncwarp();
-            if (u + 1 < units) staged = fetch_vec(u + 1);
-            ok = mbar_wait(bar(E_S0 + hf), (u >> 1) & 1, abort_flag, err, 25);
+            if (s + 1 < steps) fetch_vec(s + 1, st_l, st_d);
+            // phase A: P^T = exp2(S^T c - LSE) -> registers (fp32) and, rounded, over S^T's columns
+            ok = mbar_wait(bar(E_S0), s & 1, abort_flag, err, 25);
             if (!ok) break;
             tc_fence_after();
-            uint32_t sr[16], dr[16], pP[8], pS[8];
-            tmem_ld16(tmem + lane_base + COL_ST + hf * 64 + cg * 16, sr);
-            tmem_ld16(tmem + lane_base + COL_DPT + hf * 64 + cg * 16, dr);
+            uint32_t pr[32], lo8[8], hi8[8];
+            tmem_ld32(tmem + lane_base + COL_ST + cg * 32, pr);
             tmem_wait_ld();
-            const bool inside = __all_sync(0xffffffffu, i0 >= qi_lo && i0 + 15 <= qi_hi);
-            const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
+            const bool inside = __all_sync(0xffffffffu, i0 >= qi_lo && i0 + 31 <= qi_hi);
 #pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-                const float4 nl = *reinterpret_cast<const float4*>(vec + i);           // -lse2
-                const float4 nd = *reinterpret_cast<const float4*>(vec + 16 + i);      // -delta
-                const float2 x01 = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, make_float2(nl.x, nl.y));
-                const float2 x23 = fma2(make_float2(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])), sc2, make_float2(nl.z, nl.w));
+            for (int i = 0; i < 32; i += 4) {
+                const float4 nl = *reinterpret_cast<const float4*>(vec + i);
+                const float2 x01 = fma2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), sc2, make_float2(nl.x, nl.y));
+                const float2 x23 = fma2(make_float2(__uint_as_float(pr[i + 2]), __uint_as_float(pr[i + 3])), sc2, make_float2(nl.z, nl.w));
                 float2 p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
                 float2 p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
                 if (!inside) {
@@ -294,18 +297,39 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
                     p23.x = (qi + 2 >= qi_lo && qi + 2 <= qi_hi) ? p23.x : 0.f;
                     p23.y = (qi + 3 >= qi_lo && qi + 3 <= qi_hi) ? p23.y : 0.f;
                 }
-                const float2 d01 = mul2(p01, add2(make_float2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])), make_float2(nd.x, nd.y)));
-                const float2 d23 = mul2(p23, add2(make_float2(__uint_as_float(dr[i + 2]), __uint_as_float(dr[i + 3])), make_float2(nd.z, nd.w)));
-                pP[i / 2] = Elem<T>::pack(p01.x, p01.y);
-                pP[i / 2 + 1] = Elem<T>::pack(p23.x, p23.y);
-                pS[i / 2] = Elem<T>::pack(d01.x, d01.y);
-                pS[i / 2 + 1] = Elem<T>::pack(d23.x, d23.y);
+                pr[i] = __float_as_uint(p01.x); pr[i + 1] = __float_as_uint(p01.y);
+                pr[i + 2] = __float_as_uint(p23.x); pr[i + 3] = __float_as_uint(p23.y);
+                const uint32_t w0 = Elem<T>::pack(p01.x, p01.y), w1 = Elem<T>::pack(p23.x, p23.y);
+                if (i < 16) { lo8[i / 2] = w0; lo8[i / 2 + 1] = w1; } else { hi8[(i - 16) / 2] = w0; hi8[(i - 16) / 2 + 1] = w1; }
             }
-            tmem_st8(tmem + lane_base + COL_ST + hf * 64 + cg * 16, pP);
-            tmem_st8(tmem + lane_base + COL_DPT + hf * 64 + cg * 16, pS);
+            // each group of 16 queries (one K step of the accumulating MMAs) sits in 8 columns at a stride of 16
+            tmem_st8(tmem + lane_base + COL_ST + cg * 32, lo8);
+            tmem_st8(tmem + lane_base + COL_ST + cg * 32 + 16, hi8);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(E_P0 + hf));
+            mbar_arrive(bar(E_P0));
+            // phase B: dS^T = P^T (dP^T - delta), rounded, over dP^T's columns
+            ok = mbar_wait(bar(E_S1), s & 1, abort_flag, err, 28);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t dr[32];
+            tmem_ld32(tmem + lane_base + COL_DPT + cg * 32, dr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                const float4 nd = *reinterpret_cast<const float4*>(vec + 32 + i);
+                const float2 d01 = mul2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])),
+                                        add2(make_float2(__uint_as_float(dr[i]), __uint_as_float(dr[i + 1])), make_float2(nd.x, nd.y)));
+                const float2 d23 = mul2(make_float2(__uint_as_float(pr[i + 2]), __uint_as_float(pr[i + 3])),
+                                        add2(make_float2(__uint_as_float(dr[i + 2]), __uint_as_float(dr[i + 3])), make_float2(nd.z, nd.w)));
+                const uint32_t w0 = Elem<T>::pack(d01.x, d01.y), w1 = Elem<T>::pack(d23.x, d23.y);
+                if (i < 16) { lo8[i / 2] = w0; lo8[i / 2 + 1] = w1; } else { hi8[(i - 16) / 2] = w0; hi8[(i - 16) / 2 + 1] = w1; }
+            }
+            tmem_st8(tmem + lane_base + COL_DPT + cg * 32, lo8);
+            tmem_st8(tmem + lane_base + COL_DPT + cg * 32 + 16, hi8);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(E_P1));
         }
         if (ok) ok = mbar_wait(bar(E_ACC), 0, abort_flag, err, 26);
         if (ok) {
