@@ -199,7 +199,7 @@ int fa_fwd_kvcache(const fa_fwd_params* p) {
         if (p->rotary_dim <= 0 || p->rotary_dim > p->d || (p->rotary_dim % 2)) return fail(FA_ERR_BAD_SHAPE, "rotary_dim must be even and <= headdim");
         if (p->seqlen_ro <= 0) return fail(FA_ERR_BAD_SHAPE, "seqlen_ro must be positive");
     }
-    return run_forward(*p, false);
+    return run_forward(*p, true);
 }
 
 size_t fa_fwd_workspace_bytes(const fa_fwd_params* p) {

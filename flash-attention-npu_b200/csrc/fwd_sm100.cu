@@ -31,6 +31,12 @@ struct alignas(64) Sm100FwdArgs {
     int64_t lse_sb, lse_sh, lse_ss;
     const int32_t* cu_q;
     const int32_t* cu_k;
+    // KV-cache calls (two-query-tile kernel only): device-resident lengths, page table, cache row of a batch entry
+    const int32_t* seqused_k;
+    const int32_t* block_table;
+    const int32_t* cache_batch_idx;
+    int64_t bt_stride;
+    int page_size, s_new;
     int b, sq, sk, hq, hkv;
     float scale_log2;
     int causal, wl, wr;
@@ -362,6 +368,7 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     const int mblk = gridDim.x - 1 - blockIdx.x;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
+    if (a.seqused_k) sk = a.seqused_k[b] + a.s_new;         // cache call: the length lives on the device
     const int m0 = mblk * 256;
     if (m0 >= sq) return;
     if (g_fwd_sm100_error) return;
@@ -425,20 +432,30 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
 #pragma unroll
                 for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + L::kQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, h, qrow0 + 128, qb);
             }
+            // where key tile j lives: (row, outermost coordinate) of the K / V maps.  Dense and packed operands: row
+            // in the batch entry; cache: row in the cache entry of this batch; paged cache: row inside the page
+            // that the page table names (a tile never straddles pages: the page size is a multiple of 128)
+            const int32_t* btab = a.block_table ? a.block_table + (int64_t)b * a.bt_stride : nullptr;
+            const int kbatch = a.cu_q ? 0 : (a.cache_batch_idx ? a.cache_batch_idx[b] : b);
             bool ok = true;
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int st = j & 1, use = j >> 1;
-                const int krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128;
+                int krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128, kouter = kbatch;
+                if (btab) {
+                    const int pos = (t_lo + j) * 128;
+                    kouter = btab[pos / a.page_size];
+                    krow = pos % a.page_size;
+                }
                 if (use > 0) ok = mbar_wait(bar(C_KE0 + st), (use - 1) & 1, abort_flag, err, 1);
                 if (!ok) break;
                 mbar_expect_tx(bar(C_KF0 + st), L::kKV);
 #pragma unroll
-                for (int s = 0; s < NSUB; ++s) tma_load_4d(sK + st * L::kKV + s * L::kSub, &a.tk, bar(C_KF0 + st), s * 64, hk, krow, qb);
+                for (int s = 0; s < NSUB; ++s) tma_load_4d(sK + st * L::kKV + s * L::kSub, &a.tk, bar(C_KF0 + st), s * 64, hk, krow, kouter);
                 if (use > 0) ok = mbar_wait(bar(C_VE0 + st), (use - 1) & 1, abort_flag, err, 2);
                 if (!ok) break;
                 mbar_expect_tx(bar(C_VF0 + st), L::kKV);
 #pragma unroll
-                for (int s = 0; s < NSUB; ++s) tma_load_4d(sV + st * L::kKV + s * L::kSub, &a.tv, bar(C_VF0 + st), s * 64, hk, krow, qb);
+                for (int s = 0; s < NSUB; ++s) tma_load_4d(sV + st * L::kKV + s * L::kSub, &a.tv, bar(C_VF0 + st), s * 64, hk, krow, kouter);
             }
         }
     } else if (warp == 9) {
@@ -481,6 +498,18 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                 ok = mbar_wait(bar(C_PA), j & 1, abort_flag, err, 5);
                 if (ok) ok = mbar_wait(bar(C_VF0 + st), use & 1, abort_flag, err, 6);
                 if (!ok) break;
+                if (a.seqused_k && (t_lo + j) * 128 + 128 > sk) {
+                    // Rows of a cache past the sequence hold whatever was there before (possibly NaN patterns): their
+                    // probabilities are exact zeros, but 0 x NaN is NaN, so the V rows are cleared before the MMA.
+                    // A row is 128 bytes in every 64-column sub-tile whatever the swizzle.
+                    const int first = max(0, sk - (t_lo + j) * 128);
+#pragma unroll
+                    for (int sub = 0; sub < NSUB; ++sub)
+                        for (int idx = first * 8 + lane; idx < 128 * 8; idx += 32)      // 16-byte chunks of rows first .. 127
+                            *reinterpret_cast<uint4*>(sgen + L::oV + st * L::kKV + sub * L::kSub + idx * 16) = make_uint4(0, 0, 0, 0);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                }
                 tc_fence_after();
                 ok = issue_pv(0, st, j);
                 if (!ok) break;
@@ -1083,7 +1112,14 @@ void fwd_sm100_set_p_in_tmem(int v) { g_variant = v; }
 
 bool fwd_sm100_supported(const fa_fwd_params& p) {
     if (p.d != p.dv || (p.d != 64 && p.d != 128)) return false;
-    if (p.softcap > 0.f || p.alibi_slopes || p.block_table || p.seqused_k || p.cache_batch_idx) return false;
+    if (p.softcap > 0.f || p.alibi_slopes) return false;
+    const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
+    if (cache) {
+        // KV-cache calls (prefill against a cache): only the two-query-tile kernel reads lengths and pages on the device
+        if (g_variant != 2 || p.cu_seqlens_q || p.cu_seqlens_k || !p.seqused_k) return false;
+        if (p.block_table && (p.page_size <= 0 || p.page_size % 128)) return false;
+        if (p.sq < 64) return false;                      // short queries belong to the split-KV decode kernels
+    }
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
     if (p.kv_begin != 0 || p.kv_end > 0 || p.partials_only) return false;
     if (p.sq <= 0 || p.sk <= 0 || !(p.scale > 0.f)) return false;
@@ -1130,8 +1166,20 @@ int launch_fwd_sm100(const fa_fwd_params& p) {
     const int nb = packed ? 1 : p.b;
     auto bstride = [&](const fa_tensor& t, int64_t rows) { return packed || p.b == 1 ? rows * t.stride_s : t.stride_b; };
     if (int e = make_tile_map(&a.tq, p.dtype, p.q.ptr, p.d, p.hq, q_rows, nb, p.q.stride_h, p.q.stride_s, bstride(p.q, q_rows), 128)) return e;
-    if (int e = make_tile_map(&a.tk, p.dtype, p.k.ptr, p.d, p.hkv, k_rows, nb, p.k.stride_h, p.k.stride_s, bstride(p.k, k_rows), 128)) return e;
-    if (int e = make_tile_map(&a.tv, p.dtype, p.v.ptr, p.d, p.hkv, k_rows, nb, p.v.stride_h, p.v.stride_s, bstride(p.v, k_rows), 128)) return e;
+    const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
+    if (cache) {
+        // rows of one page / cache entry; the number of pages or cache entries is not passed down, so the outermost
+        // extent is only an upper limit (the page table and cache_batch_idx are valid by contract)
+        const int64_t rows = p.block_table ? p.page_size : p.sk;
+        const int outer = 1 << 24;
+        if (int e = make_tile_map(&a.tk, p.dtype, p.k.ptr, p.d, p.hkv, rows, outer, p.k.stride_h, p.k.stride_s, p.k.stride_b, 128)) return e;
+        if (int e = make_tile_map(&a.tv, p.dtype, p.v.ptr, p.d, p.hkv, rows, outer, p.v.stride_h, p.v.stride_s, p.v.stride_b, 128)) return e;
+    } else {
+        if (int e = make_tile_map(&a.tk, p.dtype, p.k.ptr, p.d, p.hkv, k_rows, nb, p.k.stride_h, p.k.stride_s, bstride(p.k, k_rows), 128)) return e;
+        if (int e = make_tile_map(&a.tv, p.dtype, p.v.ptr, p.d, p.hkv, k_rows, nb, p.v.stride_h, p.v.stride_s, bstride(p.v, k_rows), 128)) return e;
+    }
+    a.seqused_k = p.seqused_k; a.block_table = p.block_table; a.cache_batch_idx = p.cache_batch_idx;
+    a.bt_stride = p.block_table_stride; a.page_size = p.page_size; a.s_new = p.s_new;
     a.o = p.o.ptr; a.lse = p.lse;
     a.o_sb = p.o.stride_b; a.o_ss = p.o.stride_s; a.o_sh = p.o.stride_h;
     a.lse_sb = p.lse_stride_b; a.lse_sh = p.lse_stride_h; a.lse_ss = p.lse_stride_s;

@@ -264,3 +264,64 @@ def test_scheduler_metadata_matches_host_computation():
                                    scheduler_metadata=meta.cuda().view(torch.uint8))
     b_ = m3.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=lens.cuda(), causal=True)
     assert torch.equal(a, b_)
+
+
+@pytest.mark.parametrize("paged,page", [(True, 128), (True, 256), (False, 0)])
+@pytest.mark.parametrize("append", [False, True])
+def test_prefill_against_cache_uses_tcgen05(paged, page, append):
+    """A chunk of queries against a KV cache (chunked prefill): ragged device-resident lengths, GQA, optional
+    in-place append of the chunk's own keys, cache rows past the lengths filled with NaN (they must not leak
+    into the output); the tcgen05 kernel serves the call."""
+    import flash_attn_npu as m
+    import fa_b200_capi as capi
+    g = torch.Generator().manual_seed(321)
+    dt, b, h, hkv, sq, d = torch.bfloat16, 3, 8, 2, 200, 128
+    lens = [700, 1, 1337]
+    cap = 2048
+    q = torch.randn(b, sq, h, d, generator=g).to(dt)
+    kn = torch.randn(b, sq, hkv, d, generator=g).to(dt) if append else None
+    vn = torch.randn(b, sq, hkv, d, generator=g).to(dt) if append else None
+    if paged:
+        nb = cap // page
+        kc = torch.randn(nb * b + 3, page, hkv, d, generator=g).to(dt)
+        vc = torch.randn(nb * b + 3, page, hkv, d, generator=g).to(dt)
+        table = torch.randperm(nb * b + 3, generator=g)[: nb * b].int().reshape(b, nb)
+        for i, L in enumerate(lens):                         # poison everything past the (appended) length
+            end = L + (sq if append else 0)
+            for j in range(nb):
+                lo = max(0, end - j * page)
+                if lo < page:
+                    kc[table[i, j], lo:] = float("nan")
+                    vc[table[i, j], lo:] = float("nan")
+    else:
+        kc = torch.randn(b, cap, hkv, d, generator=g).to(dt)
+        vc = torch.randn(b, cap, hkv, d, generator=g).to(dt)
+        table = None
+        for i, L in enumerate(lens):
+            end = L + (sq if append else 0)
+            kc[i, end:] = float("nan")
+            vc[i, end:] = float("nan")
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    scale = d ** -0.5
+    # a dense cache read without append also goes through cache_batch_idx (entry i of the batch uses cache row idx[i])
+    idx = None
+    if not paged and not append:
+        idx = torch.tensor([2, 0, 1], dtype=torch.int32)
+        inv = torch.argsort(idx.long())
+        kc, vc = kc[inv].contiguous(), vc[inv].contiguous()     # row idx[i] of the cache now holds entry i
+    ref_k, ref_v = torch.nan_to_num(kc.clone()), torch.nan_to_num(vc.clone())
+    lp_o, _ = orc.kvcache_fwd(q, ref_k.clone(), ref_v.clone(), lens_t, scale, k_new=kn, v_new=vn, block_table=table,
+                              cache_batch_idx=idx, causal=True)
+    f_o, f_l = orc.kvcache_fwd(q.float(), ref_k.float(), ref_v.float(), lens_t, scale, k_new=None if kn is None else kn.float(),
+                               v_new=None if vn is None else vn.float(), block_table=table, cache_batch_idx=idx, causal=True)
+    out, lse = m.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), None if kn is None else kn.cuda(),
+                                         None if vn is None else vn.cuda(), cache_seqlens=lens_t.cuda(),
+                                         cache_batch_idx=None if idx is None else idx.cuda(),
+                                         block_table=None if table is None else table.cuda(), softmax_scale=scale,
+                                         causal=True, return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert capi.last_kernel() == "sm100_tcgen05_2q"
+    assert capi.lib.fa_debug_get(2) == 0
+    assert torch.isfinite(out).all()
+    assert_within("out", out.cpu(), lp_o, f_o)
+    assert_lse(lse, f_l)
