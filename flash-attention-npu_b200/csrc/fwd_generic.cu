@@ -426,22 +426,39 @@ template <> __device__ __forceinline__ void store_out<float>(float* d, float v) 
 template <> __device__ __forceinline__ void store_out<__half>(__half* d, float v) { *d = __float2half_rn(v); }
 template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* d, float v) { *d = __float2bfloat16_rn(v); }
 
+// One warp per output row.  The weights exp(lse_s - lse) are computed once per row (lanes stride over the splits) and
+// kept in shared memory; the partial outputs are then read with 16-byte loads, four splits in flight per lane.
+constexpr int kCombineWarps = 4, kCombineMaxSplits = 512;
+
 template <typename OutT>
-__global__ void combine_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part,
-                               int64_t o_split_stride, int64_t o_row_stride, int64_t lse_split_stride,
-                               OutT* o, float* lse, int nsplit, int64_t rows, int dv,
-                               // output addressing: row = tok * hq + head
-                               int hq, int sq_dense, int64_t o_sb, int64_t o_ss, int64_t o_sh,
-                               int64_t l_sb, int64_t l_sh, int64_t l_ss, int keep_minus_inf) {
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+__global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(
+    const float* __restrict__ o_part, const float* __restrict__ lse_part, int64_t o_split_stride, int64_t o_row_stride,
+    int64_t lse_split_stride, OutT* o, float* lse, int nsplit, int64_t rows, int dv,
+    // output addressing: row = tok * hq + head
+    int hq, int sq_dense, int64_t o_sb, int64_t o_ss, int64_t o_sh, int64_t l_sb, int64_t l_sh, int64_t l_ss,
+    int keep_minus_inf) {
+    __shared__ float s_w[kCombineWarps][kCombineMaxSplits];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kCombineWarps + wid;
     if (row >= rows) return;
-    const int lane = threadIdx.x & 31;
+    float* w = s_w[wid];
     float m = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, lse_part[s * lse_split_stride + row]);
+    for (int s = lane; s < nsplit; s += 32) {
+        const float ls = lse_part[s * lse_split_stride + row];
+        w[s] = ls;
+        m = fmaxf(m, ls);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
     const float ms = m == -INFINITY ? 0.f : m;
     float tot = 0.f;
-    for (int s = 0; s < nsplit; ++s) tot += expf(lse_part[s * lse_split_stride + row] - ms);
+    for (int s = lane; s < nsplit; s += 32) tot += expf(w[s] - ms);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, d);
     const float l = tot > 0.f ? ms + logf(tot) : -INFINITY;
+    // a split that saw no key (lse = -inf) gets weight 0 and its O slot is never read (it may hold anything)
+    for (int s = lane; s < nsplit; s += 32) w[s] = w[s] == -INFINITY ? 0.f : expf(w[s] - l);
+    __syncwarp();
     const int64_t tok = row / hq;
     const int head = (int)(row % hq);
     int64_t ooff, loff;
@@ -453,14 +470,42 @@ __global__ void combine_kernel(const float* __restrict__ o_part, const float* __
         ooff = tok * o_ss + head * o_sh;
         loff = head * l_sh + tok * l_ss;
     }
-    for (int c = lane; c < dv; c += 32) {
-        float acc = 0.f;
-        for (int s = 0; s < nsplit; ++s) {
-            const float ls = lse_part[s * lse_split_stride + row];
-            if (ls == -INFINITY) continue;                   // a split that saw no key: its O slot is not read
-            acc += expf(ls - l) * o_part[s * o_split_stride + row * o_row_stride + c];
+    const float* src = o_part + row * o_row_stride;
+    const bool vec = (dv % 4 == 0) && (o_row_stride % 4 == 0) && (o_split_stride % 4 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(o_part) & 15) == 0);
+    if (vec) {
+        for (int c = lane * 4; c < dv; c += 128) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            int s = 0;
+            for (; s + 4 <= nsplit; s += 4) {
+                float4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    v[u] = w[s + u] != 0.f ? *reinterpret_cast<const float4*>(src + (s + u) * o_split_stride + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    acc.x += w[s + u] * v[u].x; acc.y += w[s + u] * v[u].y; acc.z += w[s + u] * v[u].z; acc.w += w[s + u] * v[u].w;
+                }
+            }
+            for (; s < nsplit; ++s) {
+                if (w[s] == 0.f) continue;
+                const float4 v = *reinterpret_cast<const float4*>(src + s * o_split_stride + c);
+                acc.x += w[s] * v.x; acc.y += w[s] * v.y; acc.z += w[s] * v.z; acc.w += w[s] * v.w;
+            }
+            store_out<OutT>(o + ooff + c, acc.x);
+            store_out<OutT>(o + ooff + c + 1, acc.y);
+            store_out<OutT>(o + ooff + c + 2, acc.z);
+            store_out<OutT>(o + ooff + c + 3, acc.w);
         }
-        store_out<OutT>(o + ooff + c, acc);
+    } else {
+        for (int c = lane; c < dv; c += 32) {
+            float acc = 0.f;
+            for (int s = 0; s < nsplit; ++s) {
+                if (w[s] == 0.f) continue;
+                acc += w[s] * src[s * o_split_stride + c];
+            }
+            store_out<OutT>(o + ooff + c, acc);
+        }
     }
     if (lane == 0 && lse) lse[loff] = (tot > 0.f || keep_minus_inf) ? l : INFINITY;
 }
@@ -470,8 +515,9 @@ int launch_fwd_combine(const fa_fwd_params& p, int nsplit, const float* o_part, 
     const int64_t toks = p.cu_seqlens_q ? (int64_t)p.total_q : (int64_t)p.b * p.sq;
     const int64_t rows = toks * p.hq;
     if (rows == 0) return FA_OK;
+    if (nsplit > kCombineMaxSplits) return fail(FA_ERR_BAD_SHAPE, "at most %d splits can be combined", kCombineMaxSplits);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
-    const int wpb = 4;
+    const int wpb = kCombineWarps;
     dim3 grid((unsigned)((rows + wpb - 1) / wpb));
     const int sq_dense = p.cu_seqlens_q ? 0 : p.sq;
     if (to_partial) {
@@ -493,7 +539,7 @@ int launch_fwd_combine(const fa_fwd_params& p, int nsplit, const float* o_part, 
 // public combine entry (flat rows)
 template <typename OutT>
 static void launch_flat_combine(const fa_combine_params& c, cudaStream_t st, int keep = 0) {
-    const int wpb = 4;
+    const int wpb = kCombineWarps;
     dim3 grid((unsigned)((c.rows + wpb - 1) / wpb));
     combine_kernel<OutT><<<grid, wpb * 32, 0, st>>>(c.o_partial, c.lse_partial, c.o_split_stride, c.o_row_stride, c.lse_split_stride,
                                                    reinterpret_cast<OutT*>(c.o), c.lse, c.nsplit, c.rows, c.dv,
@@ -504,6 +550,7 @@ static void launch_flat_combine(const fa_combine_params& c, cudaStream_t st, int
 int combine_flat_keep(const fa_combine_params& c) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(c.stream);
     if (c.rows == 0) return FA_OK;
+    if (c.nsplit > kCombineMaxSplits) return fail(FA_ERR_BAD_SHAPE, "at most %d splits can be combined", kCombineMaxSplits);
     launch_flat_combine<float>(c, st, 1);
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "combine launch");
@@ -512,6 +559,7 @@ int combine_flat_keep(const fa_combine_params& c) {
 int combine_flat(const fa_combine_params& c) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(c.stream);
     if (c.rows == 0) return FA_OK;
+    if (c.nsplit > kCombineMaxSplits) return fail(FA_ERR_BAD_SHAPE, "at most %d splits can be combined", kCombineMaxSplits);
     if (c.out_dtype == FA_F16) launch_flat_combine<__half>(c, st);
     else if (c.out_dtype == FA_BF16) launch_flat_combine<__nv_bfloat16>(c, st);
     else launch_flat_combine<float>(c, st);
