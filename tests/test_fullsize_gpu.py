@@ -111,8 +111,6 @@ def test_config4_paged_decode_full_size():
         assert_within("out", out[i:i + 1].cpu(), lp_o, f_o)
         assert_lse(lse[i:i + 1].cpu(), f_l)
     # property: split equals unsplit
-    one = fa.flash_attn_with_kvcache(q.cuda(), kc, vc, cache_seqlens=(lens + 1).cuda(), block_table=table.cuda(),
-                                     causal=True, num_splits=1)
     q_rot = torch.stack([orc.apply_rotary(q[i], cos, sin, torch.tensor([int(lens[i])]), False) for i in range(b)])
     many = fa.flash_attn_with_kvcache(q_rot.cuda(), kc, vc, cache_seqlens=(lens + 1).cuda(), block_table=table.cuda(),
                                       causal=True, num_splits=0)
