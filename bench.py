@@ -153,6 +153,9 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode side measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sharded-decode", action="store_true",
+                    help="with 2 or more GPUs: also time the key-range sharded decode, NCCL all-gather + combine "
+                         "against the one kernel that exchanges the partials over peer memory")
     ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "decode", "mla"],
                     help="run two calls of one kernel on a small case (for a profiler capture) and exit")
     args = ap.parse_args()
@@ -291,6 +294,9 @@ def main():
     h2d = sum(t.numel() * 2 for t in host)
     d2h = sum(t.numel() * 2 for t in (out_h, gq_h, gk_h, gv_h))
 
+    sharded = None
+    if world > 1 and args.sharded_decode:
+        sharded = kv_sharded_decode_side_measurement(dev, rank, world)
     decode = varlen = mla = None
     if rank == 0 and not args.no_decode:
         # side measurements of the other single-GPU configurations; none may take the headline down
@@ -353,6 +359,8 @@ def main():
         line["varlen_fwd"] = varlen
     if mla is not None:
         line["mla_decode"] = mla
+    if sharded is not None:
+        line["kv_sharded_decode"] = sharded
     if not args.no_cpu and world == 1:
         v_cpu, dt, cores, sample = cpu_oracle_sample(H, 2)      # 10-30 s of host work
         line["cpu_baseline"] = {"value": v_cpu, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
@@ -415,6 +423,61 @@ def paged_decode_side_measurement(dev, iters=10):
             "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": bytes_, "kernel": kern,
             "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8000": gbs / 8000.0,
             "cache_gb": pool * page * hkv * d * 2 * 2 / 1e9}
+
+
+def kv_sharded_decode_side_measurement(dev, rank, world, iters=20):
+    """Long-context decode with the key range of every sequence cut over the ranks (B8 Hq32 Hkv8 D128 page 256,
+    131072 keys a sequence; every rank holds only the cache blocks of its own range).  Times, max over ranks:
+    the decode kernels alone (fp32 partials), the call with an NCCL all-gather of the partials + combine, and the
+    call with the kernel that exchanges them over peer memory and combines."""
+    import fa_b200_sharding as sh
+    from flash_attn_npu import flash_attn_npu as ext
+    g = torch.Generator().manual_seed(7)
+    b, hq, hkv, d, page, length = 8, 32, 8, 128, 256, 131072
+    lo, hi = sh.kv_shard_range(length, rank, world, page)
+    own = (min(hi, length) - lo) // page
+    table = torch.zeros(b, length // page, dtype=torch.int32)
+    perm = torch.randperm(b * own, generator=g).int().view(b, own)
+    table[:, lo // page:lo // page + own] = perm
+    kc = torch.randn(b * own, page, hkv, d, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn(b * own, page, hkv, d, device=dev, dtype=torch.bfloat16)
+    q = torch.randn(b, 1, hq, d, generator=g).bfloat16().to(dev)
+    lens = torch.full((b,), length, dtype=torch.int32, device=dev)
+    table = table.to(dev)
+    ex = sh.PeerExchange(b * hq, d, dev)
+    po = torch.empty(b * hq, d, dtype=torch.float32, device=dev)
+    pl = torch.empty(b * hq, dtype=torch.float32, device=dev)
+
+    def partial_only():
+        ext.kvcache_forward(q, kc, vc, None, None, lens, None, None, None, table, None, None, d ** -0.5, False, -1, -1,
+                            0.0, False, 0, kv_range=(lo, hi), partials=(po, pl))
+
+    def with_nccl():
+        return sh.sharded_kvcache_decode(q, kc, vc, lens, table, d ** -0.5, length, page)
+
+    def with_peers():
+        return sh.sharded_kvcache_decode(q, kc, vc, lens, table, d ** -0.5, length, page, exchange=ex)
+
+    a, _ = with_nccl()
+    c, _ = with_peers()
+    ex.check()
+    same = bool(torch.equal(a, c))
+    res = {}
+    for name, fn in (("decode_only_ms", partial_only), ("nccl_allgather_combine_ms", with_nccl),
+                     ("peer_exchange_combine_ms", with_peers)):
+        dist.barrier()
+        t = torch.tensor([_time_calls(fn, iters)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res[name] = t.item()
+    ex.check()
+    ex.close()
+    bytes_ = b * own * page * hkv * d * 2 * 2
+    res.update({"workload": f"decode bf16 B8 Sq1 Hq32 Hkv8 D128 page256 L131072, keys cut over {world} ranks",
+                "identical_results": same, "cache_gb_per_rank": bytes_ / 1e9,
+                "decode_gbs_per_rank": bytes_ / (res["decode_only_ms"] * 1e-3) / 1e9,
+                "exchange_cost_us": {"nccl": 1e3 * (res["nccl_allgather_combine_ms"] - res["decode_only_ms"]),
+                                     "peer_kernel": 1e3 * (res["peer_exchange_combine_ms"] - res["decode_only_ms"])}})
+    return res
 
 
 def profile_case(name):

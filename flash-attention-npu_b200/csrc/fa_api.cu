@@ -271,6 +271,16 @@ int fa_combine(const fa_combine_params* c) {
     return fa::combine_flat(*c);
 }
 
+int fa_peer_combine(const fa_peer_combine_params* c) {
+    if (!c) return fail(FA_ERR_NULL, "params is null");
+    if (c->out_dtype < 0 || c->out_dtype > 2) return fail(FA_ERR_BAD_DTYPE, "out_dtype must be f16, bf16 or fp32");
+    return fa::peer_combine(*c);
+}
+int fa_peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle) { return fa::peer_buffer_create(bytes, ptr, handle); }
+int fa_peer_buffer_open(const unsigned char* handle, void** ptr) { return fa::peer_buffer_open(handle, ptr); }
+int fa_peer_buffer_close(void* ptr) { return ptr ? fa::cuda_ok(cudaIpcCloseMemHandle(ptr), "peer buffer close") : FA_OK; }
+int fa_peer_buffer_destroy(void* ptr) { return ptr ? fa::cuda_ok(cudaFree(ptr), "peer buffer free") : FA_OK; }
+
 const char* fa_last_error(void) { return g_err; }
 const char* fa_version(void) { return "fa_b200 0.1.0 (sm_100a)"; }
 const char* fa_last_kernel(void) { return g_kernel; }

@@ -47,6 +47,10 @@ int launch_fwd_combine(const fa_fwd_params& p, int nsplit, const float* o_part, 
                        int to_partial);
 int combine_flat(const fa_combine_params& c);
 int combine_flat_keep(const fa_combine_params& c);
+// exchange of partials over peer memory fused with the combine (peer_combine.cu)
+int peer_combine(const fa_peer_combine_params& c);
+int peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle);
+int peer_buffer_open(const unsigned char* handle, void** ptr);
 int launch_bwd_generic(const fa_bwd_params& p);
 // 0 = automatic kernel choice, 1 = generic kernels only (fa_set_kernel_policy)
 int kernel_policy();

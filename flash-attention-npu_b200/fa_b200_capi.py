@@ -62,6 +62,22 @@ class CombineParams(C.Structure):
     ]
 
 
+MAX_PEERS = 16
+PEER_HANDLE_BYTES = 64
+
+
+class PeerCombineParams(C.Structure):
+    _fields_ = [
+        ("rank", C.c_int32), ("world", C.c_int32),
+        ("peers", C.c_void_p * MAX_PEERS),
+        ("slot_offset", C.c_size_t), ("lse_offset", C.c_size_t), ("flag_offset", C.c_size_t),
+        ("epoch", C.c_uint32), ("timeout_ms", C.c_uint32),
+        ("rows", C.c_int64), ("dv", C.c_int32), ("out_dtype", C.c_int32),
+        ("o", C.c_void_p), ("o_stride", C.c_int64), ("lse", C.c_void_p), ("status", C.c_void_p),
+        ("stream", C.c_void_p),
+    ]
+
+
 class MlaParams(C.Structure):
     _fields_ = [
         ("q_nope", C.c_void_p), ("q_rope", C.c_void_p),
@@ -101,6 +117,11 @@ EXPORTS = {
     "fa_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(BwdParams)]),
     "fa_combine": (C.c_int, [C.POINTER(CombineParams)]),
     "fa_mla_decode": (C.c_int, [C.POINTER(MlaParams)]),
+    "fa_peer_combine": (C.c_int, [C.POINTER(PeerCombineParams)]),
+    "fa_peer_buffer_create": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
+    "fa_peer_buffer_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "fa_peer_buffer_close": (C.c_int, [C.c_void_p]),
+    "fa_peer_buffer_destroy": (C.c_int, [C.c_void_p]),
     "fa_mla_workspace_bytes": (C.c_size_t, [C.POINTER(MlaParams)]),
     "fa_mla_num_splits": (C.c_int, [C.POINTER(MlaParams)]),
     "fa_scheduler_metadata": (C.c_int, [C.POINTER(SchedParams)]),

@@ -170,6 +170,47 @@ typedef struct {
 int fa_combine(const fa_combine_params* p);
 
 /* ------------------------------------------------------------------------
+ * KV-sharded decode over the GPUs of one box: exchange of the partial (O, LSE)
+ * fused with their combine.  No counterpart in the reference (single device;
+ * the combine itself is CombineScale.hpp:76-357).  Every rank owns an exchange
+ * buffer which the other ranks map through CUDA IPC; fa_fwd_kvcache /
+ * fa_mla_decode with partials_only leave the rank's partials in a slot of it;
+ * fa_peer_combine then signals the peers, waits (bounded) for their signals and
+ * combines all ranks' partials with loads over NVLink, without a library
+ * collective.  All ranks make the same sequence of calls with epoch = 1, 2, ...
+ * and alternate between two slots (slot = epoch & 1).
+ * ---------------------------------------------------------------------- */
+#define FA_MAX_PEERS 16
+#define FA_PEER_HANDLE_BYTES 64
+/* cudaMalloc + clear + export; `handle` is sent to the other processes */
+int fa_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[FA_PEER_HANDLE_BYTES]);
+/* maps another process's buffer into this one (peer access is enabled as needed) */
+int fa_peer_buffer_open(const unsigned char handle[FA_PEER_HANDLE_BYTES], void** ptr);
+int fa_peer_buffer_close(void* ptr);     /* of fa_peer_buffer_open   */
+int fa_peer_buffer_destroy(void* ptr);   /* of fa_peer_buffer_create */
+
+typedef struct {
+    int32_t  rank, world;
+    void*    peers[FA_MAX_PEERS];   /* buffer of every rank as mapped here; peers[rank] = own */
+    size_t   slot_offset;           /* bytes from a buffer's start to this call's (rows, dv) fp32 partial O */
+    size_t   lse_offset;            /* ... to its (rows) fp32 partial LSE                      */
+    size_t   flag_offset;           /* ... to its `world` uint32 flags (zero before epoch 1)   */
+    uint32_t epoch;                 /* call counter, the same on all ranks                     */
+    uint32_t timeout_ms;            /* limit of the wait for the peers' signals; 0 = 1000      */
+    int64_t  rows;
+    int32_t  dv;                    /* multiple of 4                                           */
+    int32_t  out_dtype;             /* fa_dtype, or 2 = fp32                                   */
+    void*    o;                     /* (rows, dv) in out_dtype, row stride o_stride            */
+    int64_t  o_stride;
+    float*   lse;                   /* (rows) or null                                          */
+    int32_t* status;                /* device int, stays 0 on success; 1 + r if rank r's signal
+                                     * did not arrive in time (nothing is written to o then)   */
+    void*    stream;
+} fa_peer_combine_params;
+
+int fa_peer_combine(const fa_peer_combine_params* p);
+
+/* ------------------------------------------------------------------------
  * int8 latent (MLA) paged decode.  No counterpart in the reference (it has no
  * quantised path).  K_j = [scale_j * latent_j (512) | rope_j (64)], V_j = the
  * dequantised latent; one shared KV head, seqlen_q = 1.

@@ -1,5 +1,6 @@
-"""Key-range sharded decode over 2 GPUs (NCCL all-gather of (O, LSE) partials + combine) against the
-single-GPU result.  Skipped when fewer than two GPUs are visible."""
+"""Key-range sharded decode over 2 GPUs against the single-GPU result: with an NCCL all-gather of the (O, LSE)
+partials followed by a combine, and with the one kernel that exchanges them over peer memory and combines.
+Skipped when fewer than two GPUs are visible."""
 import os
 
 import pytest
@@ -51,6 +52,26 @@ def _worker(rank, world, port, tmp):
         mout, mlse2 = sh.sharded_mla_decode(*args, table.to(dev), lens_t, 576 ** -0.5, max(lens), page)
         assert (mout.float() - mfull.float()).abs().max().item() <= 2 ** -7
         assert (mlse2 - mlse).abs().max().item() < 1e-4
+        # the same two calls with the partials exchanged and combined by one kernel over peer memory; several
+        # calls so that both slots of the exchange buffers are reused
+        ex = sh.PeerExchange(b * h, d, dev)
+        mex = sh.PeerExchange(b * 128, 512, dev)
+        for it in range(5):
+            qi = (q.float() * (1.0 + 0.25 * it)).bfloat16()
+            ref_o, ref_l = sh.sharded_kvcache_decode(qi, kc, vc, lens_t, table.to(dev), d ** -0.5, max(lens), page)
+            o2, l2 = sh.sharded_kvcache_decode(qi, kc, vc, lens_t, table.to(dev), d ** -0.5, max(lens), page,
+                                               exchange=ex)
+            ex.check()
+            assert torch.equal(o2, ref_o), (o2.float() - ref_o.float()).abs().max().item()
+            assert (l2 - ref_l).abs().max().item() < 1e-6
+            m2, ml2 = sh.sharded_mla_decode(*args, table.to(dev), lens_t, 576 ** -0.5, max(lens), page, exchange=mex)
+            mex.check()
+            assert (m2.float() - mfull.float()).abs().max().item() <= 2 ** -7
+            assert (ml2 - mlse).abs().max().item() < 1e-4
+        import fa_b200_capi as capi
+        assert capi.last_kernel() == "peer_combine"
+        ex.close()
+        mex.close()
         torch.cuda.synchronize()
         dist.barrier()
         torch.save({"ok": True}, os.path.join(tmp, f"rank{rank}.pt"))
