@@ -430,6 +430,7 @@ def kv_sharded_decode_side_measurement(dev, rank, world, iters=20):
     131072 keys a sequence; every rank holds only the cache blocks of its own range).  Times, max over ranks:
     the decode kernels alone (fp32 partials), the call with an NCCL all-gather of the partials + combine, and the
     call with the kernel that exchanges them over peer memory and combines."""
+    import torch.distributed as dist
     import fa_b200_sharding as sh
     from flash_attn_npu import flash_attn_npu as ext
     g = torch.Generator().manual_seed(7)
