@@ -383,6 +383,15 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
     if (sk <= 0 || lo_first >= sk) { t_lo = 0; t_hi = 0; }
     const int ntiles = max(0, t_hi - t_lo);
+    // The first 128 rows of the block may end before the last key tile of the block (under a causal mask they end one
+    // tile earlier): they skip the tiles in which every one of their entries is masked.
+    int nt0 = ntiles;
+    if (has_b) {
+        int lo_a, hi_a;
+        window_bounds(m0 + 127, sq, sk, wl, wr, lo_a, hi_a);
+        const int n = min(ntiles, (hi_a < 0 ? 0 : hi_a / 128 + 1) - t_lo);
+        if (n >= 1) nt0 = n;
+    }
 
     T* obase = reinterpret_cast<T*>(a.o) + (a.cu_q ? 0 : (int64_t)b * a.o_sb) + (int64_t)(q_off + m0) * a.o_ss + (int64_t)h * a.o_sh;
     float* lbase = a.lse ? a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + (int64_t)(q_off + m0) * a.lse_ss : nullptr;
@@ -495,7 +504,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                 const int st = j & 1, use = j >> 1;
                 const bool more = j + 1 < ntiles;
                 const int st1 = (j + 1) & 1, use1 = (j + 1) >> 1;
-                ok = mbar_wait(bar(C_PA), j & 1, abort_flag, err, 5);
+                const bool a_on = j < nt0, a_more = j + 1 < nt0;          // the first 128 rows take part in tile j / j+1
+                if (a_on) ok = mbar_wait(bar(C_PA), j & 1, abort_flag, err, 5);
                 if (ok) ok = mbar_wait(bar(C_VF0 + st), use & 1, abort_flag, err, 6);
                 if (!ok) break;
                 if (a.seqused_k && (t_lo + j) * 128 + 128 > sk) {
@@ -511,15 +521,16 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                     __syncwarp();
                 }
                 tc_fence_after();
-                ok = issue_pv(0, st, j);
-                if (!ok) break;
+                if (a_on) {
+                    ok = issue_pv(0, st, j);
+                    if (!ok) break;
+                    if (!a_more) umma_commit_w(bar(C_OA));
+                }
                 if (more) {
                     ok = mbar_wait(bar(C_KF0 + st1), use1 & 1, abort_flag, err, 7);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_qk(0, st1);
-                } else {
-                    umma_commit_w(bar(C_OA));
+                    if (a_more) issue_qk(0, st1);
                 }
                 if (has_b) {
                     ok = mbar_wait(bar(C_PB), j & 1, abort_flag, err, 8);
@@ -557,7 +568,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
         float m_used = -INFINITY, l_run = 0.f;
         const float sc = a.scale_log2;
         bool ok = true;
-        for (int j = 0; j < ntiles && ok; ++j) {
+        const int nt_x = x == 0 ? nt0 : ntiles;
+        for (int j = 0; j < nt_x && ok; ++j) {
             const int n0 = (t_lo + j) * 128;
             ok = mbar_wait(bar(C_SA + x), j & 1, abort_flag, err, 9);
             if (!ok) break;
