@@ -153,6 +153,8 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode side measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--e2e-kv-heads", type=int, default=0,
+                    help="KV heads per chunk of the end-to-end leg's host pipeline (0 = the pipeline's default)")
     ap.add_argument("--sharded-decode", action="store_true",
                     help="with 2 or more GPUs: also time the key-range sharded decode, NCCL all-gather + combine "
                          "against the one kernel that exchanges the partials over peer memory")
@@ -272,10 +274,10 @@ def main():
     out_h, gq_h, gk_h, gv_h = (torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in (hq, hq, hk, hv))
 
     import fa_b200_host
-    pipe = fa_b200_host.HostPipeline(dev)
+    pipe = fa_b200_host.HostPipeline(dev, args.e2e_kv_heads)
 
     def e2e_step():
-        # pinned host operands in, pinned host results out: one batch entry per chunk on three streams
+        # pinned host operands in, pinned host results out: chunks of one batch entry x a head group on three streams
         pipe.fwd_bwd(hq, hk, hv, hdo, out_h, gq_h, gk_h, gv_h, causal=True, softmax_scale=SCALE)
 
     e2e_step()

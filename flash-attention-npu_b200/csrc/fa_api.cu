@@ -281,6 +281,15 @@ int fa_peer_buffer_open(const unsigned char* handle, void** ptr) { return fa::pe
 int fa_peer_buffer_close(void* ptr) { return ptr ? fa::cuda_ok(cudaIpcCloseMemHandle(ptr), "peer buffer close") : FA_OK; }
 int fa_peer_buffer_destroy(void* ptr) { return ptr ? fa::cuda_ok(cudaFree(ptr), "peer buffer free") : FA_OK; }
 
+int fa_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
+                     void* stream) {
+    if (!dst || !src) return fail(FA_ERR_NULL, "null pointer");
+    if (width_bytes == 0 || rows == 0) return FA_OK;
+    if (width_bytes > dst_pitch || width_bytes > src_pitch) return fail(FA_ERR_BAD_SHAPE, "row wider than its pitch");
+    return fa::cuda_ok(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault,
+                                         reinterpret_cast<cudaStream_t>(stream)), "pitched copy");
+}
+
 const char* fa_last_error(void) { return g_err; }
 const char* fa_version(void) { return "fa_b200 0.1.0 (sm_100a)"; }
 const char* fa_last_kernel(void) { return g_kernel; }

@@ -1106,6 +1106,14 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
                   int64_t stride_h, int64_t stride_s, int64_t stride_b, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    // The encoder is a driver call and wants a current context.  A thread that has made no runtime call yet (an
+    // autograd worker whose allocations all came from the framework's cache) has none: bind the device's primary
+    // context once per thread.
+    static thread_local bool context_bound = false;
+    if (!context_bound) {
+        cudaFree(nullptr);
+        context_bound = true;
+    }
     cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)batch};
     cuuint64_t strides[3] = {(cuuint64_t)stride_h * 2, (cuuint64_t)stride_s * 2, (cuuint64_t)stride_b * 2};
     cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
@@ -1113,6 +1121,12 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
     CUresult r = fn(map, dtype == FA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_ERROR_INVALID_CONTEXT) {            // the thread's device was switched since: bind again, once
+        cudaFree(nullptr);
+        r = fn(map, dtype == FA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+               const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return FA_OK;
 }

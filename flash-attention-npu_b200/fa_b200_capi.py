@@ -118,6 +118,7 @@ EXPORTS = {
     "fa_combine": (C.c_int, [C.POINTER(CombineParams)]),
     "fa_mla_decode": (C.c_int, [C.POINTER(MlaParams)]),
     "fa_peer_combine": (C.c_int, [C.POINTER(PeerCombineParams)]),
+    "fa_copy_2d_async": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p]),
     "fa_peer_buffer_create": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
     "fa_peer_buffer_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "fa_peer_buffer_close": (C.c_int, [C.c_void_p]),

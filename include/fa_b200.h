@@ -210,6 +210,12 @@ typedef struct {
 
 int fa_peer_combine(const fa_peer_combine_params* p);
 
+/* Pitched copy on a stream (cudaMemcpy2DAsync, direction from the pointers): moves a group of heads of a
+ * (batch, seqlen, heads, headdim) tensor between pinned host memory and the device without a staging copy.
+ * No counterpart in the reference (its operands are created on the device). */
+int fa_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                     size_t rows, void* stream);
+
 /* ------------------------------------------------------------------------
  * int8 latent (MLA) paged decode.  No counterpart in the reference (it has no
  * quantised path).  K_j = [scale_j * latent_j (512) | rope_j (64)], V_j = the

@@ -109,3 +109,40 @@ def test_packed_forward_backward_random(seed):
     _close(dq1, dq2, tag + " dq")
     _close(dk1, dk2, tag + " dk")
     _close(dv1, dv2, tag + " dv")
+
+
+@pytest.mark.parametrize("sq,sk,causal,wl,wr", [
+    (512, 512, True, -1, -1),        # the first 128 rows of every block end one key tile before the last 128
+    (512, 300, True, -1, -1),        # bottom-right aligned: rows 0..211 see no key, the first half of block 0 none at all
+    (300, 1000, True, -1, -1),       # more keys than queries: both halves start late
+    (384, 384, True, -1, -1),        # last block has one half only
+    (640, 640, False, 200, 0),       # window with the causal edge
+    (640, 900, False, 64, 100),      # window whose right edge lies between the two halves' last tiles
+    (257, 129, False, -1, 0),        # one row in the second half
+])
+def test_forward_tile_ranges_of_the_two_query_halves(sq, sk, causal, wl, wr):
+    """The tcgen05 forward gives the first 128 rows of a 256-row block their own last key tile; every boundary case of
+    that against the general kernel (bit patterns of -inf rows included: zero output, +inf LSE)."""
+    from flash_attn_npu import flash_attn_npu as ext
+    import fa_b200_capi as capi
+    g = torch.Generator(device="cuda").manual_seed(sq * 7 + sk)
+    b, h, hkv, d = 2, 4, 2, 128
+    q = torch.randn(b, sq, h, d, device="cuda", generator=g).bfloat16()
+    k = torch.randn(b, sk, hkv, d, device="cuda", generator=g).bfloat16()
+    v = torch.randn(b, sk, hkv, d, device="cuda", generator=g).bfloat16()
+
+    def call():
+        out, lse, _, _ = ext.fwd(q, k, v, None, None, 0.0, d ** -0.5, causal, wl, wr, 0.0, False, None)
+        return out, lse
+
+    (o1, l1), k1 = _run(0, call)
+    (o2, l2), k2 = _run(1, call)
+    assert k1.startswith("sm100_tcgen05") and k2 == "generic_mma", (k1, k2)
+    assert capi.lib.fa_debug_get(2) == 0
+    assert not torch.isnan(o1.float()).any()
+    _close(o1, o2, "out")
+    fin = torch.isfinite(l2)
+    assert torch.equal(torch.isfinite(l1), fin)
+    assert torch.equal(l1[~fin], l2[~fin])
+    if fin.any():
+        assert (l1[fin] - l2[fin]).abs().max().item() <= 1e-4 * max(1.0, l2[fin].abs().max().item())
