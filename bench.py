@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (N = 1 and per rank for N > 1, weak scaling): BASELINE configuration 2,
+Workload (N = 1 and per rank for N > 1, weak scaling): Benchmark configuration 2,
 flash_attn_func forward + backward in bf16, batch 4, seqlen 4096, 32 query heads,
 32 KV heads, headdim 128, causal, softmax_scale 1/sqrt(128); q/k/v/dout i.i.d. N(0,1)
 from a seed (synthetic).  One step = one forward + one backward over that batch.
@@ -375,7 +375,7 @@ def main():
 
 
 def paged_decode_side_measurement(dev, iters=10):
-    """BASELINE configuration 4 (paged decode, B128 Hq32 Hkv8 D128 page 256, lengths U[1024,32768], append +
+    """Benchmark configuration 4 (paged decode, B128 Hq32 Hkv8 D128 page 256, lengths U[1024,32768], append +
     rotary) timed with CUDA events; reports achieved HBM GB/s over the algorithmic bytes (K and V rows read
     once, 4096 B per cached token and KV head set, plus q / out / table / appended rows)."""
     import flash_attn_npu as fa
@@ -550,7 +550,7 @@ def _time_calls(call, iters, warm=3):
 
 
 def varlen_side_measurement(dev, iters=10):
-    """BASELINE configuration 3 (packed forward, 16 sequences with lengths U[256,8192], Hq32 Hkv8 D128,
+    """Benchmark configuration 3 (packed forward, 16 sequences with lengths U[256,8192], Hq32 Hkv8 D128,
     causal): forward TFLOP/s over the unmasked half of every sequence's score matrix."""
     import flash_attn_npu as fa
     import fa_b200_capi as capi
@@ -574,7 +574,7 @@ def varlen_side_measurement(dev, iters=10):
 
 
 def mla_side_measurement(dev, iters=10):
-    """BASELINE configuration 5 (latent-attention decode, B64 Sq1 Hq128 against one latent head: 512 int8 +
+    """Benchmark configuration 5 (latent-attention decode, B64 Sq1 Hq128 against one latent head: 512 int8 +
     fp32 scale + 64 bf16 positional values per cached token, page 256, lengths U[4096,131072]): achieved HBM
     GB/s over 644 B per cached token plus q / out / table."""
     import flash_attn_npu_3 as fa3

@@ -208,7 +208,7 @@ def sharded_kvcache_decode(q, k_cache, v_cache, cache_seqlens, block_table, soft
 
 def sharded_mla_decode(q_nope, q_rope, latent_i8, scales, rope, block_table, cache_seqlens, softmax_scale, max_len,
                        page_size, group=None, exchange=None):
-    """int8 latent decode with the key range sharded over the ranks of `group` (BASELINE configuration 5):
+    """int8 latent decode with the key range sharded over the ranks of `group` (benchmark configuration 5):
     partial (O, LSE) per rank, one all-gather, local combine.  Returns out (B,1,H,512) bf16, lse (B,H,1)."""
     from flash_attn_npu_3 import flash_attn_npu_3 as ext3
     rank, world = dist.get_rank(group), dist.get_world_size(group)
