@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (N = 1 and per rank for N > 1, weak scaling): Benchmark configuration 2,
+Workload (N = 1 and per rank for N > 1, weak scaling): benchmark configuration 2,
 flash_attn_func forward + backward in bf16, batch 4, seqlen 4096, 32 query heads,
 32 KV heads, headdim 128, causal, softmax_scale 1/sqrt(128); q/k/v/dout i.i.d. N(0,1)
 from a seed (synthetic).  One step = one forward + one backward over that batch.
