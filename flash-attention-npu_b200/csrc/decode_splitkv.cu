@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(128) decode_splitkv_kernel(const DecodeArgs a)
     const int G = p.hq / p.hkv;
     int q_off = 0, sq = p.sq, sk = p.sk;
     if (p.cu_seqlens_q) { q_off = p.cu_seqlens_q[b]; sq = p.cu_seqlens_q[b + 1] - q_off; }
-    if (p.seqused_k) sk = p.seqused_k[b] + p.s_new;
+    if (p.seqused_k) sk = cache_len(p, b);
     const int kb = p.cache_batch_idx ? p.cache_batch_idx[b] : b;
     const int rows_total = sq * G;
     if (rows_total <= 0) return;
@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(128) decode_tma_kernel(const __grid_constant__
     const int G = p.hq / p.hkv;
     int q_off = 0, sq = p.sq, sk = p.sk;
     if (p.cu_seqlens_q) { q_off = p.cu_seqlens_q[b]; sq = p.cu_seqlens_q[b + 1] - q_off; }
-    if (p.seqused_k) sk = p.seqused_k[b] + p.s_new;
+    if (p.seqused_k) sk = cache_len(p, b);
     const int kb = p.cache_batch_idx ? p.cache_batch_idx[b] : b;
     const int rows_total = sq * G;
     if (rows_total <= 0) return;

@@ -232,9 +232,14 @@ static int check_bwd(const fa_bwd_params& p) {
 static int run_backward(const fa_bwd_params& pin) {
     fa_bwd_params p = pin;
     if (p.b == 0) return FA_OK;
-    // window normalisation of the reference's backward host code (fag_general_host.cpp:81-92)
+    // The forward's rule first (flash_api.cpp:684-704: a side that reaches the key length is unbounded), because
+    // for seqlen_q > seqlen_k it changes the mask and the saved LSE was computed under that mask; then the rule of
+    // the reference's backward host code (fag_general_host.cpp:81-92, flash_api.cpp:1155-1162), which never
+    // changes the mask.
+    if (p.sk > 0 && p.window_left >= p.sk) p.window_left = -1;
+    if (p.sk > 0 && p.window_right >= p.sk) p.window_right = -1;
     if (p.window_left >= p.sk - 1) p.window_left = -1;
-    if (p.window_right >= p.sq - 1 && !p.cu_seqlens_q) p.window_right = -1;
+    if (p.window_right >= p.sq - 1) p.window_right = -1;
     mark_kernel(reinterpret_cast<cudaStream_t>(p.stream));
     const bool fast = g_policy == 0 && bwd_sm100_supported(p);
     const size_t need = fast ? bwd_sm100_workspace(p) : bwd_generic_workspace(p);

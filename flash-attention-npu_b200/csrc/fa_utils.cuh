@@ -100,6 +100,14 @@ struct SeqInfo {
     int kb;         // batch index into the KV tensors (cache_batch_idx applied)
 };
 
+// Length of sequence b of a KV-cache call, read on the device.  A stale or oversized entry is truncated to what
+// the cache row (or the page-table row) can hold, so that no kernel indexes past the table or the cache.
+__device__ __forceinline__ int cache_len(const fa_fwd_params& p, int b) {
+    const long long cap = p.block_table ? (long long)p.block_table_stride * p.page_size : (long long)p.sk;
+    const long long len = (long long)p.seqused_k[b] + p.s_new;
+    return (int)max(0LL, min(len, cap));
+}
+
 // Visible key range of query position i (bottom-right aligned): [lo, hi] inclusive.
 __device__ __forceinline__ void window_bounds(int i, int sq, int sk, int wl, int wr, int& lo, int& hi) {
     const int diag = i + sk - sq;

@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(128) fwd_generic_kernel(const FwdArgs a) {
     int q_off = 0, sq = p.sq, k_off = 0, sk = p.sk;
     if (p.cu_seqlens_q) { q_off = p.cu_seqlens_q[b]; sq = p.cu_seqlens_q[b + 1] - q_off; }
     if (p.cu_seqlens_k) { k_off = p.cu_seqlens_k[b]; sk = p.cu_seqlens_k[b + 1] - k_off; }
-    if (p.seqused_k) sk = p.seqused_k[b] + p.s_new;
+    if (p.seqused_k) sk = cache_len(p, b);
     const int kb = p.cache_batch_idx ? p.cache_batch_idx[b] : b;
 
     const int rows_total = a.pack ? sq * G : sq;
@@ -374,6 +374,9 @@ __global__ void append_rotary_kernel(const fa_fwd_params p, T* q_rot, int rotate
         if (!p.k_new.ptr) return;
         const int i = row / p.hkv, h = row % p.hkv;
         const int pos = L + i;
+        // a length that points outside the cache (or past the page-table row) appends nothing
+        if (pos < 0 || pos >= p.sk) return;
+        if (p.block_table && pos / p.page_size >= p.block_table_stride) return;
         int64_t koff, voff;
         if (p.block_table) {
             const int blk = p.block_table[(int64_t)b * p.block_table_stride + pos / p.page_size];
@@ -389,7 +392,7 @@ __global__ void append_rotary_kernel(const fa_fwd_params p, T* q_rot, int rotate
         const T* vsrc = reinterpret_cast<const T*>(p.v_new.ptr) + (int64_t)b * p.v_new.stride_b + (int64_t)i * p.v_new.stride_s + (int64_t)h * p.v_new.stride_h;
         T* kdst = reinterpret_cast<T*>(p.k.ptr) + koff;
         T* vdst = reinterpret_cast<T*>(p.v.ptr) + voff;
-        const int cpos = min(pos, p.seqlen_ro - 1);
+        const int cpos = max(0, min(pos, p.seqlen_ro - 1));
         for (int e = threadIdx.x; e < p.d; e += blockDim.x)
             kdst[e] = rd ? rotate_elem<T>(ksrc, e, rd, p.rotary_interleaved, cosb + (int64_t)cpos * (rd / 2), sinb + (int64_t)cpos * (rd / 2)) : ksrc[e];
         for (int e = threadIdx.x; e < p.dv; e += blockDim.x) vdst[e] = vsrc[e];
@@ -399,7 +402,7 @@ __global__ void append_rotary_kernel(const fa_fwd_params p, T* q_rot, int rotate
     const int qr = row - kv_rows;              // (qpos, head)
     if (qr >= p.sq * p.hq) return;
     const int i = qr / p.hq, h = qr % p.hq;
-    const int pos = min(L + (rotate_q_by_pos ? i : 0), p.seqlen_ro - 1);
+    const int pos = max(0, min(L + (rotate_q_by_pos ? i : 0), p.seqlen_ro - 1));
     const T* src = reinterpret_cast<const T*>(p.q.ptr) + (int64_t)b * p.q.stride_b + (int64_t)i * p.q.stride_s + (int64_t)h * p.q.stride_h;
     T* dst = q_rot + (((int64_t)b * p.sq + i) * p.hq + h) * p.d;
     for (int e = threadIdx.x; e < p.d; e += blockDim.x)

@@ -42,7 +42,8 @@ __global__ void __launch_bounds__(256, 1) mla_decode_kernel(const MlaArgs a) {
     const int hg = warp & 3, dh = warp >> 2;
     const int head0 = hh * kMlaHeadsPerCta;
     if (head0 >= p.hq) return;
-    const int sk = p.cache_seqlens[b];
+    // an oversized length is truncated to what the page-table row can address
+    const int sk = (int)max(0LL, min((long long)p.cache_seqlens[b], (long long)p.block_table_stride * p.page_size));
     const int rb = max(0, p.kv_begin), re = p.kv_end > 0 ? min(sk, p.kv_end) : sk;
     const int t_begin = rb + split * a.tokens_per_split;
     const int t_end = min(re, t_begin + a.tokens_per_split);

@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sm100_kernel(const __grid_con
     const int split = blockIdx.x, half = blockIdx.y;
     const int head_tiles = (p.hq + 127) / 128;
     const int b = blockIdx.z / head_tiles, head0 = (blockIdx.z % head_tiles) * 128;
-    const int sk = p.cache_seqlens[b];
+    // an oversized length is truncated to what the page-table row can address
+    const int sk = (int)max(0LL, min((long long)p.cache_seqlens[b], (long long)p.block_table_stride * p.page_size));
     const int rb = max(0, p.kv_begin), re = p.kv_end > 0 ? min(sk, p.kv_end) : sk;
     const int t_begin = rb + split * a.tokens_per_split;
     const int t_end = min(re, t_begin + a.tokens_per_split);

@@ -81,7 +81,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
     const int split = blockIdx.y;
     const int head_tiles = (p.hq + 127) / 128;
     const int b = blockIdx.z / head_tiles, head0 = (blockIdx.z % head_tiles) * 128;
-    const int sk = p.cache_seqlens[b];
+    // an oversized length is truncated to what the page-table row can address
+    const int sk = (int)max(0LL, min((long long)p.cache_seqlens[b], (long long)p.block_table_stride * p.page_size));
     const int rb = max(0, p.kv_begin), re = p.kv_end > 0 ? min(sk, p.kv_end) : sk;
     const int t_begin = rb + split * a.tokens_per_split;
     const int t_end = min(re, t_begin + a.tokens_per_split);
@@ -326,22 +327,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
                 const unsigned char* recv = send + kXchg;
                 if (lane == 0) {
                     mbar_expect_tx(bar(P_RF0 + warp), kXchg);            // the peer's copy of this tile
-                    bulk_copy_wait_read();                                 // my copy of the previous tile has left the send buffer
+                    // The peer warp has read what I sent for the previous tile: that copy had landed there, so it has
+                    // also finished reading my send buffer, which may now be overwritten.
+                    if (j >= 1) ok = mbar_wait_cluster(bar(P_RC0 + warp), (j - 1) & 1, abort_flag, err, 35);
                 }
-                __syncwarp();
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
 #pragma unroll
                 for (int c = 0; c < 16; ++c)
                     reinterpret_cast<uint4*>(send)[c * 32 + lane] =
                         make_uint4(sreg[c >> 3][(c & 7) * 4], sreg[c >> 3][(c & 7) * 4 + 1], sreg[c >> 3][(c & 7) * 4 + 2], sreg[c >> 3][(c & 7) * 4 + 3]);
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) {
-                    // the peer warp has read what I sent for the previous tile
-                    if (j >= 1) ok = mbar_wait_cluster(bar(P_RC0 + warp), (j - 1) & 1, abort_flag, err, 35);
-                    if (ok) bulk_copy_to_peer(map_to_cta(smem_addr(recv), peer), smem_addr(send), kXchg, map_to_cta(bar(P_RF0 + warp), peer));
-                }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
+                if (lane == 0)
+                    bulk_copy_to_peer(map_to_cta(smem_addr(recv), peer), smem_addr(send), kXchg, map_to_cta(bar(P_RF0 + warp), peer));
                 ok = mbar_wait_cluster(bar(P_RF0 + warp), j & 1, abort_flag, err, 36);
                 if (!ok) break;
 #pragma unroll

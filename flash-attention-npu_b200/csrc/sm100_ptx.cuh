@@ -129,13 +129,12 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 }
 // Asynchronous bulk copy from this CTA's shared memory into a peer CTA's shared memory; `bytes` (a multiple of 16)
 // are counted on the PEER's barrier `peer_bar` when they have landed.  `peer_dst` and `peer_bar` are cluster addresses.
+// A copy that completes on an mbarrier belongs to no bulk async-group, so nothing on the issuing side tells when
+// the source has been read: reuse the source only after the receiver has acknowledged the data.
 __device__ __forceinline__ void bulk_copy_to_peer(uint32_t peer_dst, uint32_t src, uint32_t bytes, uint32_t peer_bar) {
     asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(peer_dst), "r"(src), "r"(bytes), "r"(peer_bar) : "memory");
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-// the issuing thread's earlier bulk copies have finished READING their sources
-__device__ __forceinline__ void bulk_copy_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // all threads of all CTAs of the cluster
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -40,23 +40,93 @@ def kv_shard_range(max_len: int, rank: int, world_size: int, align: int) -> Tupl
     return rank * span, (rank + 1) * span
 
 
-def pack_partials(o_partial: torch.Tensor, lse_partial: torch.Tensor) -> torch.Tensor:
-    """(rows, dv) fp32 + (rows,) fp32 -> (rows, dv + 1): one buffer, one collective."""
-    return torch.cat((o_partial, lse_partial.unsqueeze(-1)), dim=-1).contiguous()
+def dense_items(batch: int, kv_heads: int) -> List[Tuple[int, int]]:
+    """(batch entry, KV head) work items of a dense batch; a KV head carries its whole query-head group."""
+    return [(b, h) for b in range(batch) for h in range(kv_heads)]
 
 
-def unpack_partials(buf: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """(world, rows, dv + 1) -> (world, rows, dv), (world, rows)."""
-    return buf[..., :-1].contiguous(), buf[..., -1].contiguous()
+def group_items(items: Sequence[Tuple[int, int]]) -> List[Tuple[Tuple[int, ...], Tuple[int, ...]]]:
+    """Turns a rank's (outer, head) items into as few rectangular calls as possible: outer indices (batch entries
+    or sequences) that own the same set of heads are put into one (outers, heads) group."""
+    heads_of = {}
+    for o, h in items:
+        heads_of.setdefault(o, []).append(h)
+    groups = {}
+    for o in sorted(heads_of):
+        groups.setdefault(tuple(sorted(heads_of[o])), []).append(o)
+    return [(tuple(outers), heads) for heads, outers in sorted(groups.items(), key=lambda kv: (kv[1][0], kv[0]))]
+
+
+def split_pages(n_pages: int, world_size: int) -> List[Tuple[int, int]]:
+    """Contiguous page ranges [g*n/N, (g+1)*n/N) of one sequence, one per rank (some may be empty)."""
+    return [(g * n_pages // world_size, (g + 1) * n_pages // world_size) for g in range(world_size)]
+
+
+def decode_shard_plan(seqlens: Sequence[int], world_size: int, page_size: int, long_threshold: int):
+    """Long-context decode plan.  Sequences of at most `long_threshold` keys stay whole and are spread over the
+    ranks by length (longest first, on top of the load the long ones put on every rank); a longer sequence is cut
+    into `world_size` contiguous page ranges, one per rank, whose partial (O, LSE) are exchanged and combined.
+    With one rank nothing is cut.  Returns a dict:
+      short[r]      sequence indices rank r owns whole
+      long          indices of the cut sequences (the same order on every rank)
+      pages[r][k]   (first page, end page) of long sequence k on rank r
+      tokens[r][k]  keys of long sequence k that lie in that range"""
+    n = len(seqlens)
+    if world_size == 1:
+        return {"short": [list(range(n))], "long": [], "pages": [[]], "tokens": [[]]}
+    long_ids = [i for i in range(n) if seqlens[i] > long_threshold]
+    short_ids = [i for i in range(n) if seqlens[i] <= long_threshold]
+    pages = [[] for _ in range(world_size)]
+    tokens = [[] for _ in range(world_size)]
+    loads = [0.0] * world_size
+    for i in long_ids:
+        L = int(seqlens[i])
+        for r, (p0, p1) in enumerate(split_pages((L + page_size - 1) // page_size, world_size)):
+            t = max(0, min(L, p1 * page_size) - p0 * page_size)
+            pages[r].append((p0, p1))
+            tokens[r].append(t)
+            loads[r] += t
+    short = [[] for _ in range(world_size)]
+    for i in sorted(short_ids, key=lambda j: (-seqlens[j], j)):
+        r = min(range(world_size), key=lambda j: (loads[j], j))
+        short[r].append(i)
+        loads[r] += seqlens[i]
+    return {"short": [sorted(x) for x in short], "long": long_ids, "pages": pages, "tokens": tokens}
+
+
+class PartialBuffer:
+    """Send buffer of one rank for the all-gather of split partials: fp32 (rows, dv) partial O followed by the
+    (rows) partial LSE in ONE allocation, so that the decode kernels write straight into what the collective sends
+    and nothing is packed or unpacked.  `gather()` returns strided views of the receive buffer that the combine
+    kernel reads in place."""
+
+    def __init__(self, rows: int, dv: int, device, world_size: int):
+        self.rows, self.dv, self.world = int(rows), int(dv), int(world_size)
+        self.floats = (self.rows * (self.dv + 1) + 63) // 64 * 64      # every rank's part starts 256-byte aligned
+        self.send = torch.empty(self.floats, dtype=torch.float32, device=device)
+        self.recv = torch.empty(self.world * self.floats, dtype=torch.float32, device=device)
+        self.o = self.send[: self.rows * self.dv].view(self.rows, self.dv)
+        self.lse = self.send[self.rows * self.dv: self.rows * (self.dv + 1)]
+
+    def gather(self, group=None):
+        """One all-gather; returns (world, rows, dv) and (world, rows) views of the receive buffer."""
+        if self.world == 1:
+            self.recv.copy_(self.send)
+        else:
+            dist.all_gather_into_tensor(self.recv, self.send, group=group)
+        r = self.recv.view(self.world, self.floats)
+        return (r[:, : self.rows * self.dv].view(self.world, self.rows, self.dv),
+                r[:, self.rows * self.dv: self.rows * (self.dv + 1)])
 
 
 def all_gather_partials(o_partial: torch.Tensor, lse_partial: torch.Tensor, group=None):
-    """All-gather every rank's (O, LSE) partials into local memory. Returns (world, rows, dv), (world, rows)."""
+    """All-gather of (O, LSE) partials that do not live in a PartialBuffer (one staging copy).
+    Returns (world, rows, dv), (world, rows)."""
     world = dist.get_world_size(group)
-    mine = pack_partials(o_partial, lse_partial)
-    out = torch.empty((world * mine.shape[0], mine.shape[1]), dtype=mine.dtype, device=mine.device)
-    dist.all_gather_into_tensor(out, mine, group=group)      # rank-major concatenation along dim 0
-    return unpack_partials(out.view(world, mine.shape[0], mine.shape[1]))
+    buf = PartialBuffer(o_partial.shape[0], o_partial.shape[1], o_partial.device, world)
+    buf.o.copy_(o_partial)
+    buf.lse.copy_(lse_partial)
+    return buf.gather(group)
 
 
 class _DeviceMemory:
@@ -178,12 +248,13 @@ class PeerExchange:
 
 
 def sharded_kvcache_decode(q, k_cache, v_cache, cache_seqlens, block_table, softmax_scale, max_len, page_size,
-                           causal=False, group=None, out_dtype=None, exchange=None):
+                           causal=False, group=None, out_dtype=None, exchange=None, buffer=None):
     """flash_attn_with_kvcache (seqlen_q small, no append) with the key range sharded over the ranks of `group`.
     Every rank holds q and the cache blocks of its own key range (block_table entries outside it are never
     dereferenced).  Returns out (B, Sq, H, Dv) and lse (B, H, Sq), identical on all ranks.  With `exchange`
-    (a PeerExchange of rows = B*Sq*H) the partials are exchanged and combined by one kernel over peer memory
-    instead of an NCCL all-gather followed by a combine."""
+    (a PeerExchange of rows = B*Sq*H) the partials are exchanged and combined by one kernel over peer memory;
+    otherwise the decode writes them into a PartialBuffer (`buffer`, made here when not given), one NCCL
+    all-gather brings every rank's buffer into local memory and the combine kernel reads them in place."""
     from flash_attn_npu import flash_attn_npu as ext
     from flash_attn_npu_3 import flash_attn_npu_3 as ext3
     rank, world = dist.get_rank(group), dist.get_world_size(group)
@@ -193,36 +264,42 @@ def sharded_kvcache_decode(q, k_cache, v_cache, cache_seqlens, block_table, soft
     if exchange is not None:
         po, pl = exchange.partials()
     else:
-        po = torch.empty(rows, dv, dtype=torch.float32, device=q.device)
-        pl = torch.empty(rows, dtype=torch.float32, device=q.device)
+        buffer = buffer or PartialBuffer(rows, dv, q.device, world)
+        po, pl = buffer.o, buffer.lse
     ext.kvcache_forward(q, k_cache, v_cache, None, None, cache_seqlens, None, None, None, block_table, None, None,
                         softmax_scale, causal, -1, -1, 0.0, False, 0,
                         kv_range=kv_shard_range(max_len, rank, world, page_size), partials=(po, pl))
     if exchange is not None:
         out, lse = exchange.combine(out_dtype or q.dtype)
     else:
-        go, gl = all_gather_partials(po, pl, group)
+        go, gl = buffer.gather(group)
         out, lse = ext3.fwd_combine(go, gl, None, out_dtype or q.dtype)
     return out.reshape(b, sq, h, dv), lse.reshape(b, sq, h).permute(0, 2, 1).contiguous()
 
 
-def sharded_mla_decode(q_nope, q_rope, latent_i8, scales, rope, block_table, cache_seqlens, softmax_scale, max_len,
-                       page_size, group=None, exchange=None):
-    """int8 latent decode with the key range sharded over the ranks of `group` (benchmark configuration 5):
-    partial (O, LSE) per rank, one all-gather, local combine.  Returns out (B,1,H,512) bf16, lse (B,H,1)."""
+def sharded_mla_decode(q_nope, q_rope, latent_i8, scales, rope, block_table, cache_seqlens, softmax_scale, max_len=None,
+                       page_size=None, group=None, exchange=None, buffer=None):
+    """int8 latent decode of sequences whose keys are spread over the ranks of `group` (benchmark configuration
+    5): partial (O, LSE) per rank, exchange, combine.  Returns out (B,1,H,512) bf16, lse (B,H,1), identical on
+    all ranks.  Two ways to say which keys a rank holds:
+      * `max_len` given: every rank passes the full table and lengths and attends to the key range
+        kv_shard_range(max_len, rank, world, page_size) of every sequence;
+      * `max_len` None: `block_table` / `cache_seqlens` already describe only this rank's pages and key count of
+        every sequence (decode_shard_plan), which lets each sequence be cut in proportion to its own length."""
     from flash_attn_npu_3 import flash_attn_npu_3 as ext3
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     b, _, h, dl = q_nope.shape
     if exchange is not None:
         po, pl = exchange.partials()
     else:
-        po = torch.empty(b * h, dl, dtype=torch.float32, device=q_nope.device)
-        pl = torch.empty(b * h, dtype=torch.float32, device=q_nope.device)
+        buffer = buffer or PartialBuffer(b * h, dl, q_nope.device, world)
+        po, pl = buffer.o, buffer.lse
+    rng = kv_shard_range(max_len, rank, world, page_size) if max_len is not None else None
     ext3.mla_decode(q_nope, q_rope, latent_i8, scales, rope, block_table, cache_seqlens, softmax_scale, 0,
-                    kv_range=kv_shard_range(max_len, rank, world, page_size), partials=(po, pl))
+                    kv_range=rng, partials=(po, pl))
     if exchange is not None:
         out, lse = exchange.combine(torch.bfloat16)
     else:
-        go, gl = all_gather_partials(po, pl, group)
+        go, gl = buffer.gather(group)
         out, lse = ext3.fwd_combine(go, gl, None, torch.bfloat16)
     return out.reshape(b, 1, h, dl), lse.reshape(b, h, 1)

@@ -98,8 +98,10 @@ def fwd_combine(out_partial, lse_partial, out=None, out_dtype=None):
     capi.require_cuda(out_partial, lse_partial)
     nsplit = out_partial.shape[0]
     dv = out_partial.shape[-1]
-    op = out_partial.contiguous().float()
-    lp = lse_partial.contiguous().float()
+    # the partials of one split must be dense; the splits themselves may lie any distance apart (the receive buffer
+    # of an all-gather holds [O | LSE] of every rank back to back)
+    op = out_partial if out_partial.dtype == torch.float32 and out_partial[0].is_contiguous() else out_partial.contiguous().float()
+    lp = lse_partial if lse_partial.dtype == torch.float32 and lse_partial[0].is_contiguous() else lse_partial.contiguous().float()
     rows = lp[0].numel()
     out_dtype = out_dtype or (out.dtype if out is not None else torch.float32)
     code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[out_dtype]
@@ -107,7 +109,7 @@ def fwd_combine(out_partial, lse_partial, out=None, out_dtype=None):
     lse = torch.empty(lse_partial.shape[1:], dtype=torch.float32, device=op.device)
     c = CombineParams()
     c.o_partial, c.lse_partial = op.data_ptr(), lp.data_ptr()
-    c.o_split_stride, c.o_row_stride, c.lse_split_stride = rows * dv, dv, rows
+    c.o_split_stride, c.o_row_stride, c.lse_split_stride = op.stride(0), dv, lp.stride(0)
     c.o, c.o_stride, c.lse = res.data_ptr(), dv, lse.data_ptr()
     c.nsplit, c.rows, c.dv, c.out_dtype = nsplit, rows, dv, code
     c.stream = capi.stream_ptr(op.device)

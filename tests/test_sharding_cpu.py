@@ -69,8 +69,50 @@ def test_all_gather_of_partials_and_combine_over_two_gloo_ranks(tmp_path):
     assert all(os.path.exists(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(2))
 
 
-def test_pack_unpack_roundtrip():
-    o, l = torch.randn(5, 7), torch.randn(5)
-    buf = sh.pack_partials(o, l).unsqueeze(0)
-    o2, l2 = sh.unpack_partials(buf)
-    assert torch.equal(o2[0], o) and torch.equal(l2[0], l)
+def test_partial_buffer_views_share_one_allocation():
+    buf = sh.PartialBuffer(5, 8, "cpu", 1)
+    buf.o.copy_(torch.arange(40, dtype=torch.float32).view(5, 8))
+    buf.lse.copy_(torch.arange(5, dtype=torch.float32) + 100)
+    assert buf.o.data_ptr() == buf.send.data_ptr() and buf.lse.data_ptr() == buf.send.data_ptr() + 5 * 8 * 4
+    go, gl = buf.gather()
+    assert go.shape == (1, 5, 8) and gl.shape == (1, 5)
+    assert torch.equal(go[0], buf.o) and torch.equal(gl[0], buf.lse)
+    assert go[0].is_contiguous() and gl[0].is_contiguous() and buf.floats % 64 == 0
+
+
+def test_group_items_makes_rectangular_calls():
+    items = sh.dense_items(4, 32)
+    assert len(items) == 128
+    for world in (1, 2, 4, 8):
+        bins = sh.balance_items([1.0] * len(items), world)
+        assert sorted(i for b in bins for i in b) == list(range(128))
+        for mine in bins:
+            assert len(mine) == 128 // world
+            groups = sh.group_items([items[i] for i in mine])
+            # equal costs deal the heads round-robin: every batch entry gets the same heads -> one call per rank
+            assert len(groups) == 1 and len(groups[0][0]) == 4 and len(groups[0][1]) == 32 // world
+    groups = sh.group_items([(0, 1), (0, 2), (1, 1), (2, 2), (2, 1)])
+    assert groups == [((0, 2), (1, 2)), ((1,), (1,))]
+
+
+def test_decode_shard_plan_cuts_long_sequences_by_their_own_length():
+    gen = torch.Generator().manual_seed(5)
+    lens = torch.randint(4096, 131073, (64,), generator=gen).tolist()
+    page, thr = 256, 32768
+    one = sh.decode_shard_plan(lens, 1, page, thr)
+    assert one["long"] == [] and one["short"] == [list(range(64))]
+    for world in (2, 4, 8):
+        plan = sh.decode_shard_plan(lens, world, page, thr)
+        longs = plan["long"]
+        assert all(lens[i] > thr for i in longs)
+        owned = sorted(i for r in range(world) for i in plan["short"][r])
+        assert owned == [i for i in range(64) if lens[i] <= thr]
+        for k, i in enumerate(longs):
+            n = (lens[i] + page - 1) // page
+            ranges = [plan["pages"][r][k] for r in range(world)]
+            assert ranges[0][0] == 0 and ranges[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+            assert sum(plan["tokens"][r][k] for r in range(world)) == lens[i]
+            assert max(b - a for a, b in ranges) - min(b - a for a, b in ranges) <= 1
+        loads = [sum(plan["tokens"][r]) + sum(lens[i] for i in plan["short"][r]) for r in range(world)]
+        assert max(loads) - min(loads) <= thr
