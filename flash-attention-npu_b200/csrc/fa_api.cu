@@ -112,15 +112,26 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
     }
 }
 
+// Window normalisation of the reference's forward host code (flash_api.cpp:684-704, :936-956, :483-505), `sk` being
+// the (longest) key length the host knows: a side that reaches sk is unbounded; under a sliding window an unbounded
+// RIGHT side then becomes sk keys past the diagonal, which for seqlen_q > seqlen_k + 1 is a real bound (rows whose
+// diagonal lies more than sk keys before the first key see nothing).  The reference does the same to the left
+// side, where it never changes the mask.
+static void normalize_windows_like_forward(int sk, int causal, int32_t& wl, int32_t& wr) {
+    if (sk <= 0) return;
+    if (wl >= sk) wl = -1;
+    if (wr >= sk) wr = -1;
+    if (causal) return;                                   // the kernels force window_right = 0
+    const bool is_causal = wl < 0 && wr == 0;
+    const bool is_local = (wl >= 0 || wr >= 0) && !is_causal;
+    if (is_local && wr < 0) wr = sk;
+}
+
 static int run_forward(const fa_fwd_params& pin, bool allow_fast) {
     fa_fwd_params p = pin;
     if (p.b == 0 || p.hq == 0) return FA_OK;
     if ((p.cu_seqlens_q ? p.total_q : p.sq) == 0) return FA_OK;
-    // Window normalisation of the reference's forward host code (flash_api.cpp:684-704, :936-956,
-    // :483-505): a side that reaches the (longest) key length is unbounded.  For the right side this
-    // is not a no-op when seqlen_q exceeds the window, so it is applied here exactly as there.
-    if (p.sk > 0 && p.window_left >= p.sk) p.window_left = -1;
-    if (p.sk > 0 && p.window_right >= p.sk) p.window_right = -1;
+    normalize_windows_like_forward(p.sk, p.causal, p.window_left, p.window_right);
     FwdPlan plan;
     plan_forward(p, plan);
     mark_kernel(reinterpret_cast<cudaStream_t>(p.stream));
@@ -232,12 +243,11 @@ static int check_bwd(const fa_bwd_params& p) {
 static int run_backward(const fa_bwd_params& pin) {
     fa_bwd_params p = pin;
     if (p.b == 0) return FA_OK;
-    // The forward's rule first (flash_api.cpp:684-704: a side that reaches the key length is unbounded), because
-    // for seqlen_q > seqlen_k it changes the mask and the saved LSE was computed under that mask; then the rule of
+    // The forward's rule first, because for seqlen_q > seqlen_k it changes the mask and the saved LSE was computed
+    // under that mask; then the rule of
     // the reference's backward host code (fag_general_host.cpp:81-92, flash_api.cpp:1155-1162), which never
     // changes the mask.
-    if (p.sk > 0 && p.window_left >= p.sk) p.window_left = -1;
-    if (p.sk > 0 && p.window_right >= p.sk) p.window_right = -1;
+    normalize_windows_like_forward(p.sk, p.causal, p.window_left, p.window_right);
     if (p.window_left >= p.sk - 1) p.window_left = -1;
     if (p.window_right >= p.sq - 1) p.window_right = -1;
     mark_kernel(reinterpret_cast<cudaStream_t>(p.stream));

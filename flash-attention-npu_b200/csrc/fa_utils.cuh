@@ -100,12 +100,12 @@ struct SeqInfo {
     int kb;         // batch index into the KV tensors (cache_batch_idx applied)
 };
 
-// Length of sequence b of a KV-cache call, read on the device.  A stale or oversized entry is truncated to what
-// the cache row (or the page-table row) can hold, so that no kernel indexes past the table or the cache.
+// Length of sequence b of a KV-cache call, read on the device.  A stale or oversized entry is truncated to the
+// capacity the host passed (`sk`: rows of a dense cache, page-table width x page size of a paged one), so that no
+// kernel indexes past the table or the cache.
 __device__ __forceinline__ int cache_len(const fa_fwd_params& p, int b) {
-    const long long cap = p.block_table ? (long long)p.block_table_stride * p.page_size : (long long)p.sk;
     const long long len = (long long)p.seqused_k[b] + p.s_new;
-    return (int)max(0LL, min(len, cap));
+    return (int)max(0LL, min(len, (long long)p.sk));
 }
 
 // Visible key range of query position i (bottom-right aligned): [lo, hi] inclusive.

@@ -376,7 +376,6 @@ __global__ void append_rotary_kernel(const fa_fwd_params p, T* q_rot, int rotate
         const int pos = L + i;
         // a length that points outside the cache (or past the page-table row) appends nothing
         if (pos < 0 || pos >= p.sk) return;
-        if (p.block_table && pos / p.page_size >= p.block_table_stride) return;
         int64_t koff, voff;
         if (p.block_table) {
             const int blk = p.block_table[(int64_t)b * p.block_table_stride + pos / p.page_size];

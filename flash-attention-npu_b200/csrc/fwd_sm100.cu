@@ -369,8 +369,7 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
     if (a.seqused_k) {                                       // cache call: the length lives on the device
-        const long long cap = a.block_table ? (long long)a.bt_stride * a.page_size : (long long)a.sk;
-        sk = (int)max(0LL, min((long long)a.seqused_k[b] + a.s_new, cap));     // an oversized entry is truncated
+        sk = (int)max(0LL, min((long long)a.seqused_k[b] + a.s_new, (long long)a.sk));   // an oversized entry is truncated to the capacity
     }
     const int m0 = mblk * 256;
     if (m0 >= sq) return;

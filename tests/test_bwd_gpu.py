@@ -126,3 +126,29 @@ def test_packed_backward_variants():
     (g,) = torch.autograd.grad(out, (x,), do.cuda())
     for i, name in enumerate(("dq", "dk", "dv")):
         assert_within(name, g[:, :, i].cpu(), lp[i], f32[i], roundings=3)
+
+
+def test_backward_uses_the_mask_of_the_forward_when_queries_outnumber_keys():
+    """seqlen_q > seqlen_k with a right window in [seqlen_k, seqlen_q - 1): the forward host rule turns that side
+    into "unbounded" and then, under a sliding window, into seqlen_k keys past the diagonal (flash_api.cpp:684-704),
+    which changes the mask; the saved LSE belongs to that mask, so the backward must differentiate the same one (the
+    reference's two host files disagree here; this library keeps the forward's mask in both directions)."""
+    import flash_attn_npu as m
+    torch.manual_seed(5)
+    b, sq, sk, h, d, win = 1, 300, 128, 2, 128, (40, 200)
+    q, do = (torch.rand(b, sq, h, d) * 2 - 1).bfloat16(), (torch.rand(b, sq, h, d) * 2 - 1).bfloat16()
+    k, v = (torch.rand(b, sk, h, d) * 2 - 1).bfloat16(), (torch.rand(b, sk, h, d) * 2 - 1).bfloat16()
+    eff = (40, sk)                                            # what the forward attends under
+    scale = d ** -0.5
+    lp_o, _ = orc.attention_fwd(q, k, v, scale, False, win)
+    f_o, f_l = orc.attention_fwd(q.float(), k.float(), v.float(), scale, False, win, data_type=torch.float32)
+    same_o, same_l = orc.attention_fwd(q.float(), k.float(), v.float(), scale, False, eff, data_type=torch.float32)
+    assert torch.equal(f_o, same_o) and torch.equal(f_l, same_l)          # the oracle's forward applies the same rule
+    lp = orc.attention_bwd(q, k, v, do, f_l, scale, False, eff)
+    f32 = orc.attention_bwd(q.float(), k.float(), v.float(), do.float(), f_l, scale, False, eff)
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = m.flash_attn_func(qc, kc, vc, softmax_scale=scale, window_size=win)
+    grads = torch.autograd.grad(out, (qc, kc, vc), do.cuda())
+    assert_within("out", out.detach().cpu(), lp_o, f_o)
+    for name, got, a, b_ in zip(("dq", "dk", "dv"), grads, lp, f32):
+        assert_within(name, got.cpu(), a, b_, roundings=3)

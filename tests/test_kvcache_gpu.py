@@ -325,3 +325,62 @@ def test_prefill_against_cache_uses_tcgen05(paged, page, append):
     assert torch.isfinite(out).all()
     assert_within("out", out.cpu(), lp_o, f_o)
     assert_lse(lse, f_l)
+
+
+@pytest.mark.parametrize("paged", [True, False])
+def test_oversized_cache_seqlens_are_truncated_and_append_nothing(paged):
+    """A stale or oversized cache_seqlens entry (the host never sees the device-resident lengths) must not make any
+    kernel index past the page-table row or the cache: such a length is truncated to the capacity and its append is
+    dropped.  The cache and the table carry sentinel padding so that every access stays inside the allocations with
+    or without the guard; the sentinels must come back untouched."""
+    import flash_attn_npu as m
+    gen = torch.Generator().manual_seed(77)
+    b, h, hkv, d, page, dt = 3, 8, 2, 128, 64, torch.bfloat16
+    cap_blocks = 4                                                   # capacity: 256 keys a sequence
+    guard = 8                                                        # sentinel pages / table columns
+    q = torch.randn(b, 1, h, d, generator=gen).to(dt)
+    kn, vn = torch.randn(b, 1, hkv, d, generator=gen).to(dt), torch.randn(b, 1, hkv, d, generator=gen).to(dt)
+    lens = torch.tensor([100, 256, 100000], dtype=torch.int32)      # fine, full (append would overflow), stale
+    if paged:
+        pool = b * cap_blocks
+        kc = torch.randn(pool + guard, page, hkv, d, generator=gen).to(dt)
+        vc = torch.randn(pool + guard, page, hkv, d, generator=gen).to(dt)
+        big = torch.full((b, cap_blocks + guard), pool + guard - 1, dtype=torch.int32)     # sentinel columns name the last sentinel page
+        big[:, :cap_blocks] = torch.arange(pool, dtype=torch.int32).reshape(b, cap_blocks)
+        table = big[:, :cap_blocks]                                  # a view: row stride cap_blocks + guard, width cap_blocks
+        assert table.stride(0) == cap_blocks + guard
+    else:
+        kc = torch.randn(b + 1, cap_blocks * page + guard * page, hkv, d, generator=gen).to(dt)
+        vc = torch.randn(b + 1, cap_blocks * page + guard * page, hkv, d, generator=gen).to(dt)
+        table = None
+    kg, vg = kc.cuda(), vc.cuda()
+    if paged:
+        tg = big.cuda()[:, :cap_blocks]
+        k_view, v_view = kg, vg
+    else:
+        tg = None
+        k_view, v_view = kg[:b, :cap_blocks * page], vg[:b, :cap_blocks * page]     # capacity = 256 rows of a longer allocation
+    out, lse = m.flash_attn_with_kvcache(q.cuda(), k_view, v_view, kn.cuda(), vn.cuda(), cache_seqlens=lens.cuda(),
+                                         block_table=tg, causal=True, return_softmax_lse=True)
+    torch.cuda.synchronize()
+    k_after, v_after = kg.cpu(), vg.cpu()
+    # sequence 0 appended one row at position 100; sequences 1 and 2 appended nothing; sentinels untouched
+    exp_k, exp_v = kc.clone(), vc.clone()
+    if paged:
+        exp_k[int(big[0, 100 // page]), 100 % page], exp_v[int(big[0, 100 // page]), 100 % page] = kn[0, 0], vn[0, 0]
+    else:
+        exp_k[0, 100], exp_v[0, 100] = kn[0, 0], vn[0, 0]
+    assert torch.equal(k_after.view(torch.int16), exp_k.view(torch.int16))
+    assert torch.equal(v_after.view(torch.int16), exp_v.view(torch.int16))
+    # sequence 0 is an ordinary call; the truncated ones attend to their 256 cached keys
+    cap = cap_blocks * page
+    for i, L in ((0, 101), (1, cap), (2, cap)):
+        if paged:
+            ki = orc.gather_paged(exp_k, big[i], L).unsqueeze(0)
+            vi = orc.gather_paged(exp_v, big[i], L).unsqueeze(0)
+        else:
+            ki, vi = exp_k[i:i + 1, :L], exp_v[i:i + 1, :L]
+        lp_o, _ = orc.attention_fwd(q[i:i + 1], ki, vi, d ** -0.5, True)
+        f_o, f_l = orc.attention_fwd(q[i:i + 1].float(), ki.float(), vi.float(), d ** -0.5, True, data_type=torch.float32)
+        assert_within(f"out[{i}]", out[i:i + 1].cpu(), lp_o, f_o)
+        assert_lse(lse[i:i + 1], f_l)

@@ -2,7 +2,10 @@
 (a serving loop with a sealed memory pool, a plugin that must not call the allocator inside a step).
 Called straight through the C-ABI and compared with fa_fwd_kvcache on the same inputs, twice in a row:
 the built-in pool is shared and keeps the previous call's contents, so the second call must not be
-disturbed by the first.  Collected last so that a failure here cannot hide any other test."""
+disturbed by the first.  A third call repeats the second and checks the property the entry point exists for: the
+device's free memory and the framework's allocation counter are the same before and after it (the first calls may
+still make the driver load kernel images, which takes memory once).  Collected last so that a failure here cannot hide
+any other test."""
 import pytest
 import torch
 
@@ -34,7 +37,8 @@ def test_static_scratch_matches_caller_workspace_twice_in_a_row():
     kc = torch.randn(b * blocks_per_seq, page, hkv, d, device="cuda").bfloat16()
     vc = torch.randn(b * blocks_per_seq, page, hkv, d, device="cuda").bfloat16()
     table = torch.randperm(b * blocks_per_seq, device="cuda").int().reshape(b, blocks_per_seq)
-    for round_, (lens_list, splits) in enumerate((([2500, 64, 1, 1999, 777], 6), ([900, 2560, 333, 5, 1500], 0))):
+    rounds = (([2500, 64, 1, 1999, 777], 6), ([900, 2560, 333, 5, 1500], 0), ([900, 2560, 333, 5, 1500], 0))
+    for round_, (lens_list, splits) in enumerate(rounds):
         lens = torch.tensor(lens_list, dtype=torch.int32, device="cuda")
         q = torch.randn(b, 2, hq, d, device="cuda").bfloat16()
         ref_out, new_out = torch.empty_like(q), torch.empty_like(q)
@@ -47,8 +51,13 @@ def test_static_scratch_matches_caller_workspace_twice_in_a_row():
         p.workspace, p.workspace_bytes = ws.data_ptr(), need
         assert capi.lib.fa_fwd_kvcache(p) == 0, capi.lib.fa_last_error()
         p2 = build_params(q, kc, vc, table, lens, new_out, new_lse, splits)      # no workspace given
+        torch.cuda.synchronize()
+        free_before, held_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         assert capi.lib.fa_fwd_kvcache_static(p2) == 0, capi.lib.fa_last_error()
         torch.cuda.synchronize()
+        if round_ == 2:
+            assert torch.cuda.mem_get_info()[0] == free_before, "device memory in use changed across the call"
+            assert torch.cuda.memory_allocated() == held_before
         # same tolerance as the other KV-cache tests (2^-6 on bf16 outputs, 1e-4 on LSE)
         assert (new_out.float() - ref_out.float()).abs().max().item() <= 2 ** -6, f"call {round_}"
         fin = torch.isfinite(ref_lse)            # rows without a visible key carry LSE = +inf in both
