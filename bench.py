@@ -673,11 +673,19 @@ def config5_leg(dd, iters=10):
     def cut_peer():
         return sh.sharded_mla_decode(qn_l, qr_l, lat, sc, rope, tab_l, len_l, scale, exchange=ex)
 
+    own0, own1 = rank * nl // world, (rank + 1) * nl // world          # cut sequences whose result THIS rank keeps
+
+    def cut_peer_own_rows():
+        po, pl = ex.partials()
+        ext3.mla_decode(qn_l, qr_l, lat, sc, rope, tab_l, len_l, scale, 0, partials=(po, pl))
+        return ex.combine(torch.bfloat16, own0 * hq, own1 * hq)
+
     variants = {}
     if nl:
         variants = {"decode_only_ms": lambda: (whole(), cut_partials_only()),
                     "nccl_allgather_combine_ms": lambda: (whole(), cut_nccl()),
-                    "peer_exchange_combine_ms": lambda: (whole(), cut_peer())}
+                    "peer_exchange_combine_ms": lambda: (whole(), cut_peer()),
+                    "peer_exchange_own_rows_ms": lambda: (whole(), cut_peer_own_rows())}
     else:
         variants = {"decode_only_ms": whole}
     times = {}
@@ -712,8 +720,9 @@ def config5_leg(dd, iters=10):
         o_n, l_n = cut_nccl()
         if ex is not None:
             o_p, l_p = cut_peer()
+            o_own, _ = cut_peer_own_rows()
             ex.check()
-            same = bool(torch.equal(o_n, o_p))
+            same = bool(torch.equal(o_n, o_p)) and bool(torch.equal(o_own, o_n[own0:own1].reshape(-1, dl)))
         # every rank checks a different cut sequence (the shortest ones): all its ranges are regenerated from the seeds
         order = sorted(range(nl), key=lambda x: lens[longs[x]])
         k = order[rank % nl]
@@ -753,7 +762,10 @@ def config5_leg(dd, iters=10):
                                 "max over ranks of (whole-sequence call + cut-sequence call + exchange + combine)",
                         "identical_results": same, "partial_rows": rows, "exchange_bytes_per_rank": rows * (dl + 1) * 4,
                         "exchange_cost_us": {"nccl": 1e3 * (times["nccl_allgather_combine_ms"] - times["decode_only_ms"]),
-                                             "peer_kernel": 1e3 * (times["peer_exchange_combine_ms"] - times["decode_only_ms"])}})
+                                             "peer_kernel": 1e3 * (times["peer_exchange_combine_ms"] - times["decode_only_ms"]),
+                                             "peer_kernel_own_rows": 1e3 * (times["peer_exchange_own_rows_ms"] - times["decode_only_ms"])},
+                        "own_rows": "every rank combines only the cut sequences whose result it keeps (1/N of the rows): "
+                                    "the all-gather variants leave every result on every rank"})
     return res, sharded
 
 

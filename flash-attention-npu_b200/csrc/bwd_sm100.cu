@@ -54,6 +54,11 @@ struct alignas(64) Sm100BwdArgs {
     int b, sq, sk, hq, hkv;
     float scale, scale_log2;
     int causal, wl, wr;
+    // dS^T tiles handed from the dK/dV kernel to the dQ kernel through global memory (dense calls within the
+    // workspace limit): tile (batch, head, key block n, query block m) = 128 keys x 128 queries of the input type,
+    // stored as [16 chunks of 8 queries][128 keys][8 queries]
+    void* ds_tiles;
+    int nkb, nqb;
 };
 
 template <int D>
@@ -307,7 +312,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
             tmem_st8(tmem + lane_base + COL_ST + cg * 32 + 16, hi8);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(E_P0));
+            mbar_arrive_relaxed(bar(E_P0));
             // phase B: dS^T = P^T (dP^T - delta), rounded, over dP^T's columns
             ok = mbar_wait(bar(E_S1), s & 1, abort_flag, err, 28);
             if (!ok) break;
@@ -329,7 +334,20 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
             tmem_st8(tmem + lane_base + COL_DPT + cg * 32 + 16, hi8);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(E_P1));
+            mbar_arrive_relaxed(bar(E_P1));
+            if (a.ds_tiles) {
+                // the same rounded dS^T goes to global memory for the dQ kernel, which then needs one GEMM a tile
+                // instead of recomputing S and dP.  Issued after the hand-off so that the stores are off the chain.
+                const int64_t tile = (((int64_t)b * a.hq + (hk * G + s / nmb)) * a.nkb + blockIdx.x) * a.nqb + (mb_lo + s % nmb);
+                // tile layout [16 chunks of 8 queries][128 keys][16 bytes]: a warp's 32 rows of one chunk are 512
+                // contiguous bytes (one fully coalesced store instruction), and the tile is at the same time the
+                // unswizzled operand layout the dQ kernel's MMA reads
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(a.ds_tiles) + tile * (128 * 128 * 2)) + (cg * 4) * 128 + r;
+                dst[0] = make_uint4(lo8[0], lo8[1], lo8[2], lo8[3]);
+                dst[128] = make_uint4(lo8[4], lo8[5], lo8[6], lo8[7]);
+                dst[256] = make_uint4(hi8[0], hi8[1], hi8[2], hi8[3]);
+                dst[384] = make_uint4(hi8[4], hi8[5], hi8[6], hi8[7]);
+            }
         }
         if (ok) ok = mbar_wait(bar(E_ACC), 0, abort_flag, err, 26);
         if (ok) {
@@ -590,6 +608,133 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
 }
 
 // ------------------------------------------------------------------------------------------------------
+// dQ from stored dS^T tiles: dQ = scale * sum over key blocks of dS K, one GEMM a tile.  The dK/dV kernel has
+// written every (key block, query block) tile it visited; this kernel visits exactly the same pairs (it derives its
+// key blocks from the dK/dV kernel's rule), streams dS^T and K tiles through a three-stage TMA ring and multiplies.
+// No element-wise work, no exponentials: HBM-bound on reading the dS^T tiles once.
+//   warp 0 TMA producer, warp 1 MMA issuer (also owns the tensor memory), warps 2-5 epilogue (thread = query row)
+// ------------------------------------------------------------------------------------------------------
+enum { H_KF0 = 0, H_KF1, H_KF2, H_KE0, H_KE1, H_KE2, H_ACC, H_COUNT };
+
+template <typename T, int D>
+__global__ void __launch_bounds__(192, 1) bwd_dq_from_ds_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
+    using L = BwdSm100Smem<D>;
+    constexpr int NSUB = D / 64;
+    constexpr int kStage = 2 * L::kSub + L::kTileB;          // dS^T tile (128 x 128) + K tile (128 x D)
+    constexpr uint32_t TMEM_COLS = D <= 64 ? 64 : 128;
+    constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
+    // M = 128 queries, N = D, K = keys; both operands are read "across" their tiles: A = dS^T tile [key][query]
+    // (query-contiguous), B = K tile [key][dim] (dim-contiguous)
+    constexpr uint32_t IDESC = umma_idesc(FMT, 128, D, 1, 1);
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
+    const uint32_t bars = sbase + 3 * kStage;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + 3 * kStage + 8 * H_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + 3 * kStage + 8 * H_COUNT + 8);
+    auto bar = [&](int i) { return bars + 8u * i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int mblk = gridDim.x - 1 - blockIdx.x;
+    const int sq = a.sq, sk = a.sk;
+    const int m0 = mblk * 128;
+    if (m0 >= sq) return;
+    if (g_bwd_sm100_error) return;
+    const int hk = h / (a.hq / a.hkv);
+    const int wl = a.wl, wr = a.causal ? 0 : a.wr;
+    const int diff = sk - sq;
+    const int rows = min(128, sq - m0);
+    // key blocks whose dK/dV CTA walked this query block (the rule of bwd_dkdv_sm100_kernel); they form one range
+    int t_lo = a.nkb, t_hi = 0;
+    for (int n = 0; n < a.nkb; ++n) {
+        const int n0 = n * 128, krows = min(128, sk - n0);
+        int i_lo = 0, i_hi = sq - 1;
+        if (wr >= 0) i_lo = max(0, n0 - diff - wr);
+        if (wl >= 0) i_hi = min(sq - 1, n0 + krows - 1 + wl - diff);
+        const int mb_lo = i_lo / 128, mb_hi = i_hi >= i_lo ? i_hi / 128 + 1 : mb_lo;
+        if (mblk >= mb_lo && mblk < mb_hi) { t_lo = min(t_lo, n); t_hi = max(t_hi, n + 1); }
+    }
+    const int ntiles = max(0, t_hi - t_lo);
+    T* dqb = reinterpret_cast<T*>(a.dq) + (int64_t)b * a.dq_sb + (int64_t)m0 * a.dq_ss + (int64_t)h * a.dq_sh;
+    if (ntiles == 0) {
+        if (tid < rows) {
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            T* row = dqb + (int64_t)tid * a.dq_ss;
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(row)[c] = z;
+        }
+        return;
+    }
+    if (tid == 0) {
+        for (int i = 0; i < H_COUNT; ++i) mbar_init(bar(i), 1u);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) { tmem_alloc(smem_addr(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    int* err = &g_bwd_sm100_error;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&a.tk);
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int st = j % 3;
+                if (j >= 3) ok = mbar_wait(bar(H_KE0 + st), (j / 3 - 1) & 1, abort_flag, err, 51);
+                if (!ok) break;
+                const int n = t_lo + j;
+                const int64_t tile = (((int64_t)b * a.hq + h) * a.nkb + n) * a.nqb + mblk;
+                mbar_expect_tx(bar(H_KF0 + st), kStage);
+                const uint32_t s0 = sbase + st * kStage;
+                bulk_load_1d(s0, reinterpret_cast<const unsigned char*>(a.ds_tiles) + tile * (128 * 128 * 2), 2 * L::kSub, bar(H_KF0 + st));
+#pragma unroll
+                for (int c = 0; c < NSUB; ++c) tma_load_4d(s0 + 2 * L::kSub + c * L::kSub, &a.tk, bar(H_KF0 + st), c * 64, hk, n * 128, b);
+            }
+        }
+    } else if (warp == 1) {
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int st = j % 3;
+            ok = mbar_wait(bar(H_KF0 + st), (j / 3) & 1, abort_flag, err, 52);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t s0 = sbase + st * kStage;
+            // A: the dS^T tile as stored ([chunk][key][16 B], no swizzle): 8 keys of a chunk are 128 contiguous bytes,
+            // chunks are 2048 bytes apart, a K step of 16 keys is 256 bytes further on; B: the K tile (128-byte swizzle)
+            const uint64_t dA = umma_desc_mn_noswizzle(s0, 128, 2048), dB = umma_desc(s0 + 2 * L::kSub, L::kSub, 1024);
+            if (j > 0) umma_ss_w<1>(tmem, dA, dB, IDESC); else umma_ss_w<0>(tmem, dA, dB, IDESC);
+#pragma unroll
+            for (int kk = 1; kk < 8; ++kk) umma_ss_w<1>(tmem, umma_desc_at(dA, kk * 256), umma_desc_at(dB, kk * 2048), IDESC);
+            umma_commit_w(bar(H_KE0 + st));
+        }
+        if (ok) umma_commit_w(bar(H_ACC));
+    } else {
+        // Rows of tiles past the last key hold zeros (their probabilities are zero), so nothing needs masking here.
+        const int r = (warp & 3) * 32 + lane;               // warps 2..5 cover the four lane quarters 2,3,0,1
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        if (mbar_wait(bar(H_ACC), 0, abort_flag, err, 53)) {
+            tc_fence_after();
+            T* row = dqb + (int64_t)r * a.dq_ss;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t acc[32];
+                tmem_ld32(tmem + lane_base + c * 32, acc);
+                tmem_wait_ld();
+                if (r < rows) store_row_scaled<T>(row + c * 32, acc, a.scale);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------------------------------------------
 // host
 // ------------------------------------------------------------------------------------------------------
 // delta[row] = sum_d O[row, d] * dO[row, d].  HBM-bound: D/8 lanes share a row with one 16-byte load each of O and
@@ -661,6 +806,11 @@ static cudaStream_t side_stream() {
     return streams[dev];
 }
 
+// 1 (default): dense calls hand dS^T from the dK/dV kernel to a one-GEMM dQ kernel through the workspace;
+// 0: the dQ kernel always recomputes S and dP (fa_debug_set key 7)
+static int g_ds_spill = 1;
+void bwd_sm100_set_ds_spill(int v) { g_ds_spill = v; }
+
 bool bwd_sm100_supported(const fa_bwd_params& p) {
     if (p.d != p.dv_dim || (p.d != 64 && p.d != 128)) return false;
     if (p.softcap > 0.f || !(p.scale > 0.f)) return false;
@@ -675,7 +825,19 @@ bool bwd_sm100_supported(const fa_bwd_params& p) {
     return tensor_map_encoder_available();
 }
 
-size_t bwd_sm100_workspace(const fa_bwd_params& p) { return bwd_generic_workspace(p); }
+// The dK/dV kernel can hand its dS^T tiles to the dQ kernel through the workspace (then the backward executes the
+// algorithm's five GEMMs a tile pair instead of seven): dense calls whose tiles fit into this many bytes.
+constexpr size_t kDsTileBytes = 128 * 128 * 2;
+constexpr size_t kDsWorkspaceLimit = (size_t)6 << 30;
+static size_t ds_tiles_bytes(const fa_bwd_params& p) {
+    if (p.cu_seqlens_q || p.cu_seqlens_k || p.b <= 0) return 0;
+    const size_t tiles = (size_t)p.b * p.hq * ((p.sk + 127) / 128) * ((p.sq + 127) / 128);
+    const size_t bytes = tiles * kDsTileBytes;
+    return bytes <= kDsWorkspaceLimit ? bytes : 0;
+}
+static size_t delta_bytes(const fa_bwd_params& p) { return (bwd_generic_workspace(p) + 255) & ~(size_t)255; }
+
+size_t bwd_sm100_workspace(const fa_bwd_params& p) { return delta_bytes(p) + ds_tiles_bytes(p); }
 
 template <typename T, int D>
 static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* delta, cudaStream_t st) {
@@ -692,6 +854,18 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
     auto k2 = bwd_dq_sm100_kernel<T, D>;
     const int smem = BwdSm100Smem<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+    if (a.ds_tiles) {
+        // five-GEMM path: the dQ kernel consumes the dS^T tiles the dK/dV kernel leaves, so it runs after it
+        auto k3 = bwd_dq_from_ds_sm100_kernel<T, D>;
+        const int smem3 = 3 * (2 * BwdSm100Smem<D>::kSub + BwdSm100Smem<D>::kTileB) + 256 + 1024;
+        if (int e = cuda_ok(cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, smem3), "cudaFuncSetAttribute")) return e;
+        dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g3((p.sq + 127) / 128, p.hq, p.b);
+        k1<<<g1, 608, smem, st>>>(a);
+        mark_kernel(st);
+        k3<<<g3, 192, smem3, st>>>(a);
+        mark_kernel(st);
+        return cuda_ok(cudaGetLastError(), "bwd_sm100 launch");
+    }
     const int smem_dq = 7 * BwdSm100Smem<D>::kTileB + 256 + 1024;     // Q, dO, three K stages, two V stages, barriers
     if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq), "cudaFuncSetAttribute")) return e;
     dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g2((p.sq + 127) / 128, p.hq, p.b);
@@ -740,6 +914,10 @@ int launch_bwd_sm100(const fa_bwd_params& p) {
     a.dv_sb = p.dv.stride_b; a.dv_ss = p.dv.stride_s; a.dv_sh = p.dv.stride_h;
     a.lse = p.lse; a.lse_sb = p.lse_stride_b; a.lse_sh = p.lse_stride_h; a.lse_ss = p.lse_stride_s;
     a.delta = reinterpret_cast<const float*>(p.workspace);
+    a.ds_tiles = nullptr; a.nkb = (p.sk + 127) / 128; a.nqb = (p.sq + 127) / 128;
+    if (g_ds_spill && ds_tiles_bytes(p) > 0 && p.workspace_bytes >= delta_bytes(p) + ds_tiles_bytes(p)) {
+        a.ds_tiles = reinterpret_cast<unsigned char*>(p.workspace) + delta_bytes(p);
+    }
     a.cu_q = p.cu_seqlens_q; a.cu_k = p.cu_seqlens_k;
     a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv;
     a.scale = p.scale; a.scale_log2 = p.scale * kLog2e;

@@ -22,7 +22,19 @@ struct DecodeArgs {
     int tokens_per_split;
     float* o_part;
     float* lse_part;
+    const int32_t* meta;          // scheduler-metadata blob or null
 };
+
+// Keys per split for sequence b: the blob's per-sequence figure when the blob was built for this launch (same batch
+// and split count) and for the length the kernel itself reads now; otherwise the host's uniform plan.  A blob of
+// another call shape, or one that has gone stale because the lengths moved on, is therefore ignored, never trusted.
+__device__ __forceinline__ int keys_per_split(const DecodeArgs& a, int b, int sk) {
+    const int32_t* m = a.meta;
+    if (!m || m[0] != kSchedMagic || m[1] != a.p.b || m[2] != a.nsplit) return a.tokens_per_split;
+    const int32_t* s = m + kSchedHeaderInts + kSchedSeqInts * b;
+    if (s[0] != sk || s[3] <= 0 || (long long)s[3] * a.nsplit < sk) return a.tokens_per_split;
+    return s[3];
+}
 
 constexpr int kDecStages = 3;
 
@@ -51,13 +63,14 @@ __global__ void __launch_bounds__(128) decode_splitkv_kernel(const DecodeArgs a)
     if (rows_total <= 0) return;
     const int wl = p.window_left, wr = p.causal ? 0 : p.window_right;
     const int rb = max(0, p.kv_begin), re = p.kv_end > 0 ? min(sk, p.kv_end) : sk;
+    const int tps = keys_per_split(a, b, sk);
 
     // token range of this split, intersected with what any row can see
     int lo_any, hi_any, tmp;
     window_bounds(0, sq, sk, wl, wr, lo_any, tmp);
     window_bounds(sq - 1, sq, sk, wl, wr, tmp, hi_any);
-    int t_begin = max(max(rb, lo_any), rb + split * a.tokens_per_split);
-    int t_end = min(min(re, hi_any + 1), rb + (split + 1) * a.tokens_per_split);
+    int t_begin = max(max(rb, lo_any), rb + split * tps);
+    int t_end = min(min(re, hi_any + 1), rb + (split + 1) * tps);
     t_begin = t_begin / kDecTile * kDecTile;
 
     int vrow[2], qpos[2], head[2], klo[2], khi[2];
@@ -71,8 +84,8 @@ __global__ void __launch_bounds__(128) decode_splitkv_kernel(const DecodeArgs a)
         klo[r] = 1; khi[r] = 0;
         if (ok) {
             window_bounds(qpos[r], sq, sk, wl, wr, klo[r], khi[r]);
-            klo[r] = max(max(klo[r], rb), rb + split * a.tokens_per_split);
-            khi[r] = min(min(khi[r], re - 1), rb + (split + 1) * a.tokens_per_split - 1);
+            klo[r] = max(max(klo[r], rb), rb + split * tps);
+            khi[r] = min(min(khi[r], re - 1), rb + (split + 1) * tps - 1);
         }
         slope[r] = p.alibi_slopes ? p.alibi_slopes[(int64_t)b * p.alibi_stride_b + head[r]] * kLog2e : 0.f;
     }
@@ -312,11 +325,12 @@ __global__ void __launch_bounds__(128) decode_tma_kernel(const __grid_constant__
     if (rows_total <= 0) return;
     const int wl = p.window_left, wr = p.causal ? 0 : p.window_right;
     const int rb = max(0, p.kv_begin), re = p.kv_end > 0 ? min(sk, p.kv_end) : sk;
+    const int tps = keys_per_split(a, b, sk);
     int lo_any, hi_any, tmp;
     window_bounds(0, sq, sk, wl, wr, lo_any, tmp);
     window_bounds(sq - 1, sq, sk, wl, wr, tmp, hi_any);
-    int t_begin = max(max(rb, lo_any), rb + split * a.tokens_per_split);
-    int t_end = min(min(re, hi_any + 1), rb + (split + 1) * a.tokens_per_split);
+    int t_begin = max(max(rb, lo_any), rb + split * tps);
+    int t_end = min(min(re, hi_any + 1), rb + (split + 1) * tps);
     t_begin = t_begin / TILE * TILE;
 
     int vrow[2], qpos[2], head[2], klo[2], khi[2];
@@ -330,8 +344,8 @@ __global__ void __launch_bounds__(128) decode_tma_kernel(const __grid_constant__
         klo[r] = 1; khi[r] = 0;
         if (ok) {
             window_bounds(qpos[r], sq, sk, wl, wr, klo[r], khi[r]);
-            klo[r] = max(max(klo[r], rb), rb + split * a.tokens_per_split);
-            khi[r] = min(min(khi[r], re - 1), rb + (split + 1) * a.tokens_per_split - 1);
+            klo[r] = max(max(klo[r], rb), rb + split * tps);
+            khi[r] = min(min(khi[r], re - 1), rb + (split + 1) * tps - 1);
         }
         slope[r] = p.alibi_slopes ? p.alibi_slopes[(int64_t)b * p.alibi_stride_b + head[r]] * kLog2e : 0.f;
     }
@@ -576,6 +590,8 @@ int launch_fwd_decode(const fa_fwd_params& p, const FwdPlan& plan, float* o_part
     a.tokens_per_split = plan.blocks_per_split * kGenericBN;
     a.o_part = o_part;
     a.lse_part = lse_part;
+    // the blob plans whole sequences; a call restricted to a key range keeps the host's uniform plan
+    a.meta = (p.kv_begin <= 0 && p.kv_end <= 0) ? reinterpret_cast<const int32_t*>(p.sched_meta) : nullptr;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
     const int dmax = p.d > p.dv ? p.d : p.dv;
     if (g_decode_use_tma && decode_tma_ok(p)) {

@@ -25,6 +25,11 @@ struct FwdPlan {
     int use_decode;      // warp-per-split decode kernel eligible
 };
 
+// scheduler-metadata blob (sched_meta.cu): header, then kSchedSeqInts entries per sequence
+constexpr int kSchedMagic = 0x46413130;
+constexpr int kSchedHeaderInts = 8;
+constexpr int kSchedSeqInts = 8;
+
 constexpr int kGenericBM = 64;
 constexpr int kGenericBN = 64;
 
@@ -69,6 +74,8 @@ int mla_pair_error_flag(bool clear);
 int launch_bwd_sm100(const fa_bwd_params& p);
 // 1 (default): the dQ kernel runs on an internal stream beside the dK/dV kernel (fa_debug_set key 6)
 void bwd_sm100_set_overlap(int v);
+// 1 (default): dense calls hand dS^T tiles from the dK/dV kernel to a one-GEMM dQ kernel (fa_debug_set key 7)
+void bwd_sm100_set_ds_spill(int v);
 // true while the caller has lent per-kernel timing events to this thread
 bool kernel_events_active();
 bool bwd_sm100_supported(const fa_bwd_params& p);

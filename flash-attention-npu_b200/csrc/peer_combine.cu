@@ -142,10 +142,10 @@ int peer_combine(const fa_peer_combine_params& c) {
     if (c.world < 1 || c.world > FA_MAX_PEERS || c.rank < 0 || c.rank >= c.world)
         return fail(FA_ERR_BAD_SHAPE, "peer combine: rank %d of %d (at most %d ranks)", c.rank, c.world, FA_MAX_PEERS);
     if (c.dv <= 0 || c.dv % 4 != 0) return fail(FA_ERR_BAD_SHAPE, "peer combine: dv must be a multiple of 4");
-    if (c.rows < 0 || c.status == nullptr || c.o == nullptr) return fail(FA_ERR_BAD_SHAPE, "peer combine: null argument");
+    if (c.rows < 0 || c.status == nullptr || (c.o == nullptr && c.rows > 0)) return fail(FA_ERR_BAD_SHAPE, "peer combine: null argument");
     if (c.slot_offset % 16 != 0 || c.lse_offset % 16 != 0 || c.flag_offset % 16 != 0)
         return fail(FA_ERR_BAD_SHAPE, "peer combine: offsets must be multiples of 16 bytes");
-    if (c.rows == 0) return FA_OK;
+    // a rank without rows of its own still signals and waits: the other ranks count on its flag
     PeerArgs a{};
     for (int r = 0; r < c.world; ++r) {
         if (c.peers[r] == nullptr) return fail(FA_ERR_BAD_SHAPE, "peer combine: buffer of rank %d is not mapped", r);
@@ -157,7 +157,7 @@ int peer_combine(const fa_peer_combine_params& c) {
     a.rank = c.rank; a.world = c.world; a.epoch = c.epoch; a.rows = c.rows; a.dv = c.dv;
     a.o_stride = c.o_stride; a.o = c.o; a.lse = c.lse; a.status = c.status;
     a.timeout_ns = (unsigned long long)(c.timeout_ms ? c.timeout_ms : 1000u) * 1000000ull;
-    dim3 grid((unsigned)((c.rows + kPeerWarps - 1) / kPeerWarps));
+    dim3 grid((unsigned)((c.rows + kPeerWarps - 1) / kPeerWarps > 0 ? (c.rows + kPeerWarps - 1) / kPeerWarps : 1));
     if (c.out_dtype == FA_F16) peer_combine_kernel<__half><<<grid, kPeerWarps * 32, 0, st>>>(a);
     else if (c.out_dtype == FA_BF16) peer_combine_kernel<__nv_bfloat16><<<grid, kPeerWarps * 32, 0, st>>>(a);
     else peer_combine_kernel<float><<<grid, kPeerWarps * 32, 0, st>>>(a);

@@ -30,6 +30,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrival that orders nothing but itself: for hand-offs of TENSOR-memory data, whose completion the thread has
+// already awaited (tcgen05.wait) and fenced (tcgen05.fence::before_thread_sync).  The default arrival is a release
+// and first waits until the thread's earlier global stores have been performed, which puts the latency of
+// unrelated stores on the hand-off.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -173,6 +180,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+// Plain (untiled) bulk copy of `bytes` contiguous bytes from global to this CTA's shared memory; both addresses
+// 16-byte aligned, `bytes` a multiple of 16; completes on `bar` like a tile load.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -200,6 +213,18 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= static_cast<uint64_t>(1) << 46;     // descriptor version (sm_100)
     d |= static_cast<uint64_t>(2) << 61;     // SWIZZLE_128B
+    return d;
+}
+// Shared-memory matrix descriptor WITHOUT swizzle for an MN-major operand stored as [chunk of 8 MN elements][k][16 bytes]:
+// eight consecutive k rows of one chunk are a contiguous 128-byte core matrix; `k_group_bytes` = distance between
+// 8-row groups along K (leading offset), `mn_chunk_bytes` = distance between neighbouring 8-element chunks along MN
+// (stride offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_noswizzle(uint32_t saddr, uint32_t k_group_bytes, uint32_t mn_chunk_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>((k_group_bytes >> 4) & 0x3FFF) << 16;
+    d |= static_cast<uint64_t>((mn_chunk_bytes >> 4) & 0x3FFF) << 32;
+    d |= static_cast<uint64_t>(1) << 46;     // descriptor version (sm_100)
     return d;
 }
 // Descriptor of the same tile `byte_off` further on (the start-address field counts 16-byte units and

@@ -206,20 +206,26 @@ class PeerExchange:
         o, l, _ = self.views(self.rank, self.epoch)
         return o, l
 
-    def combine(self, out_dtype=torch.bfloat16):
-        """Signal, bounded wait, combine over peer memory -> out (rows, dv), lse (rows).  `check()` reports a timeout."""
+    def combine(self, out_dtype=torch.bfloat16, row_begin: int = 0, row_end: int = None):
+        """Signal, bounded wait, combine over peer memory -> out (rows, dv), lse (rows).  `check()` reports a timeout.
+        With a row range only rows [row_begin, row_end) are combined (and returned): when every rank needs the
+        result of its OWN sequences only, each combines its own range and the bytes that cross NVLink drop by the
+        number of ranks.  All ranks still make the call (the signals are per call, not per row)."""
         C, capi = self._C, self._capi
-        out = torch.empty(self.rows, self.dv, dtype=out_dtype, device=self.device)
-        lse = torch.empty(self.rows, dtype=torch.float32, device=self.device)
+        row_end = self.rows if row_end is None else row_end
+        n = max(0, row_end - row_begin)
+        out = torch.empty(n, self.dv, dtype=out_dtype, device=self.device)
+        lse = torch.empty(n, dtype=torch.float32, device=self.device)
         c = capi.PeerCombineParams()
         c.rank, c.world = self.rank, self.world
         for r, p in enumerate(self.ptrs):
             c.peers[r] = p
-        c.slot_offset = self._slot(self.epoch)
-        c.lse_offset = c.slot_offset + self.o_bytes
-        c.flag_offset = c.lse_offset + self.l_bytes
+        slot = self._slot(self.epoch)
+        c.slot_offset = slot + row_begin * self.dv * 4
+        c.lse_offset = slot + self.o_bytes + row_begin * 4
+        c.flag_offset = slot + self.o_bytes + self.l_bytes
         c.epoch, c.timeout_ms = self.epoch, self.timeout_ms
-        c.rows, c.dv = self.rows, self.dv
+        c.rows, c.dv = n, self.dv
         c.out_dtype = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[out_dtype]
         c.o, c.o_stride, c.lse, c.status = out.data_ptr(), self.dv, lse.data_ptr(), self.status.data_ptr()
         c.stream = capi.stream_ptr(self.device)

@@ -167,10 +167,13 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k_, leftpad_k_
 def kvcache_forward(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_, cache_batch_idx_,
                     block_table_, alibi_slopes_, out_, softmax_scale, is_causal, window_size_left,
                     window_size_right, softcap, is_rotary_interleaved, num_splits,
-                    cu_seqlens_q=None, max_seqlen_q=None, kv_range=None, partials=None):
+                    cu_seqlens_q=None, max_seqlen_q=None, kv_range=None, partials=None, sched_meta=None):
     """Shared by the v2 and v3 kvcache entry points.  q (B,Sq,H,D) or packed (Tq,H,D) with
     cu_seqlens_q.  kv_range=(begin,end) and partials=(o fp32, lse fp32) select the
-    cross-device KV-sharded mode, where fp32 partial results are left for a later combine."""
+    cross-device KV-sharded mode, where fp32 partial results are left for a later combine.
+    sched_meta: the device blob of get_scheduler_metadata (uint8 or int32 view); the split-KV decode kernels take
+    every sequence's keys per split from it (a blob built for another batch, split count or for other lengths is
+    ignored on the device, so a stale blob costs balance, never correctness)."""
     _common_checks(q, kcache, vcache, softcap, what="key_cache")
     packed_q = cu_seqlens_q is not None
     if packed_q:
@@ -246,6 +249,13 @@ def kvcache_forward(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_s
     if partials is not None:
         p.partials_only = 1
         p.o_partial, p.lse_partial = partials[0].data_ptr(), partials[1].data_ptr()
+    if sched_meta is not None:
+        capi.require_cuda(sched_meta)
+        if sched_meta.dtype not in (torch.uint8, torch.int32) or not sched_meta.is_contiguous():
+            raise RuntimeError("scheduler_metadata must be the contiguous uint8 / int32 tensor get_scheduler_metadata returned")
+        if sched_meta.numel() * sched_meta.element_size() < 4 * lib.fa_scheduler_metadata_ints(batch) or sched_meta.data_ptr() % 4:
+            raise RuntimeError("scheduler_metadata is too small for this batch size")
+        p.sched_meta = sched_meta.data_ptr()
     keep = _alibi(p, alibi_slopes_, batch, hq)
     ws = capi.workspace(lib.fa_fwd_workspace_bytes(p), q.device)
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()

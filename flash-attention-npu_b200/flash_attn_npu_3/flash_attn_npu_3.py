@@ -36,13 +36,15 @@ def fwd(q, k, v, k_new, v_new, qv, out_, cu_seqlens_q, cu_seqlens_k, cu_seqlens_
         softmax_scale = q.shape[-1] ** (-0.5)
     cache_like = page_table is not None or seqused_k is not None or k_new is not None or kv_batch_idx is not None
     if cache_like:
-        # scheduler_metadata only carries the split count decided on the device-resident lengths;
-        # the kernels read the lengths themselves, so the call is sync-free with or without it.
+        # The kernels read the lengths themselves, so the call is sync-free with or without the blob; with it the
+        # split-KV decode takes each sequence's keys per split from the device-side plan (flash_api.cpp:248-267
+        # takes its tiling from the blob in the same way).
         out, lse = _v2.kvcache_forward(q, k, v, k_new, v_new, seqused_k, rotary_cos, rotary_sin, kv_batch_idx,
                                        page_table, None, out_, softmax_scale, is_causal, window_size_left,
                                        window_size_right, softcap, is_rotary_interleaved,
                                        num_splits if num_splits is not None else 0,
-                                       cu_seqlens_q=cu_seqlens_q, max_seqlen_q=max_seqlen_q)
+                                       cu_seqlens_q=cu_seqlens_q, max_seqlen_q=max_seqlen_q,
+                                       sched_meta=scheduler_metadata)
         return [out, lse, None, None]
     if cu_seqlens_q is not None:
         out, lse, _, _ = _v2.varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, None, None, None, None,

@@ -100,7 +100,11 @@ typedef struct {
     float*  lse_partial;           /* (splits, rows) fp32                              */
     void*   workspace;             /* >= fa_fwd_workspace_bytes()                      */
     size_t  workspace_bytes;
-    const void* sched_meta;        /* blob from fa_scheduler_metadata, or null         */
+    const void* sched_meta;        /* blob from fa_scheduler_metadata, or null.  The
+                                    * split-KV decode kernels take every sequence's keys
+                                    * per split from it; a blob built for another batch
+                                    * size, split count or for other lengths is ignored
+                                    * on the device (the host's uniform plan runs).     */
     void*   stream;                /* cudaStream_t                                     */
 } fa_fwd_params;
 
@@ -178,7 +182,12 @@ int fa_combine(const fa_combine_params* p);
  * fa_peer_combine then signals the peers, waits (bounded) for their signals and
  * combines all ranks' partials with loads over NVLink, without a library
  * collective.  All ranks make the same sequence of calls with epoch = 1, 2, ...
- * and alternate between two slots (slot = epoch & 1).
+ * and alternate between two slots (slot = epoch & 1).  A rank may combine only
+ * a range of the rows (slot_offset / lse_offset advanced to the first row, rows
+ * = the count; rows = 0 is allowed and still signals): when every rank needs
+ * the result of its own sequences only, the bytes crossing NVLink drop by the
+ * number of ranks.  If `status` comes back non-zero the contents of `o` are
+ * undefined and the exchange must be rebuilt before its next use.
  * ---------------------------------------------------------------------- */
 #define FA_MAX_PEERS 16
 #define FA_PEER_HANDLE_BYTES 64
@@ -204,7 +213,8 @@ typedef struct {
     int64_t  o_stride;
     float*   lse;                   /* (rows) or null                                          */
     int32_t* status;                /* device int, stays 0 on success; 1 + r if rank r's signal
-                                     * did not arrive in time (nothing is written to o then)   */
+                                     * did not arrive in time (o is then undefined: blocks that
+                                     * saw the signal in time may have written their rows)     */
     void*    stream;
 } fa_peer_combine_params;
 
@@ -250,8 +260,17 @@ int    fa_mla_num_splits(const fa_mla_params* p);
 /* ------------------------------------------------------------------------
  * Device-side schedule for the kvcache forward: get_scheduler_metadata
  * csrc/ascend910/flash_attn_npu_3/flash_api.cpp:506-571 (ComputeFAMetadata,
- * fa_metadata.aicpu:32-151).  Fills `meta` (int32, fa_scheduler_metadata_ints()
- * entries) on the stream from the device-resident lengths, without a host sync.
+ * fa_metadata.aicpu:32-151); the forward that takes its tiling from the blob
+ * instead of planning on the host is flash_api.cpp:248-267 there.  Fills `meta`
+ * (int32, fa_scheduler_metadata_ints(b) = 8 + 8 b entries) on the stream from
+ * the device-resident lengths, without a host sync:
+ *   [0] magic  [1] b  [2] split count of the launch grid  [3] 64-key blocks per
+ *   split of the host plan  [4] longest sequence  [5] total blocks  [6] active
+ *   (sequence, split) pairs  [7] 0; then per sequence: length, blocks, active
+ *   splits, keys per active split (the sequence's keys spread evenly), prefix of
+ *   active splits, 0, 0, 0.
+ * `sk` must be the capacity the forward call will pass (page-table width x page
+ * size, or the rows of a dense cache), since the grid is planned from it.
  * ---------------------------------------------------------------------- */
 typedef struct {
     const int32_t* seqused_k;   /* (b) */

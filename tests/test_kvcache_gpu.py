@@ -240,11 +240,12 @@ def test_kv_range_partials_recombine_to_the_full_result():
     assert (lse.reshape(b, h, 1) - full_lse).abs().max().item() < 1e-4
 
 
-def test_scheduler_metadata_matches_host_computation():
+def test_scheduler_metadata_blob_layout():
+    """The device-built blob against the same plan worked out on the host from the lengths (layout: sched_meta.cu)."""
     import flash_attn_npu_3 as m3
-    import fa_b200_capi as capi
     lens = torch.tensor([1000, 64, 65, 7000, 1], dtype=torch.int32)
     meta = m3.get_scheduler_metadata(5, 1, 8192, 32, 8, 128, lens.cuda(), page_size=256, causal=True).view(torch.int32).cpu()
+    assert meta.numel() == 8 + 8 * 5
     assert meta[0].item() == 0x46413130 and meta[1].item() == 5
     nsplit, bps = meta[2].item(), meta[3].item()
     assert meta[4].item() == 7000
@@ -253,17 +254,82 @@ def test_scheduler_metadata_matches_host_computation():
     run = 0
     for i, l in enumerate(lens.tolist()):
         act = min(nsplit, (nb[i] + bps - 1) // bps)
-        assert meta[8 + 4 * i: 12 + 4 * i].tolist() == [l, nb[i], act, run]
+        per = ((l + act - 1) // act + 63) // 64 * 64
+        assert meta[8 + 8 * i: 13 + 8 * i].tolist() == [l, nb[i], act, per, run]
+        assert act * per >= l
         run += act
     assert meta[6].item() == run
-    # the blob is accepted by the kvcache call and does not change the result
-    torch.manual_seed(3)
-    kc, vc = torch.randn(5, 8192, 8, 128).bfloat16().cuda(), torch.randn(5, 8192, 8, 128).bfloat16().cuda()
-    q = torch.randn(5, 1, 32, 128).bfloat16().cuda()
-    a = m3.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=lens.cuda(), causal=True,
-                                   scheduler_metadata=meta.cuda().view(torch.uint8))
-    b_ = m3.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=lens.cuda(), causal=True)
-    assert torch.equal(a, b_)
+
+
+def test_scheduler_metadata_is_consumed_by_the_decode():
+    """Configuration 4's length spread, scaled down: with the blob every sequence spreads its keys evenly over the
+    splits it needs, so fewer (sequence, split) pairs are active than the grid has and no active split is nearly
+    empty; the result matches the oracle exactly as the call without the blob does.  A blob built for other
+    lengths is ignored (the call still gives the right answer)."""
+    import flash_attn_npu_3 as m3
+    import fa_b200_capi as capi
+    gen = torch.Generator().manual_seed(14)
+    b, h, hkv, d, page = 16, 32, 8, 128, 256
+    lens = torch.randint(1024, 32769, (b,), generator=gen, dtype=torch.int32)
+    kc, vc, table = paged_setup(gen, b, lens.tolist(), hkv, d, page, torch.bfloat16, extra=0)
+    q = torch.randn(b, 1, h, d, generator=gen).bfloat16()
+    cap = table.shape[1] * page
+    meta = m3.get_scheduler_metadata(b, 1, cap, h, hkv, d, lens.cuda(), page_size=page, causal=True)
+    hdr = meta.view(torch.int32).cpu()
+    nsplit, active = hdr[2].item(), hdr[6].item()
+    assert nsplit > 1 and active < b * nsplit                       # a grid of b x nsplit, only `active` pairs do work
+    kg, vg, tg, lg, qg = kc.cuda(), vc.cuda(), table.cuda(), lens.cuda(), q.cuda()
+    with_blob, lse_a, *_ = m3.flash_attn_with_kvcache(qg, kg, vg, cache_seqlens=lg, page_table=tg, causal=True,
+                                                      scheduler_metadata=meta, return_softmax_lse=True)
+    assert capi.last_kernel() == "decode_splitkv_tma"
+    without, lse_b, *_ = m3.flash_attn_with_kvcache(qg, kg, vg, cache_seqlens=lg, page_table=tg, causal=True, return_softmax_lse=True)
+    # What the kernel did with the blob, seen through the partial LSEs it left in the workspace of a call made
+    # straight through the C-ABI: a split without keys leaves -inf.  With the blob exactly the planned number of
+    # splits per sequence carry keys and every one of them carries its even share.
+    from fa_b200_capi import FwdParams, tensor4
+    out_c, lse_c = torch.empty_like(qg), torch.empty(b, h, 1, device="cuda")
+    p = FwdParams()
+    p.q, p.k, p.v, p.o = tensor4(qg), tensor4(kg), tensor4(vg), tensor4(out_c)
+    p.lse, p.lse_stride_b, p.lse_stride_h, p.lse_stride_s = lse_c.data_ptr(), lse_c.stride(0), lse_c.stride(1), lse_c.stride(2)
+    p.block_table, p.block_table_stride, p.page_size, p.seqused_k = tg.data_ptr(), tg.stride(0), page, lg.data_ptr()
+    p.b, p.sq, p.sk, p.hq, p.hkv, p.d, p.dv = b, 1, cap, h, hkv, d, d
+    p.scale, p.causal, p.window_left, p.window_right, p.dtype = d ** -0.5, 1, -1, -1, 1
+    p.stream = torch.cuda.current_stream().cuda_stream
+    assert capi.lib.fa_fwd_num_splits(p) == nsplit
+    ws = torch.zeros(capi.lib.fa_fwd_workspace_bytes(p), dtype=torch.uint8, device="cuda")
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    rows = b * h
+    o_bytes = (nsplit * rows * d * 4 + 255) // 256 * 256
+    plan = hdr[8:].reshape(b, 8)
+    for blob in (None, meta):
+        p.sched_meta = None if blob is None else blob.data_ptr()
+        assert capi.lib.fa_fwd_kvcache(p) == 0, capi.lib.fa_last_error()
+        torch.cuda.synchronize()
+        part = ws[o_bytes: o_bytes + nsplit * rows * 4].view(torch.float32).view(nsplit, b, h)
+        used = torch.isfinite(part[:, :, 0]).sum(0).cpu()                # splits with keys, per sequence
+        if blob is None:
+            uniform_used = used
+        else:
+            assert used.tolist() == plan[:, 2].tolist()                   # the blob's active splits, no more, no fewer
+            assert (used <= uniform_used).all() and used.sum().item() == active
+        assert torch.equal(out_c, with_blob if blob is not None else without)
+    for i in torch.argsort(lens).tolist()[:3]:
+        L = int(lens[i])
+        ki, vi = orc.gather_paged(kc, table[i], L).unsqueeze(0), orc.gather_paged(vc, table[i], L).unsqueeze(0)
+        lp_o, _ = orc.attention_fwd(q[i:i + 1], ki, vi, d ** -0.5, True)
+        f_o, f_l = orc.attention_fwd(q[i:i + 1].float(), ki.float(), vi.float(), d ** -0.5, True, data_type=torch.float32)
+        for out, lse in ((with_blob, lse_a), (without, lse_b)):
+            assert_within("out", out[i:i + 1].cpu(), lp_o, f_o)
+            assert_lse(lse[i:i + 1], f_l)
+    assert (with_blob.float() - without.float()).abs().max().item() <= 2 ** -7
+    stale = m3.get_scheduler_metadata(b, 1, cap, h, hkv, d, (lens // 2).cuda(), page_size=page, causal=True)
+    again = m3.flash_attn_with_kvcache(qg, kg, vg, cache_seqlens=lg, page_table=tg, causal=True, scheduler_metadata=stale)
+    assert torch.equal(again, without)                              # ignored: the host's uniform plan ran
+    other = m3.get_scheduler_metadata(b + 1, 1, cap, h, hkv, d, torch.cat((lens, lens[:1])).cuda(), page_size=page, causal=True)
+    again = m3.flash_attn_with_kvcache(qg, kg, vg, cache_seqlens=lg, page_table=tg, causal=True, scheduler_metadata=other)
+    assert torch.equal(again, without)
+    with pytest.raises(RuntimeError):
+        m3.flash_attn_with_kvcache(qg, kg, vg, cache_seqlens=lg, page_table=tg, causal=True, scheduler_metadata=meta[:16])
 
 
 @pytest.mark.parametrize("paged,page", [(True, 128), (True, 256), (False, 0)])
