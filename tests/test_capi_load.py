@@ -71,4 +71,4 @@ def test_split_planner_is_host_only():
     assert capi.lib.fa_fwd_num_splits(p) == 1 and capi.lib.fa_fwd_workspace_bytes(p) == 0
     p.num_splits = 4
     assert capi.lib.fa_fwd_num_splits(p) == 4
-    assert capi.lib.fa_scheduler_metadata_ints(16) == 8 + 64
+    assert capi.lib.fa_scheduler_metadata_ints(16) == 8 + 8 * 16
