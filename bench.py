@@ -45,8 +45,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 L2_BYTES = 126e6
 
 # DRAM bytes of one dK/dV launch at B2 S4096 H32 D128 causal in the committed ncu capture of that kernel
-# (dram__bytes_read.sum 270.8 MB + dram__bytes_write.sum 107.1 MB); the traffic grows in proportion to the batch
-DKDV_TRAFFIC_B2 = 270.8e6 + 107.1e6
+# (dram__bytes_read.sum 278.8 MB + dram__bytes_write.sum 1203.7 MB, of which 1107 MB are the dS tiles it hands to the dQ
+# kernel); the traffic grows in proportion to the batch
+DKDV_TRAFFIC_B2 = 278.8e6 + 1203.7e6
 
 
 def measured_peaks():
@@ -855,9 +856,11 @@ def main():
     share = 1.0 / world                                    # rank 0's part of the batch (equal item costs)
     parts = [("fwd:" + c2["fwd_kernel"], fwd_ms, FWD_FLOPS * share)]
     names = ["bwd:delta", "bwd:dk_dv", "bwd:dq"] if len(bwd_parts) == 3 else [f"bwd:{j}" for j in range(len(bwd_parts))]
-    # flops per backward launch: the dK/dV pass recomputes S and dP (2) and does dV, dK (2); the dQ pass S, dP, dQ (3)
+    # flops per backward launch: the dK/dV pass computes S, dP, dV, dK (4 GEMMs); the dQ pass multiplies the dS tiles the
+    # dK/dV pass left in the workspace (1 GEMM), or recomputes S and dP first (3) when the call takes that path
     unit = FWD_FLOPS * share / 2.0
-    flops_of = {"bwd:delta": 0.0, "bwd:dk_dv": 4 * unit, "bwd:dq": 3 * unit}
+    five = c2["bwd_kernel"].endswith("5gemm")
+    flops_of = {"bwd:delta": 0.0, "bwd:dk_dv": 4 * unit, "bwd:dq": (1 if five else 3) * unit}
     for n, t in zip(names, bwd_parts):
         parts.append((n, t, flops_of.get(n, BWD_FLOPS * share)))
     dom = max(parts, key=lambda x: x[1])
@@ -893,8 +896,9 @@ def main():
                                        "B2 case, scaled by the batch entries x heads one launch covers",
                      "peak_source": peaks["_source"] + (" sustained" if sustained else " burst") + " cuBLAS bf16",
                      "frac_of_nominal_2250": achieved / 2250.0,
-                     "per_rank": "rank 0's launches", "flops_counted": "executed by that launch (the two-kernel backward runs 7 GEMMs "
-                                                                        "where the algorithm counts 5)",
+                     "per_rank": "rank 0's launches", "flops_counted": "executed by that launch (dK/dV pass: 4 GEMMs; dQ pass: 1 GEMM over the stored dS "
+                                                                        "tiles, so the backward executes the algorithm's 5)" if five else
+                                                        "executed by that launch (this call recomputes S and dP in the dQ pass: 7 GEMMs for 5)",
                      "fwd_frac": FWD_FLOPS * share / (fwd_ms * 1e-3) / 1e12 / peak,
                      "bwd_frac_algorithmic": BWD_FLOPS * share / (bwd_ms * 1e-3) / 1e12 / peak},
         "gpu_launches": c2["launches_per_step"] * args.steps * args.repeats,

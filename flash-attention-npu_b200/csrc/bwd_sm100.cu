@@ -924,7 +924,7 @@ int launch_bwd_sm100(const fa_bwd_params& p) {
     a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
     float* delta = reinterpret_cast<float*>(p.workspace);
-    note_kernel("sm100_tcgen05_bwd");
+    note_kernel(a.ds_tiles ? "sm100_tcgen05_bwd_5gemm" : "sm100_tcgen05_bwd");
     if (p.dtype == FA_F16) return p.d == 64 ? launch_bwd_sm100_t<__half, 64>(p, a, delta, st) : launch_bwd_sm100_t<__half, 128>(p, a, delta, st);
     return p.d == 64 ? launch_bwd_sm100_t<__nv_bfloat16, 64>(p, a, delta, st) : launch_bwd_sm100_t<__nv_bfloat16, 128>(p, a, delta, st);
 }

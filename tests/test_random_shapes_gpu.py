@@ -57,7 +57,7 @@ def test_dense_forward_backward_random(seed):
 
     (o1, l1, dq1, dk1, dv1, f1), b1 = _run(0, call)
     (o2, l2, dq2, dk2, dv2, f2), b2 = _run(1, call)
-    assert f1.startswith("sm100_tcgen05") and b1 == "sm100_tcgen05_bwd", (f1, b1)
+    assert f1.startswith("sm100_tcgen05") and b1.startswith("sm100_tcgen05_bwd"), (f1, b1)
     assert f2 == "generic_mma" and b2 == "generic_mma_bwd", (f2, b2)
     assert capi.lib.fa_debug_get(2) == 0
     tag = f"seed {seed}: b{b} sq{sq} sk{sk} h{h}/{hkv} d{d} {mode} ({wl},{wr}) {dt}"
@@ -102,7 +102,7 @@ def test_packed_forward_backward_random(seed):
 
     (o1, dq1, dk1, dv1), b1 = _run(0, call)
     (o2, dq2, dk2, dv2), b2 = _run(1, call)
-    assert b1 == "sm100_tcgen05_bwd" and b2 == "generic_mma_bwd", (b1, b2)
+    assert b1.startswith("sm100_tcgen05_bwd") and b2 == "generic_mma_bwd", (b1, b2)
     assert capi.lib.fa_debug_get(2) == 0
     tag = f"seed {seed}: lens {lens} h{h}/{hkv} d{d} causal {causal}"
     _close(o1, o2, tag + " out")
