@@ -27,7 +27,6 @@
 #include "fa_utils.cuh"
 #include "fa_internal.h"
 #include "sm100_ptx.cuh"
-#include <mutex>
 
 namespace fa {
 
@@ -789,23 +788,6 @@ __global__ void __launch_bounds__(256) bwd_delta_sm100_kernel(const fa_bwd_param
     }
 }
 
-static int g_overlap = 1;
-void bwd_sm100_set_overlap(int v) { g_overlap = v; }
-
-// one internal non-blocking stream per device, created on first use
-static cudaStream_t side_stream() {
-    static std::mutex mu;
-    static cudaStream_t streams[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    std::lock_guard<std::mutex> lock(mu);
-    if (!streams[dev] && cudaStreamCreateWithFlags(&streams[dev], cudaStreamNonBlocking) != cudaSuccess) {
-        streams[dev] = nullptr;
-        cudaGetLastError();
-    }
-    return streams[dev];
-}
-
 // 1 (default): dense calls hand dS^T from the dK/dV kernel to a one-GEMM dQ kernel through the workspace;
 // 0: the dQ kernel always recomputes S and dP (fa_debug_set key 7)
 static int g_ds_spill = 1;
@@ -869,32 +851,12 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
     const int smem_dq = 7 * BwdSm100Smem<D>::kTileB + 256 + 1024;     // Q, dO, three K stages, two V stages, barriers
     if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq), "cudaFuncSetAttribute")) return e;
     dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g2((p.sq + 127) / 128, p.hq, p.b);
-    // dK/dV and dQ are independent of each other (both need only delta): the dQ kernel goes to an internal stream
-    // that is forked from and joined back into the caller's stream, so that its CTAs fill the SMs the last wave of
-    // the dK/dV kernel leaves idle.  With per-kernel timing events lent, the two run one after the other instead.
-    cudaStream_t side = (g_overlap && !kernel_events_active()) ? side_stream() : nullptr;
-    cudaEvent_t fork = nullptr, join = nullptr;
-    if (side && (cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) != cudaSuccess ||
-                 cudaEventCreateWithFlags(&join, cudaEventDisableTiming) != cudaSuccess)) {
-        if (fork) cudaEventDestroy(fork);
-        fork = nullptr;
-        side = nullptr;
-        cudaGetLastError();
-    }
-    if (side) {
-        cudaEventRecord(fork, st);
-        cudaStreamWaitEvent(side, fork, 0);
-    }
+    // packed calls and calls beyond the workspace limit: the dQ kernel recomputes S and dP; both kernels on the
+    // caller's stream, one after the other
     k1<<<g1, 608, smem, st>>>(a);
     mark_kernel(st);
-    k2<<<g2, 608, smem_dq, side ? side : st>>>(a);
+    k2<<<g2, 608, smem_dq, st>>>(a);
     mark_kernel(st);
-    if (side) {
-        cudaEventRecord(join, side);
-        cudaStreamWaitEvent(st, join, 0);
-        cudaEventDestroy(fork);          // released once the recorded work has completed
-        cudaEventDestroy(join);
-    }
     return cuda_ok(cudaGetLastError(), "bwd_sm100 launch");
 }
 

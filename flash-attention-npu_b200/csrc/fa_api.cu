@@ -313,7 +313,6 @@ void fa_debug_set(int key, int value) {
     if (key == 3) { fa::sm100_error_flag(true); fa::decode_error_flag(true); }
     if (key == 4) fa::decode_set_use_tma(value);
     if (key == 5) g_mla_variant = value;
-    if (key == 6) fa::bwd_sm100_set_overlap(value);
     if (key == 7) fa::bwd_sm100_set_ds_spill(value);
 }
 int fa_debug_get(int key) {

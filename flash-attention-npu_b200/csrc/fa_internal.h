@@ -72,8 +72,6 @@ int launch_mla_pair(const fa_mla_params& p, int nsplit, int tokens_per_split, fl
                     int final_direct, cudaStream_t st);
 int mla_pair_error_flag(bool clear);
 int launch_bwd_sm100(const fa_bwd_params& p);
-// 1 (default): the dQ kernel runs on an internal stream beside the dK/dV kernel (fa_debug_set key 6)
-void bwd_sm100_set_overlap(int v);
 // 1 (default): dense calls hand dS^T tiles from the dK/dV kernel to a one-GEMM dQ kernel (fa_debug_set key 7)
 void bwd_sm100_set_ds_spill(int v);
 // true while the caller has lent per-kernel timing events to this thread

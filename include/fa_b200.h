@@ -297,9 +297,9 @@ void        fa_set_kernel_policy(int policy);
  * tcgen05 forward (set), key 2 = error code left by a timed-out wait in a tcgen05 kernel (get;
  * synchronises the device), key 3 = clear that code (set), key 4 = 0 makes the decode kernel load
  * cache tiles with 16-byte cp.async copies instead of TMA (set), key 5 = 1 makes the int8 latent
- * decode use its single-CTA tcgen05 kernel instead of the CTA-pair one (set), key 6 = 0 keeps the
- * two tcgen05 backward kernels on the caller's stream one after the other instead of running the dQ
- * kernel on an internal stream beside the dK/dV kernel (set). */
+ * decode use its single-CTA tcgen05 kernel instead of the CTA-pair one (set), key 7 = 0 makes the tcgen05
+ * backward recompute S and dP in its dQ kernel instead of reading the dS tiles the dK/dV kernel leaves in the
+ * workspace (set). */
 void        fa_debug_set(int key, int value);
 int         fa_debug_get(int key);
 
