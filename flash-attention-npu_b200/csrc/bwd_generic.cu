@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(128) bwd_dkdv_kernel(const fa_bwd_params p, co
         cp_async_commit();
         const int gi = step / nmb, mb = mb_lo + step % nmb;
         const int h = hk * G + gi;
+        const float slope = p.alibi_slopes ? p.alibi_slopes[(int64_t)b * p.alibi_stride_b + h] * kLog2e : 0.f;
         const uint32_t sQs = smem_u32(sQ) + stage * BM * PITCH, sdOs = smem_u32(sdO) + stage * BM * PITCH;
 
         // ---- M-phase: this warp owns query rows [16 warp, +16) ------------------------------
@@ -185,6 +186,7 @@ __global__ void __launch_bounds__(128) bwd_dkdv_kernel(const fa_bwd_params p, co
             const bool ok = i < sq;
             int lo = 1, hi = 0;
             float lse2 = INFINITY, dl = 0.f;
+            const float rel = (float)(i + sk - sq);      // alibi: distance of key j is |rel - j|
             if (ok) {
                 window_bounds(i, sq, sk, wl, wr, lo, hi);
                 const int64_t tok = (int64_t)sq_.q_off + i;
@@ -199,6 +201,7 @@ __global__ void __launch_bounds__(128) bwd_dkdv_kernel(const fa_bwd_params p, co
                     float x = s[nt][2 * r + e], fac = 1.f;
                     if (has_cap) { const float th = tanhf(x * cap_in); x = cap_out * th; fac = 1.f - th * th; }
                     else x *= scale_log2;
+                    if (p.alibi_slopes) x -= slope * fabsf(rel - (float)col);
                     const float pr = (col >= lo && col <= hi) ? exp2f(x - lse2) : 0.f;
                     s[nt][2 * r + e] = pr;
                     dp[nt][2 * r + e] = pr * (dp[nt][2 * r + e] - dl) * fac;
@@ -316,6 +319,7 @@ __global__ void __launch_bounds__(128) bwd_dq_kernel(const fa_bwd_params p, cons
     const bool has_cap = p.softcap > 0.f;
     const float cap_in = has_cap ? p.scale / p.softcap : 0.f;
     const float cap_out = p.softcap * kLog2e;
+    const float slope = p.alibi_slopes ? p.alibi_slopes[(int64_t)b * p.alibi_stride_b + h] * kLog2e : 0.f;
     const int ksteps = ceil_div(p.d, 16), vsteps = ceil_div(p.dv_dim, 16);
 
     for (int nb = nb_lo; nb < nb_hi; ++nb) {
@@ -367,6 +371,7 @@ __global__ void __launch_bounds__(128) bwd_dq_kernel(const fa_bwd_params p, cons
                     float x = s[nt][2 * r + e], fac = 1.f;
                     if (has_cap) { const float th = tanhf(x * cap_in); x = cap_out * th; fac = 1.f - th * th; }
                     else x *= scale_log2;
+                    if (p.alibi_slopes) x -= slope * fabsf((float)(m0 + warp * 16 + g + r * 8 + sk - sq - col));
                     const float pr = (col >= lo[r] && col <= hi[r]) ? exp2f(x - lse2[r]) : 0.f;
                     dp[nt][2 * r + e] = pr * (dp[nt][2 * r + e] - dl[r]) * fac;
                 }

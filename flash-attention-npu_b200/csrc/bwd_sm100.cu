@@ -27,6 +27,7 @@
 #include "fa_utils.cuh"
 #include "fa_internal.h"
 #include "sm100_ptx.cuh"
+#include <atomic>
 
 namespace fa {
 
@@ -790,12 +791,12 @@ __global__ void __launch_bounds__(256) bwd_delta_sm100_kernel(const fa_bwd_param
 
 // 1 (default): dense calls hand dS^T from the dK/dV kernel to a one-GEMM dQ kernel through the workspace;
 // 0: the dQ kernel always recomputes S and dP (fa_debug_set key 7)
-static int g_ds_spill = 1;
+static std::atomic<int> g_ds_spill{1};
 void bwd_sm100_set_ds_spill(int v) { g_ds_spill = v; }
 
 bool bwd_sm100_supported(const fa_bwd_params& p) {
     if (p.d != p.dv_dim || (p.d != 64 && p.d != 128)) return false;
-    if (p.softcap > 0.f || !(p.scale > 0.f)) return false;
+    if (p.softcap > 0.f || p.alibi_slopes || !(p.scale > 0.f)) return false;
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
     if (p.sq <= 0 || p.sk <= 0) return false;
     if (p.cu_seqlens_q && (p.total_q <= 0 || p.total_k <= 0)) return false;

@@ -13,6 +13,7 @@
 #include "fa_utils.cuh"
 #include "fa_internal.h"
 #include "sm100_ptx.cuh"
+#include <atomic>
 
 namespace fa {
 
@@ -572,7 +573,7 @@ static int launch_decode_t(const DecodeArgs& a, cudaStream_t st) {
     return cuda_ok(cudaGetLastError(), "decode_splitkv launch");
 }
 
-static int g_decode_use_tma = 1;
+static std::atomic<int> g_decode_use_tma{1};
 void decode_set_use_tma(int v) { g_decode_use_tma = v; }
 
 bool fwd_decode_supported(const fa_fwd_params& p) {

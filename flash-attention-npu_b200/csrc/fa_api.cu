@@ -1,5 +1,6 @@
 // C-ABI entry points of libfa_b200.so: argument validation, launch planning, dispatch.
 // Nothing here allocates, synchronises or reads device memory.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -9,8 +10,7 @@ namespace fa {
 
 static thread_local char g_err[512] = "";
 static thread_local const char* g_kernel = "";
-static int g_policy = 0;
-static int g_mla_variant = 0;     // 0: CTA-pair latent decode, 1: single-CTA kernel (fa_debug_set key 5)
+static std::atomic<int> g_policy{0};          // process-wide test switch (fa_set_kernel_policy)
 // optional per-kernel timing: the caller lends CUDA events, one is recorded after every launch
 static thread_local cudaEvent_t* g_events = nullptr;
 static thread_local int g_nevents = 0, g_event_idx = 0;
@@ -309,10 +309,8 @@ const char* fa_last_error(void) { return g_err; }
 const char* fa_version(void) { return "fa_b200 0.1.0 (sm_100a)"; }
 const char* fa_last_kernel(void) { return g_kernel; }
 void fa_debug_set(int key, int value) {
-    if (key == 1) fa::fwd_sm100_set_p_in_tmem(value);
     if (key == 3) { fa::sm100_error_flag(true); fa::decode_error_flag(true); }
     if (key == 4) fa::decode_set_use_tma(value);
-    if (key == 5) g_mla_variant = value;
     if (key == 7) fa::bwd_sm100_set_ds_spill(value);
 }
 int fa_debug_get(int key) {
@@ -328,7 +326,7 @@ void fa_set_kernel_events(void** events, int count) {
 int fa_kernel_events_used(void) { return g_event_idx; }
 void fa_set_kernel_policy(int policy) { g_policy = policy; }
 }  // extern "C"
-namespace fa { int kernel_policy() { return g_policy; } int mla_variant() { return g_mla_variant; } }
+namespace fa { int kernel_policy() { return g_policy; } }
 extern "C" {
 
 }  // extern "C"

@@ -44,7 +44,6 @@ void decode_set_use_tma(int v);
 int decode_error_flag(bool clear);
 int launch_fwd_sm100(const fa_fwd_params& p);
 bool fwd_sm100_supported(const fa_fwd_params& p);
-void fwd_sm100_set_p_in_tmem(int v);
 // reads (and optionally clears) the code a timed-out wait left behind; synchronises
 int sm100_error_flag(bool clear);
 int launch_append_rotary(const fa_fwd_params& p, void* q_rot, int rotate_q_by_pos);
@@ -59,14 +58,7 @@ int peer_buffer_open(const unsigned char* handle, void** ptr);
 int launch_bwd_generic(const fa_bwd_params& p);
 // 0 = automatic kernel choice, 1 = generic kernels only (fa_set_kernel_policy)
 int kernel_policy();
-// 0 = CTA-pair latent-decode kernel preferred, 1 = single-CTA kernel (fa_debug_set key 5)
-int mla_variant();
-// int8 latent decode on tcgen05 (mla_sm100.cu)
-bool mla_sm100_supported(const fa_mla_params& p);
-int launch_mla_sm100(const fa_mla_params& p, int nsplit, int tokens_per_split, float* o_part, float* lse_part,
-                     int final_direct, cudaStream_t st);
-int mla_sm100_error_flag(bool clear);
-// the same over a pair of CTAs that split the score dimensions (mla_sm100_pair.cu)
+// int8 latent decode on tcgen05 over a pair of CTAs that split the score dimensions (mla_sm100_pair.cu)
 bool mla_pair_supported(const fa_mla_params& p);
 int launch_mla_pair(const fa_mla_params& p, int nsplit, int tokens_per_split, float* o_part, float* lse_part,
                     int final_direct, cudaStream_t st);

@@ -1,15 +1,7 @@
-// Forward attention on Blackwell tensor cores (tcgen05 + TMEM + TMA), sm_100a.
-//
-// One CTA owns a 128-row query tile of one head and walks 128-key tiles.
-//   warp 4 (one lane)  TMA producer: Q once, K and V tiles through two-stage rings.
-//   warp 5 (one lane)  MMA issuer:   S = Q K^T into one of two TMEM score buffers, O += P V
-//                                     into the TMEM output accumulator.
-//   warps 0-3          softmax:      one thread per query row reads its score row from TMEM,
-//                                     keeps the running max / sum, writes P (rounded to the input
-//                                     type) into swizzled shared memory for the second MMA and
-//                                     rescales O in TMEM when the running max moves.
-// Scores of tile j+1 are computed while tile j goes through softmax.  Math as the reference's
-// forward (mha_fwd_kvcache.cpp:632-969, online_softmax.hpp:623-875, rescale_o.hpp:318-531).
+// Forward attention on Blackwell tensor cores (tcgen05 + TMEM + TMA), sm_100a: one CTA owns 256 query rows of one
+// head (two 128-row tiles) and walks 128-key tiles; a TMA warp, an MMA-issuing warp and two softmax warp groups
+// (thread = query row).  Math as the reference's forward (mha_fwd_kvcache.cpp:632-969, online_softmax.hpp:623-875,
+// rescale_o.hpp:318-531).
 //
 // Every mbarrier wait is bounded; a timeout records a code in g_fwd_sm100_error and the CTA
 // frees its tensor memory and returns.
@@ -31,7 +23,7 @@ struct alignas(64) Sm100FwdArgs {
     int64_t lse_sb, lse_sh, lse_ss;
     const int32_t* cu_q;
     const int32_t* cu_k;
-    // KV-cache calls (two-query-tile kernel only): device-resident lengths, page table, cache row of a batch entry
+    // KV-cache calls: device-resident lengths, page table, cache row of a batch entry
     const int32_t* seqused_k;
     const int32_t* block_table;
     const int32_t* cache_batch_idx;
@@ -40,279 +32,7 @@ struct alignas(64) Sm100FwdArgs {
     int b, sq, sk, hq, hkv;
     float scale_log2;
     int causal, wl, wr;
-    int p_in_tmem;
 };
-
-template <int D>
-struct FwdSm100Smem {
-    static constexpr int kTile = 128;
-    static constexpr int kSub = 128 * 128;                  // bytes of one [128 rows][64 elem] sub-tile
-    static constexpr int kQ = (D / 64) * kSub;
-    static constexpr int kKV = (D / 64) * kSub;
-    static constexpr int kP = 2 * kSub;
-    static constexpr int oQ = 0;
-    static constexpr int oK = oQ + kQ;                      // 2 stages
-    static constexpr int oV = oK + 2 * kKV;                 // 2 stages
-    static constexpr int oP = oV + 2 * kKV;
-    static constexpr int oBar = oP + kP;
-    static constexpr int kBytes = oBar + 256;
-};
-
-// barrier slots (8 bytes each)
-enum { B_Q = 0, B_KF0, B_KF1, B_KE0, B_KE1, B_VF0, B_VF1, B_VE0, B_VE1, B_S0, B_S1, B_P, B_PV, B_COUNT };
-
-template <typename T, int D>
-__global__ void __launch_bounds__(192, 1) fwd_sm100_kernel(const __grid_constant__ Sm100FwdArgs a) {
-    using L = FwdSm100Smem<D>;
-    constexpr int NSUB = D / 64;
-    constexpr int KSTEPS = D / 16;
-    constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t COL_S0 = 0, COL_S1 = 128, COL_O = 256;
-    constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
-    constexpr uint32_t IDESC_QK = umma_idesc(FMT, 128, 128, 0, 0);
-    constexpr uint32_t IDESC_PV = umma_idesc(FMT, 128, D, 0, 1);
-
-    extern __shared__ unsigned char smem_raw[];
-    const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
-    unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
-    const uint32_t sQ = sbase + L::oQ, sK = sbase + L::oK, sV = sbase + L::oV, sP = sbase + L::oP;
-    const uint32_t bars = sbase + L::oBar;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * B_COUNT);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * B_COUNT + 8);
-    auto bar = [&](int i) { return bars + 8u * i; };
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int mblk = gridDim.x - 1 - blockIdx.x;            // heavy (late) tiles first under a causal mask
-    int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
-    if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
-    const int m0 = mblk * 128;
-    if (m0 >= sq) return;
-    if (g_fwd_sm100_error) return;
-    const int hk = h / (a.hq / a.hkv);
-    const int wl = a.wl, wr = a.causal ? 0 : a.wr;
-    const int rows = min(128, sq - m0);
-
-    // key tiles this query tile touches
-    int lo_first, hi_first, lo_last, hi_last;
-    window_bounds(m0, sq, sk, wl, wr, lo_first, hi_first);
-    window_bounds(m0 + rows - 1, sq, sk, wl, wr, lo_last, hi_last);
-    int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
-    if (sk <= 0 || lo_first >= sk) { t_lo = 0; t_hi = 0; }
-    const int ntiles = max(0, t_hi - t_lo);
-
-    T* obase = reinterpret_cast<T*>(a.o) + (a.cu_q ? 0 : (int64_t)b * a.o_sb) + (int64_t)(q_off + m0) * a.o_ss + (int64_t)h * a.o_sh;
-    float* lbase = a.lse ? a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + (int64_t)(q_off + m0) * a.lse_ss : nullptr;
-
-    if (ntiles == 0) {                                      // nothing visible: O = 0, LSE = +inf
-        if (tid < rows) {
-            uint4 z = make_uint4(0, 0, 0, 0);
-            T* orow = obase + (int64_t)tid * a.o_ss;
-#pragma unroll
-            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
-            if (lbase) lbase[(int64_t)tid * a.lse_ss] = INFINITY;
-        }
-        return;
-    }
-
-    if (tid == 0) {
-        for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), i == B_P ? 128u : 1u);
-        *abort_flag = 0;
-        mbar_fence_init();
-    }
-    if (warp == 4) {
-        tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-    int* err = &g_fwd_sm100_error;
-
-    const int qrow0 = (a.cu_q ? q_off : 0) + m0;            // TMA row coordinate of the query tile
-    const int qb = a.cu_q ? 0 : b;
-
-    if (warp == 4) {
-        // ---------------------------------------------------------------- TMA producer
-        if (lane == 0) {
-            tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
-            mbar_expect_tx(bar(B_Q), L::kQ);
-#pragma unroll
-            for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + s * L::kSub, &a.tq, bar(B_Q), s * 64, h, qrow0, qb);
-            bool ok = true;
-            for (int j = 0; j < ntiles && ok; ++j) {
-                const int st = j & 1, use = j >> 1;
-                const int krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128;
-                if (use > 0) ok = mbar_wait(bar(B_KE0 + st), (use - 1) & 1, abort_flag, err, 1);
-                if (!ok) break;
-                mbar_expect_tx(bar(B_KF0 + st), L::kKV);
-#pragma unroll
-                for (int s = 0; s < NSUB; ++s) tma_load_4d(sK + st * L::kKV + s * L::kSub, &a.tk, bar(B_KF0 + st), s * 64, hk, krow, qb);
-                if (use > 0) ok = mbar_wait(bar(B_VE0 + st), (use - 1) & 1, abort_flag, err, 2);
-                if (!ok) break;
-                mbar_expect_tx(bar(B_VF0 + st), L::kKV);
-#pragma unroll
-                for (int s = 0; s < NSUB; ++s) tma_load_4d(sV + st * L::kKV + s * L::kSub, &a.tv, bar(B_VF0 + st), s * 64, hk, krow, qb);
-            }
-        }
-    } else if (warp == 5) {
-        // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            bool ok = mbar_wait(bar(B_Q), 0, abort_flag, err, 3);
-            auto issue_pv = [&](int i) -> bool {
-                const int st = i & 1, use = i >> 1;
-                if (!mbar_wait(bar(B_P), i & 1, abort_flag, err, 4)) return false;
-                if (!mbar_wait(bar(B_VF0 + st), use & 1, abort_flag, err, 5)) return false;
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint64_t bd = umma_desc(sV + st * L::kKV + kk * 2048, L::kSub, 1024);
-                    if (a.p_in_tmem) {
-                        umma_ts(tmem + COL_O, tmem + ((i & 1) ? COL_S1 : COL_S0) + kk * 8, bd, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
-                    } else {
-                        const uint64_t ad = umma_desc(sP + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
-                        umma_ss(tmem + COL_O, ad, bd, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
-                    }
-                }
-                umma_commit(bar(B_VE0 + st));
-                umma_commit(bar(B_PV));
-                return true;
-            };
-            for (int j = 0; j < ntiles && ok; ++j) {
-                const int st = j & 1, use = j >> 1;
-                ok = mbar_wait(bar(B_KF0 + st), use & 1, abort_flag, err, 6);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t d_s = tmem + ((j & 1) ? COL_S1 : COL_S0);
-#pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk) {
-                    const uint64_t ad = umma_desc(sQ + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bd = umma_desc(sK + st * L::kKV + (kk >> 2) * L::kSub + (kk & 3) * 32, 16, 1024);
-                    umma_ss(d_s, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
-                }
-                umma_commit(bar(B_KE0 + st));
-                umma_commit(bar(B_S0 + (j & 1)));
-                if (j > 0) ok = issue_pv(j - 1);
-            }
-            if (ok) issue_pv(ntiles - 1);
-        }
-    } else {
-        // ---------------------------------------------------------------- softmax: thread = query row
-        const int r = tid;                                   // 0..127, TMEM lane
-        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-        const int qi = m0 + r;
-        int klo = 1, khi = 0;
-        if (r < rows) window_bounds(qi, sq, sk, wl, wr, klo, khi);
-        float m_run = -INFINITY, l_run = 0.f;
-        bool ok = true;
-        for (int j = 0; j < ntiles && ok; ++j) {
-            const int n0 = (t_lo + j) * 128;
-            ok = mbar_wait(bar(B_S0 + (j & 1)), (j >> 1) & 1, abort_flag, err, 7);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t t_s = tmem + lane_base + ((j & 1) ? COL_S1 : COL_S0);
-            uint32_t sreg[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
-            tmem_wait_ld();
-            const bool full = n0 >= lo_last && n0 + 127 <= hi_first;     // no masking needed anywhere in the tile
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __uint_as_float(sreg[c][i]) * a.scale_log2;
-                    if (!full) { const int col = n0 + c * 32 + i; x = (col >= klo && col <= khi) ? x : -INFINITY; }
-                    sreg[c][i] = __float_as_uint(x);
-                    mx = fmaxf(mx, x);
-                }
-            }
-            const float m_new = fmaxf(m_run, mx);
-            const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = exp2f(m_run - m_safe);
-            m_run = m_new;
-            float sum = 0.f;
-            uint32_t preg[64];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = exp2f(__uint_as_float(sreg[c][i]) - m_safe);
-                    const float p1 = exp2f(__uint_as_float(sreg[c][i + 1]) - m_safe);
-                    sum += p0 + p1;
-                    preg[c * 16 + i / 2] = Elem<T>::pack(p0, p1);
-                }
-            }
-            l_run = l_run * alpha + sum;
-            if (j > 0) {
-                ok = mbar_wait(bar(B_PV), (j - 1) & 1, abort_flag, err, 8);      // O holds tiles < j, P buffer is free
-                if (!ok) break;
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, alpha < 1.f)) {
-#pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t oreg[32];
-                        tmem_ld32(tmem + lane_base + COL_O + c * 32, oreg);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-                        tmem_st32(tmem + lane_base + COL_O + c * 32, oreg);
-                    }
-                }
-            }
-            if (a.p_in_tmem) {
-                // P over the score buffer: 64 columns of packed pairs
-                uint32_t* pp = preg;
-                tmem_st32(t_s, *reinterpret_cast<uint32_t(*)[32]>(pp));
-                tmem_st32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(pp + 32));
-            } else {
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {               // 16-byte chunk c holds keys 8c..8c+7
-                    const uint32_t addr = sP + (c >> 3) * L::kSub + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(preg[4 * c]), "r"(preg[4 * c + 1]),
-                                 "r"(preg[4 * c + 2]), "r"(preg[4 * c + 3]) : "memory");
-                }
-                fence_proxy_async_smem();
-            }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(B_P));
-        }
-        if (ok) ok = mbar_wait(bar(B_PV), (ntiles - 1) & 1, abort_flag, err, 9);
-        if (ok) {
-            tc_fence_after();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            T* orow = obase + (int64_t)r * a.o_ss;
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t oreg[32];
-                tmem_ld32(tmem + lane_base + COL_O + c * 32, oreg);
-                tmem_wait_ld();
-                if (r < rows) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 pk;
-                        pk.x = Elem<T>::pack(__uint_as_float(oreg[8 * v + 0]) * inv, __uint_as_float(oreg[8 * v + 1]) * inv);
-                        pk.y = Elem<T>::pack(__uint_as_float(oreg[8 * v + 2]) * inv, __uint_as_float(oreg[8 * v + 3]) * inv);
-                        pk.z = Elem<T>::pack(__uint_as_float(oreg[8 * v + 4]) * inv, __uint_as_float(oreg[8 * v + 5]) * inv);
-                        pk.w = Elem<T>::pack(__uint_as_float(oreg[8 * v + 6]) * inv, __uint_as_float(oreg[8 * v + 7]) * inv);
-                        reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
-                    }
-                }
-            }
-            if (r < rows && lbase) lbase[(int64_t)r * a.lse_ss] = l_run > 0.f ? (m_run + log2f(l_run)) * kLn2 : INFINITY;
-        }
-    }
-    // ---- teardown: nothing of this CTA may still touch tensor memory ------------------------------------
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 4) {
-        tc_fence_after();
-        tmem_dealloc(tmem, TMEM_COLS);
-    }
-}
-
 
 // =================================================================================================
 // Two query tiles per CTA (256 rows), P kept in tensor memory.
@@ -335,7 +55,7 @@ struct FwdSm100Smem2 {
     static constexpr int oK = oQ + 2 * kQ;                  // 2 stages
     static constexpr int oV = oK + 2 * kKV;                 // 2 stages
     static constexpr int oBar = oV + 2 * kKV;
-    static constexpr int kBytes = oBar + 320;        // barriers, flags and the persistent kernel's four 16-byte slots
+    static constexpr int kBytes = oBar + 320;        // barriers and flags
 };
 
 #ifndef FA_FWD_POLY
@@ -695,396 +415,6 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     }
 }
 
-// ------------------------------------------------------------------------------------------------------------
-// Persistent variant of the kernel above.  It is launched with the same grid, but a CTA that has issued the loads
-// of its item asks the hardware for the next CTA of the grid that has not started yet and runs that CTA's item
-// itself (the hardware keeps the launch order, so the query blocks of a head still run together and share K/V in
-// L2).  All barriers keep running across items (their parities come from running counts of tiles and items), so the
-// copy warp already loads Q, K and V of the next item and the MMA warp already multiplies its first Q K^T while the
-// softmax warps still write the previous item's output; only the first P V of an item waits until the accumulator
-// has been read out (C3_OFA / C3_OFB), and the Q buffer is reloaded once the last Q K^T of the previous item has
-// completed (C3_QE).  The answers of the hardware arrive in a ring of four 16-byte slots, each with its barrier
-// (C3_IT0..3): the copy warp is never more than two items ahead of the slowest warp, so four slots suffice.
-enum { C3_QE = C_COUNT, C3_OFA, C3_OFB, C3_IT0, C3_IT1, C3_IT2, C3_IT3, C3_COUNT };
-
-template <typename T, int D>
-__global__ void __launch_bounds__(384, 1) fwd_sm100_kernel3(const __grid_constant__ Sm100FwdArgs a) {
-    using L = FwdSm100Smem2<D>;
-    constexpr int NSUB = D / 64;
-    constexpr int KSTEPS = D / 16;
-    constexpr uint32_t TMEM_COLS = 512;
-    constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
-    constexpr uint32_t IDESC_QK = umma_idesc(FMT, 128, 128, 0, 0);
-    constexpr uint32_t IDESC_PV = umma_idesc(FMT, 128, D, 0, 1);
-    constexpr float kRescaleThreshold = 8.f;
-    static_assert(8 * C3_COUNT + 16 + 64 <= L::kBytes - L::oBar && (8 * C3_COUNT + 16) % 16 == 0, "barrier area");
-
-    extern __shared__ unsigned char smem_raw[];
-    const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
-    unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
-    const uint32_t sQ = sbase + L::oQ, sK = sbase + L::oK, sV = sbase + L::oV;
-    const uint32_t bars = sbase + L::oBar;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * C3_COUNT);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * C3_COUNT + 8);
-    const uint32_t slots = bars + 8u * C3_COUNT + 16u;                   // four 16-byte answers of the work-stealing requests
-    auto bar = [&](int i) { return bars + 8u * i; };
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (g_fwd_sm100_error) return;
-    const int wl = a.wl, wr = a.causal ? 0 : a.wr;
-
-    struct Item {
-        int b, h, hk, m0, sq, sk, q_off, k_off, rows_cta, t_lo, ntiles;
-        bool has_b, live;
-    };
-    // k-th item of this CTA: its own block index first, then whatever the hardware handed over; false = no work left
-    auto item_at = [&](int k, int& bx, int& by, int& bz) -> bool {
-        if (k == 0) { bx = blockIdx.x; by = blockIdx.y; bz = blockIdx.z; return true; }
-        const int idx = (k - 1) & 3;
-        if (!mbar_wait(bar(C3_IT0 + idx), ((k - 1) >> 2) & 1, abort_flag, &g_fwd_sm100_error, 15)) return false;
-        return next_cta_decode(slots + idx * 16, bx, by, bz);
-    };
-    auto decode = [&](int bx, int by, int bz) {
-        Item it;
-        const int mblk = (int)gridDim.x - 1 - bx;
-        it.h = by;
-        it.b = bz;
-        it.hk = it.h / (a.hq / a.hkv);
-        it.q_off = 0; it.k_off = 0; it.sq = a.sq; it.sk = a.sk;
-        if (a.cu_q) {
-            it.q_off = a.cu_q[it.b]; it.sq = a.cu_q[it.b + 1] - it.q_off;
-            it.k_off = a.cu_k[it.b]; it.sk = a.cu_k[it.b + 1] - it.k_off;
-        }
-        it.m0 = mblk * 256;
-        it.live = it.m0 < it.sq;
-        it.rows_cta = min(256, it.sq - it.m0);
-        it.has_b = it.rows_cta > 128;
-        it.t_lo = 0; it.ntiles = 0;
-        if (it.live) {
-            int lo_first, hi_first, lo_last, hi_last;
-            window_bounds(it.m0, it.sq, it.sk, wl, wr, lo_first, hi_first);
-            window_bounds(it.m0 + it.rows_cta - 1, it.sq, it.sk, wl, wr, lo_last, hi_last);
-            int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
-            if (it.sk <= 0 || lo_first >= it.sk) { t_lo = 0; t_hi = 0; }
-            it.t_lo = t_lo;
-            it.ntiles = max(0, t_hi - t_lo);
-        }
-        return it;
-    };
-
-    if (tid == 0) {
-        for (int i = 0; i < C3_COUNT; ++i)
-            mbar_init(bar(i), ((i >= C_PA && i <= C_PB2) || i == C3_OFA || i == C3_OFB) ? 128u : 1u);
-        *abort_flag = 0;
-        mbar_fence_init();
-    }
-    if (warp == 8) {
-        tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-    int* err = &g_fwd_sm100_error;
-
-    static_assert(128 * 48 + 256 * 224 <= 384 * 168, "register split exceeds the CTA's allocation");
-    if (warp >= 8) {
-    reg_dealloc<48>();
-    if (warp == 8) {
-        if (lane == 0) {
-            tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
-            int gt = 0, ni = 0;                       // tiles and items (with keys) so far
-            bool ok = true;
-            for (int k = 0; ok; ++k) {
-                int bx, by, bz;
-                if (!item_at(k, bx, by, bz)) break;
-                // ask for item k + 1 now: its answer is there long before anyone needs it
-                mbar_expect_tx(bar(C3_IT0 + (k & 3)), 16);
-                next_cta_request(slots + (k & 3) * 16, bar(C3_IT0 + (k & 3)));
-                const Item it = decode(bx, by, bz);
-                if (!it.live || it.ntiles == 0) continue;
-                const int qrow0 = (a.cu_q ? it.q_off : 0) + it.m0, qb = a.cu_q ? 0 : it.b;
-                if (ni > 0) ok = mbar_wait(bar(C3_QE), (ni - 1) & 1, abort_flag, err, 12);
-                if (!ok) break;
-                mbar_expect_tx(bar(C_Q), it.has_b ? 2 * L::kQ : L::kQ);
-#pragma unroll
-                for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, it.h, qrow0, qb);
-                if (it.has_b) {
-#pragma unroll
-                    for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + L::kQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, it.h, qrow0 + 128, qb);
-                }
-                for (int j = 0; j < it.ntiles && ok; ++j) {
-                    const int st = (gt + j) & 1, use = (gt + j) >> 1;
-                    const int krow = (a.cu_q ? it.k_off : 0) + (it.t_lo + j) * 128;
-                    if (use > 0) ok = mbar_wait(bar(C_KE0 + st), (use - 1) & 1, abort_flag, err, 1);
-                    if (!ok) break;
-                    mbar_expect_tx(bar(C_KF0 + st), L::kKV);
-#pragma unroll
-                    for (int s = 0; s < NSUB; ++s) tma_load_4d(sK + st * L::kKV + s * L::kSub, &a.tk, bar(C_KF0 + st), s * 64, it.hk, krow, qb);
-                    if (use > 0) ok = mbar_wait(bar(C_VE0 + st), (use - 1) & 1, abort_flag, err, 2);
-                    if (!ok) break;
-                    mbar_expect_tx(bar(C_VF0 + st), L::kKV);
-#pragma unroll
-                    for (int s = 0; s < NSUB; ++s) tma_load_4d(sV + st * L::kKV + s * L::kSub, &a.tv, bar(C_VF0 + st), s * 64, it.hk, krow, qb);
-                }
-                gt += it.ntiles;
-                ++ni;
-            }
-        }
-    } else if (warp == 9) {
-        const uint64_t dQ0 = umma_desc(sQ, 16, 1024), dK0 = umma_desc(sK, 16, 1024), dV0 = umma_desc(sV, L::kSub, 1024);
-        auto issue_qk = [&](int x, int st) {
-            const uint32_t d_s = tmem + x * 128;
-            const uint64_t aq = umma_desc_at(dQ0, x * L::kQ), bk = umma_desc_at(dK0, st * L::kKV);
-            umma_ss_wo<0, 0, 0>(d_s, aq, bk, IDESC_QK);
-            static_for<1, KSTEPS>([&](auto kk) {
-                constexpr uint32_t off = (kk.value >> 2) * L::kSub + (kk.value & 3) * 32;
-                umma_ss_wo<1, off, off>(d_s, aq, bk, IDESC_QK);
-            });
-            umma_commit_w(bar(C_SA + x));
-        };
-        // P V of tile x in two halves of 64 keys; `pp` = parity of the tile's P barriers
-        auto issue_pv = [&](int x, int st, bool first, int pp) -> bool {
-            const uint64_t bv = umma_desc_at(dV0, st * L::kKV);
-            const uint32_t d_o = tmem + 256 + x * 128, a_p = tmem + x * 128;
-            if (!first) umma_ts_wo<1, 0, 0>(d_o, a_p, bv, IDESC_PV); else umma_ts_wo<0, 0, 0>(d_o, a_p, bv, IDESC_PV);
-            static_for<1, 4>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
-            if (!mbar_wait(bar(C_PA2 + x), pp, abort_flag, err, 11)) return false;
-            tc_fence_after();
-            static_for<4, 8>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
-            return true;
-        };
-        int gt = 0, gtb = 0, ni = 0, nib = 0;         // tiles / items so far, all and those with a second query tile
-        bool ok = true;
-        for (int k = 0; ok; ++k) {
-            int bx, by, bz;
-            if (!item_at(k, bx, by, bz)) break;
-            const Item it = decode(bx, by, bz);
-            if (!it.live || it.ntiles == 0) continue;
-            const int ntiles = it.ntiles;
-            const bool has_b = it.has_b;
-            ok = mbar_wait(bar(C_Q), ni & 1, abort_flag, err, 3);
-            if (ok) ok = mbar_wait(bar(C_KF0 + (gt & 1)), (gt >> 1) & 1, abort_flag, err, 4);
-            if (!ok) break;
-            tc_fence_after();
-            issue_qk(0, gt & 1);
-            if (has_b) issue_qk(1, gt & 1);
-            umma_commit_w(bar(C_KE0 + (gt & 1)));
-            for (int j = 0; j < ntiles && ok; ++j) {
-                const int st = (gt + j) & 1, use = (gt + j) >> 1;
-                const bool more = j + 1 < ntiles;
-                const int st1 = (gt + j + 1) & 1, use1 = (gt + j + 1) >> 1;
-                if (!more) umma_commit_w(bar(C3_QE));                 // every Q K^T of this item has been issued
-                ok = mbar_wait(bar(C_PA), (gt + j) & 1, abort_flag, err, 5);
-                if (ok) ok = mbar_wait(bar(C_VF0 + st), use & 1, abort_flag, err, 6);
-                if (ok && j == 0 && ni > 0) ok = mbar_wait(bar(C3_OFA), (ni - 1) & 1, abort_flag, err, 13);
-                if (!ok) break;
-                tc_fence_after();
-                ok = issue_pv(0, st, j == 0, (gt + j) & 1);
-                if (!ok) break;
-                if (more) {
-                    ok = mbar_wait(bar(C_KF0 + st1), use1 & 1, abort_flag, err, 7);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_qk(0, st1);
-                } else {
-                    umma_commit_w(bar(C_OA));
-                }
-                if (has_b) {
-                    ok = mbar_wait(bar(C_PB), (gtb + j) & 1, abort_flag, err, 8);
-                    if (ok && j == 0 && nib > 0) ok = mbar_wait(bar(C3_OFB), (nib - 1) & 1, abort_flag, err, 14);
-                    if (!ok) break;
-                    tc_fence_after();
-                    ok = issue_pv(1, st, j == 0, (gtb + j) & 1);
-                    if (!ok) break;
-                }
-                umma_commit_w(bar(C_VE0 + st));
-                if (more) {
-                    if (has_b) issue_qk(1, st1);
-                    umma_commit_w(bar(C_KE0 + st1));
-                } else if (has_b) {
-                    umma_commit_w(bar(C_OB));
-                }
-            }
-            gt += ntiles;
-            ++ni;
-            if (has_b) { gtb += ntiles; ++nib; }
-        }
-    }
-    } else {
-    reg_alloc<224>();
-    {
-        int gt = 0, ni = 0;                           // tiles / items this softmax group has handled
-        for (int k = 0;; ++k) {
-            int bx, by, bz;
-            if (!item_at(k, bx, by, bz)) break;
-            const Item it = decode(bx, by, bz);
-            if (!it.live) continue;
-            const int b = it.b, h = it.h, m0 = it.m0, sq = it.sq, sk = it.sk, q_off = it.q_off;
-            const int rows_cta = it.rows_cta, t_lo = it.t_lo, ntiles = it.ntiles;
-            T* obase = reinterpret_cast<T*>(a.o) + (a.cu_q ? 0 : (int64_t)b * a.o_sb) + (int64_t)(q_off + m0) * a.o_ss + (int64_t)h * a.o_sh;
-            float* lbase = a.lse ? a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + (int64_t)(q_off + m0) * a.lse_ss : nullptr;
-            if (ntiles == 0) {                        // no visible key for any row of the item
-                if (tid < rows_cta) {
-                    uint4 z = make_uint4(0, 0, 0, 0);
-                    T* orow = obase + (int64_t)tid * a.o_ss;
-#pragma unroll
-                    for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
-                    if (lbase) lbase[(int64_t)tid * a.lse_ss] = INFINITY;
-                }
-                continue;
-            }
-            if (warp >= 4 && !it.has_b) continue;     // the second query tile does not exist
-            {
-            const int x = warp >> 2;
-            const int r = tid & 127;
-            const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-            const uint32_t t_s = tmem + lane_base + x * 128;
-            const uint32_t t_o = tmem + lane_base + 256 + x * 128;
-            const int rows = min(128, rows_cta - x * 128);
-            const int qi = m0 + x * 128 + r;
-            int klo = 1, khi = 0;
-            if (r < rows) window_bounds(qi, sq, sk, wl, wr, klo, khi);
-            int lo_l, hi_f, tmp;
-            window_bounds(m0 + x * 128, sq, sk, wl, wr, tmp, hi_f);
-            window_bounds(m0 + x * 128 + rows - 1, sq, sk, wl, wr, lo_l, tmp);
-            float m_used = -INFINITY, l_run = 0.f;
-            const float sc = a.scale_log2;
-            bool ok = true;
-            for (int j = 0; j < ntiles && ok; ++j) {
-                const int n0 = (t_lo + j) * 128;
-                ok = mbar_wait(bar(C_SA + x), (gt + j) & 1, abort_flag, err, 9);
-                if (!ok) break;
-                tc_fence_after();
-                uint32_t sreg[4][32];
-#pragma unroll
-                for (int c = 0; c < 2; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
-                tmem_wait_ld();
-                // the second half of the row is in flight while the first half is reduced
-#pragma unroll
-                for (int c = 2; c < 4; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
-                const bool full = n0 >= lo_l && n0 + 127 <= hi_f;
-                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    if (hh == 1) tmem_wait_ld();
-                    if (!full) {
-#pragma unroll
-                        for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const int col = n0 + c * 32 + i;
-                                if (col < klo || col > khi) sreg[c][i] = 0xff800000u;     // -inf
-                            }
-                        }
-                    }
-                    // four independent chains of three-input maxima
-#pragma unroll
-                    for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            mx0 = fmaxf(fmaxf(mx0, __uint_as_float(sreg[c][i])), __uint_as_float(sreg[c][i + 1]));
-                            mx1 = fmaxf(fmaxf(mx1, __uint_as_float(sreg[c][i + 2])), __uint_as_float(sreg[c][i + 3]));
-                            mx2 = fmaxf(fmaxf(mx2, __uint_as_float(sreg[c][i + 4])), __uint_as_float(sreg[c][i + 5]));
-                            mx3 = fmaxf(fmaxf(mx3, __uint_as_float(sreg[c][i + 6])), __uint_as_float(sreg[c][i + 7]));
-                        }
-                    }
-                }
-                const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;       // log2 domain
-                if (m_used == -INFINITY) m_used = m_new;
-                if (j > 0 && __any_sync(0xffffffffu, m_new > m_used + kRescaleThreshold)) {
-                    const float m_next = fmaxf(m_used, m_new);
-                    const float alpha = m_used == -INFINITY ? 1.f : ex2_approx(m_used - m_next);
-                    m_used = m_next;
-                    l_run *= alpha;
-#pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t oreg[32];
-                        tmem_ld32(t_o + c * 32, oreg);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-                        tmem_st32(t_o + c * 32, oreg);
-                    }
-                }
-                const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-                const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(neg_m, neg_m);
-                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-                // NPOLY of every 8 pairs take the polynomial 2^x, spread evenly between the special-function ones
-                auto exp_phase = [&](auto npoly_c) {
-                    constexpr int NPOLY = decltype(npoly_c)::value;
-#pragma unroll
-                    for (int hlf = 0; hlf < 2; ++hlf) {
-                        uint32_t preg[32];
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            const uint32_t* src = &sreg[2 * hlf + (g >> 1)][(g & 1) * 16];
-                            static_for<0, 8>([&](auto pi) {
-                                constexpr bool poly = (pi.value * NPOLY) % 8 < NPOLY;
-                                const float2 xv = fma2(make_float2(__uint_as_float(src[2 * pi.value]), __uint_as_float(src[2 * pi.value + 1])), sc2, nm2);
-                                float2 pv;
-                                if constexpr (poly) pv = ex2_poly2(xv);
-                                else pv = make_float2(ex2_approx(xv.x), ex2_approx(xv.y));
-                                if constexpr (pi.value & 1) sum_b = add2(sum_b, pv); else sum_a = add2(sum_a, pv);
-                                preg[g * 8 + pi.value] = Elem<T>::pack(pv.x, pv.y);
-                            });
-                        }
-                        tmem_st32(t_s + hlf * 32, preg);
-                        tmem_wait_st();
-                        tc_fence_before();
-                        mbar_arrive(bar((hlf ? C_PA2 : C_PA) + x));
-                    }
-                };
-                // masked tiles keep the special-function path: it maps -inf to an exact zero
-                if (full) exp_phase(std::integral_constant<int, FA_FWD_POLY>{});
-                else exp_phase(std::integral_constant<int, 0>{});
-                const float s0 = sum_a.x + sum_b.x, s1 = sum_a.y + sum_b.y;
-                l_run += s0 + s1;
-            }
-            if (ok) ok = mbar_wait(bar(C_OA + x), ni & 1, abort_flag, err, 10);
-            if (ok) {
-                tc_fence_after();
-                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-                T* orow = obase + (int64_t)(x * 128 + r) * a.o_ss;
-#pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t oreg[32];
-                    tmem_ld32(t_o + c * 32, oreg);
-                    tmem_wait_ld();
-                    if (r < rows) {
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 pk;
-                            pk.x = Elem<T>::pack(__uint_as_float(oreg[8 * v + 0]) * inv, __uint_as_float(oreg[8 * v + 1]) * inv);
-                            pk.y = Elem<T>::pack(__uint_as_float(oreg[8 * v + 2]) * inv, __uint_as_float(oreg[8 * v + 3]) * inv);
-                            pk.z = Elem<T>::pack(__uint_as_float(oreg[8 * v + 4]) * inv, __uint_as_float(oreg[8 * v + 5]) * inv);
-                            pk.w = Elem<T>::pack(__uint_as_float(oreg[8 * v + 6]) * inv, __uint_as_float(oreg[8 * v + 7]) * inv);
-                            reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
-                        }
-                    }
-                }
-                if (r < rows && lbase) lbase[(int64_t)(x * 128 + r) * a.lse_ss] = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : INFINITY;
-
-                    // the accumulator has been read: the next item's first P V may overwrite it
-                    tc_fence_before();
-                    mbar_arrive(bar(C3_OFA + x));
-                }
-                if (!ok) break;
-            }
-            gt += ntiles;
-            ++ni;
-        }
-    }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 8) {
-        tc_fence_after();
-        tmem_dealloc(tmem, TMEM_COLS);
-    }
-}
-
 // ---- host side ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1133,18 +463,13 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
     return FA_OK;
 }
 
-// 0: one query tile per CTA, P through shared memory; 1: same with P in tensor memory;
-// 2: two query tiles per CTA, P in tensor memory; 3: the same as persistent CTAs over a static item list
-static int g_variant = 2;
-void fwd_sm100_set_p_in_tmem(int v) { g_variant = v; }
-
 bool fwd_sm100_supported(const fa_fwd_params& p) {
     if (p.d != p.dv || (p.d != 64 && p.d != 128)) return false;
     if (p.softcap > 0.f || p.alibi_slopes) return false;
     const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
     if (cache) {
-        // KV-cache calls (prefill against a cache): only the two-query-tile kernel reads lengths and pages on the device
-        if (g_variant != 2 || p.cu_seqlens_q || p.cu_seqlens_k || !p.seqused_k) return false;
+        // KV-cache calls (prefill against a cache): lengths and pages are read on the device
+        if (p.cu_seqlens_q || p.cu_seqlens_k || !p.seqused_k) return false;
         if (p.block_table && (p.page_size <= 0 || p.page_size % 128)) return false;
         if (p.sq < 64) return false;                      // short queries belong to the split-KV decode kernels
     }
@@ -1163,25 +488,11 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
 template <typename T, int D>
 static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
-    if (g_variant == 3) {
-        auto kern = fwd_sm100_kernel3<T, D>;
-        const int smem = FwdSm100Smem2<D>::kBytes + 1024;
-        if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-        dim3 grid((p.sq + 255) / 256, p.hq, p.b);
-        kern<<<grid, 384, smem, st>>>(a);
-    } else if (g_variant == 2) {
-        auto kern = fwd_sm100_kernel2<T, D>;
-        const int smem = FwdSm100Smem2<D>::kBytes + 1024;
-        if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-        dim3 grid((p.sq + 255) / 256, p.hq, p.b);
-        kern<<<grid, 384, smem, st>>>(a);
-    } else {
-        auto kern = fwd_sm100_kernel<T, D>;
-        const int smem = FwdSm100Smem<D>::kBytes + 1024;
-        if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-        dim3 grid((p.sq + 127) / 128, p.hq, p.b);
-        kern<<<grid, 192, smem, st>>>(a);
-    }
+    auto kern = fwd_sm100_kernel2<T, D>;
+    const int smem = FwdSm100Smem2<D>::kBytes + 1024;
+    if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+    dim3 grid((p.sq + 255) / 256, p.hq, p.b);
+    kern<<<grid, 384, smem, st>>>(a);
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
 }
@@ -1215,8 +526,7 @@ int launch_fwd_sm100(const fa_fwd_params& p) {
     a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv;
     a.scale_log2 = p.scale * kLog2e;
     a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
-    a.p_in_tmem = g_variant == 1;
-    note_kernel(g_variant == 3 ? "sm100_tcgen05_2q_persistent" : g_variant == 2 ? "sm100_tcgen05_2q" : g_variant == 1 ? "sm100_tcgen05_ts" : "sm100_tcgen05");
+    note_kernel("sm100_tcgen05_2q");
     if (p.dtype == FA_F16) return p.d == 64 ? launch_sm100_t<__half, 64>(p, a) : launch_sm100_t<__half, 128>(p, a);
     return p.d == 64 ? launch_sm100_t<__nv_bfloat16, 64>(p, a) : launch_sm100_t<__nv_bfloat16, 128>(p, a);
 }
@@ -1226,9 +536,8 @@ int sm100_error_flag(bool clear) {
     cudaMemcpyFromSymbol(&v, g_fwd_sm100_error, sizeof(int));
     if (clear) { int z = 0; cudaMemcpyToSymbol(g_fwd_sm100_error, &z, sizeof(int)); }
     const int w = bwd_sm100_error_flag(clear);
-    const int m = mla_sm100_error_flag(clear);
-    const int m2 = mla_pair_error_flag(clear);
-    return v ? v : (w ? w : (m ? m : m2));
+    const int m = mla_pair_error_flag(clear);
+    return v ? v : (w ? w : m);
 }
 
 }  // namespace fa

@@ -234,7 +234,7 @@ static void plan_mla(const fa_mla_params& p, int& nsplit, int& tps, int max_len)
     if (p.num_splits > 1) n = p.num_splits;
     else if (p.num_splits == 0) {
         // the tcgen05 kernel stages all of Q (144 KB) per CTA, so its splits are longer
-        const long per_split = (kernel_policy() == 0 && mla_sm100_supported(p)) ? 8192 : 2048;
+        const long per_split = (kernel_policy() == 0 && mla_pair_supported(p)) ? 8192 : 2048;
         const long by_bal = (max_len + per_split - 1) / per_split;
         const long base = 2L * (p.b > 0 ? p.b : 1);
         const long by_occ = (2L * sm_count() + base - 1) / base;
@@ -306,10 +306,8 @@ int fa_mla_decode(const fa_mla_params* pp) {
         }
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
-    if (kernel_policy() == 0 && mla_variant() == 0 && mla_pair_supported(p)) {
+    if (kernel_policy() == 0 && mla_pair_supported(p)) {
         if (int e = launch_mla_pair(p, a.nsplit, a.tokens_per_split, a.o_part, a.lse_part, a.final_direct, st)) return e;
-    } else if (kernel_policy() == 0 && mla_sm100_supported(p)) {
-        if (int e = launch_mla_sm100(p, a.nsplit, a.tokens_per_split, a.o_part, a.lse_part, a.final_direct, st)) return e;
     } else {
         const int smem = 3 * kMlaTile * kMlaPitch;
         if (int e = cuda_ok(cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;

@@ -49,6 +49,7 @@ class BwdParams(C.Structure):
         ("causal", C.c_int32), ("window_left", C.c_int32), ("window_right", C.c_int32),
         ("dtype", C.c_int32), ("deterministic", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+        ("alibi_slopes", C.c_void_p), ("alibi_stride_b", C.c_int64),
     ]
 
 

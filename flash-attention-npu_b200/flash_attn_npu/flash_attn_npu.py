@@ -292,8 +292,6 @@ def _bwd_common(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, alibi_slopes_, p
         raise RuntimeError("softcap must be non-negative (0.0 disables softcap)")
     if p_dropout != 0.0:
         raise RuntimeError("FlashAttention on B200 does not support dropout.")
-    if alibi_slopes_ is not None:
-        raise RuntimeError("FlashAttention on B200 does not support alibi_slopes in the backward pass.")
     packed = cu_q is not None
     d_og = q.size(-1)
     if d_og % 8 != 0:
@@ -337,6 +335,7 @@ def _bwd_common(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, alibi_slopes_, p
     p.causal, p.window_left, p.window_right = int(is_causal), wl, wr
     p.dtype = _dtype_code(q)
     p.deterministic = int(deterministic)
+    keep = _alibi(p, alibi_slopes_, batch, hq)
     ws = capi.workspace(lib.fa_bwd_workspace_bytes(p), q.device)
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     p.stream = capi.stream_ptr(q.device)

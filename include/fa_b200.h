@@ -129,7 +129,9 @@ int    fa_fwd_num_splits(const fa_fwd_params* p);
  * fag_general_host.cpp:18);  fa_varlen_bwd: mha_varlen_bwd flash_api.cpp:1092;
  * v3 mha_bwd csrc/ascend910/flash_attn_npu_3/flash_api.cpp:573.
  * dq/dk/dv are written in the input dtype.  deterministic != 0 selects a fixed
- * accumulation order for dQ.
+ * accumulation order for dQ.  alibi_slopes (as in fa_fwd_params) adds the same
+ * bias -slope * |i + sk - sq - j| to the recomputed scores; the reference's
+ * backward takes the argument and ignores it, the slopes get no gradient.
  * ---------------------------------------------------------------------- */
 typedef struct {
     fa_tensor dout, q, k, v, o, dq, dk, dv;
@@ -147,6 +149,8 @@ typedef struct {
     void*   workspace;             /* >= fa_bwd_workspace_bytes()                      */
     size_t  workspace_bytes;
     void*   stream;
+    const float* alibi_slopes;     /* (hq) or (b,hq) fp32, or null                     */
+    int64_t      alibi_stride_b;   /* 0 when slopes are shared by the batch            */
 } fa_bwd_params;
 
 int    fa_bwd(const fa_bwd_params* p);
@@ -290,14 +294,13 @@ const char* fa_version(void);
 /* Name of the kernel family the last forward / backward call on this thread used
  * ("sm100_tcgen05", "generic_mma", "decode_splitkv", ...); for tests and benchmarks. */
 const char* fa_last_kernel(void);
-/* Force the kernel family: 0 = automatic, 1 = generic tensor-core kernels only. */
+/* Force the kernel family, process-wide: 0 = automatic, 1 = generic tensor-core kernels only. */
 void        fa_set_kernel_policy(int policy);
 
-/* Debug switches and status, for tests: key 1 = keep P in tensor memory for the second MMA of the
- * tcgen05 forward (set), key 2 = error code left by a timed-out wait in a tcgen05 kernel (get;
- * synchronises the device), key 3 = clear that code (set), key 4 = 0 makes the decode kernel load
- * cache tiles with 16-byte cp.async copies instead of TMA (set), key 5 = 1 makes the int8 latent
- * decode use its single-CTA tcgen05 kernel instead of the CTA-pair one (set), key 7 = 0 makes the tcgen05
+/* Process-wide switches for tests and benchmarks (plain atomics: flipping one while another thread is inside a
+ * call changes which kernel that call's NEXT launch takes, never its results).  Debug keys: 2 = error code left by a
+ * timed-out wait in a tcgen05 / TMA kernel (get; synchronises the device), 3 = clear that code (set), 4 = 0 makes
+ * the decode kernel load cache tiles with 16-byte cp.async copies instead of TMA (set), 7 = 0 makes the tcgen05
  * backward recompute S and dP in its dQ kernel instead of reading the dS tiles the dK/dV kernel leaves in the
  * workspace (set). */
 void        fa_debug_set(int key, int value);

@@ -432,11 +432,13 @@ def mla_decode(q_nope, q_rope, latent_i8, scales, rope, block_table, cache_seqle
 # --------------------------------------------------------------------------
 # backward
 # --------------------------------------------------------------------------
-def _bwd_one(q, k, v, dout, lse, scale, softcap, mask, gtype):
+def _bwd_one(q, k, v, dout, lse, scale, softcap, mask, gtype, bias=None):
     """q (H,Sq,D) in its own dtype, k/v (H,Sk,D) already broadcast over the group,
     lse (H,Sq) fp32. All returned in gtype. Follows tests/fa_small_op_golden.py:104-135,
     :169-185: the score recompute runs in the tensors' own dtype (so bf16 inputs give
-    bf16-rounded scores), everything after it in gtype."""
+    bf16-rounded scores), everything after it in gtype.  `bias` (H,Sq,Sk) fp32 is added to
+    the scores after scaling and softcap, like the forward's (alibi; not in the reference,
+    whose backward ignores the slopes); it is constant, so dS is unchanged in form."""
     cd = q.dtype
     s = torch.matmul(q.to(cd), k.to(cd).transpose(-1, -2)).to(torch.float32).mul(scale)
     factor = None
@@ -444,6 +446,8 @@ def _bwd_one(q, k, v, dout, lse, scale, softcap, mask, gtype):
         t = torch.tanh(s.to(gtype) / softcap)
         factor = 1.0 - t * t
         s = softcap * torch.tanh(s / softcap)
+    if bias is not None:
+        s = s + bias
     if mask is not None:
         s = s + mask.to(torch.float32) * BWD_MASK
     p = torch.exp(s.to(gtype) - lse.to(torch.float32).to(gtype).unsqueeze(-1))
@@ -461,10 +465,10 @@ def _bwd_one(q, k, v, dout, lse, scale, softcap, mask, gtype):
 
 
 def attention_bwd(q, k, v, dout, lse, scale, causal=False, window=(-1, -1), softcap=0.0,
-                  gtype=torch.float64, head_chunk: Optional[int] = None):
+                  gtype=torch.float64, head_chunk: Optional[int] = None, alibi_slopes=None):
     """BSND backward golden. q/dout (B,Sq,H,D), k/v (B,Sk,Hkv,D), lse (B,H,Sq).
     Returns dq, dk, dv in q's dtype. `head_chunk` bounds memory by walking KV heads in
-    groups (exact: heads are independent)."""
+    groups (exact: heads are independent).  alibi_slopes (H,) or (B,H) as in attention_fwd."""
     b, sq, h, d = q.shape
     sk, hkv = k.shape[1], k.shape[2]
     g = h // hkv
@@ -480,7 +484,11 @@ def attention_bwd(q, k, v, dout, lse, scale, causal=False, window=(-1, -1), soft
             dos = dout[i, :, h0 * g:h1 * g].permute(1, 0, 2)
             ks = k[i, :, h0:h1].permute(1, 0, 2).repeat_interleave(g, dim=0)
             vs = v[i, :, h0:h1].permute(1, 0, 2).repeat_interleave(g, dim=0)
-            dqi, dki, dvi = _bwd_one(qs, ks, vs, dos, lse[i, h0 * g:h1 * g], scale, softcap, mask, gtype)
+            bias = None
+            if alibi_slopes is not None:
+                sl = alibi_slopes if alibi_slopes.dim() == 1 else alibi_slopes[i]
+                bias = alibi_bias(sl[h0 * g:h1 * g], sq, sk)
+            dqi, dki, dvi = _bwd_one(qs, ks, vs, dos, lse[i, h0 * g:h1 * g], scale, softcap, mask, gtype, bias)
             dq[i, :, h0 * g:h1 * g] = dqi.permute(1, 0, 2).to(q.dtype)
             dk[i, :, h0:h1] = dki.reshape(h1 - h0, g, sk, d).sum(dim=1).permute(1, 0, 2).to(k.dtype)
             dv[i, :, h0:h1] = dvi.reshape(h1 - h0, g, sk, -1).sum(dim=1).permute(1, 0, 2).to(v.dtype)

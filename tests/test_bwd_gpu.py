@@ -152,3 +152,31 @@ def test_backward_uses_the_mask_of_the_forward_when_queries_outnumber_keys():
     assert_within("out", out.detach().cpu(), lp_o, f_o)
     for name, got, a, b_ in zip(("dq", "dk", "dv"), grads, lp, f32):
         assert_within(name, got.cpu(), a, b_, roundings=3)
+
+
+@pytest.mark.parametrize("per_batch", [False, True])
+@pytest.mark.parametrize("causal,window,cap", [(True, (-1, -1), 0.0), (False, (48, 16), 0.0), (True, (-1, -1), 15.0)])
+def test_alibi_backward(per_batch, causal, window, cap):
+    """Alibi slopes in the backward (the reference's backward takes and ignores them): the bias of the forward is
+    added to the recomputed scores, so the gradients belong to the forward that was run.  Dense and packed."""
+    import flash_attn_npu as m
+    torch.manual_seed(21)
+    b, sq, sk, h, hkv, d = 2, 200, 264, 4, 2, 128
+    q, do = (torch.rand(b, sq, h, d) * 2 - 1).bfloat16(), (torch.rand(b, sq, h, d) * 2 - 1).bfloat16()
+    k, v = (torch.rand(b, sk, hkv, d) * 2 - 1).bfloat16(), (torch.rand(b, sk, hkv, d) * 2 - 1).bfloat16()
+    slopes = torch.rand(b, h) * 0.3 if per_batch else torch.rand(h) * 0.3
+    scale = d ** -0.5
+    _, f_l = orc.attention_fwd(q.float(), k.float(), v.float(), scale, causal, window, cap, data_type=torch.float32,
+                               alibi_slopes=slopes)
+    lp = orc.attention_bwd(q, k, v, do, f_l, scale, causal, window, cap, alibi_slopes=slopes)
+    f32 = orc.attention_bwd(q.float(), k.float(), v.float(), do.float(), f_l, scale, causal, window, cap,
+                            alibi_slopes=slopes)
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out, lse, _ = m.flash_attn_func(qc, kc, vc, softmax_scale=scale, causal=causal, window_size=window, softcap=cap,
+                                    alibi_slopes=slopes.cuda(), return_attn_probs=True)
+    grads = torch.autograd.grad(out, (qc, kc, vc), do.cuda())
+    for name, got, a, b_ in zip(("dq", "dk", "dv"), grads, lp, f32):
+        assert_within(name, got.cpu(), a, b_, roundings=3)
+    # without the slopes the gradients differ by far more than the tolerance: the bias is really applied
+    plain = orc.attention_bwd(q.float(), k.float(), v.float(), do.float(), f_l, scale, causal, window, cap)
+    assert (plain[0] - f32[0]).abs().max() > 0.05

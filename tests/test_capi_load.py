@@ -35,7 +35,7 @@ def test_struct_layouts_match_header_sizes():
     assert ctypes.sizeof(capi.FaTensor) == 32
     assert ctypes.sizeof(capi.FwdParams) % 8 == 0
     assert capi.FwdParams.stream.offset + 8 == ctypes.sizeof(capi.FwdParams)
-    assert capi.BwdParams.stream.offset + 8 == ctypes.sizeof(capi.BwdParams)
+    assert capi.BwdParams.alibi_stride_b.offset + 8 == ctypes.sizeof(capi.BwdParams) == 408
 
 
 def test_argument_validation_needs_no_gpu():

@@ -49,12 +49,10 @@ def oracle_fp32(qn, qr, lat, sc, rope, table, lens, scale):
     (2, 80, [129, 4000], 5),
 ])
 @pytest.mark.parametrize("page,family", [(64, "mla_int8_tcgen05_pair"), (256, "mla_int8_tcgen05_pair"),
-                                         (64, "single:mla_int8_tcgen05"), (48, "mla_int8_decode"),
-                                         (64, "forced:mla_int8_decode")])
+                                         (48, "mla_int8_decode"), (64, "forced:mla_int8_decode")])
 def test_mla_decode_matches_oracle(b, h, lens, splits, page, family):
-    """All kernel families: the tcgen05 kernels (a CTA pair that splits the score dims, or one CTA per output half)
-    take pages that hold whole 64-token tiles, the mma.sync kernel everything else (and everything when the
-    generic policy is forced)."""
+    """Both kernel families: the tcgen05 kernel (a CTA pair that splits the score dims) takes pages that hold whole
+    64-token tiles, the mma.sync kernel everything else (and everything when the generic policy is forced)."""
     import flash_attn_npu_3 as m3
     import fa_b200_capi as capi
     gen = torch.Generator().manual_seed(50 + b + h)
@@ -64,7 +62,6 @@ def test_mla_decode_matches_oracle(b, h, lens, splits, page, family):
     f_o, f_l = oracle_fp32(qn, qr, lat, sc, rope, table, lens, scale)
     forced = family.startswith("forced:")
     capi.lib.fa_set_kernel_policy(1 if forced else 0)
-    capi.lib.fa_debug_set(5, 1 if family.startswith("single:") else 0)
     try:
         out, lse = m3.flash_attn_mla_with_kvcache(qn.cuda(), qr.cuda(), lat.cuda(), sc.cuda(), rope.cuda(),
                                                   torch.tensor(lens, dtype=torch.int32).cuda(), table.cuda(),
@@ -72,7 +69,6 @@ def test_mla_decode_matches_oracle(b, h, lens, splits, page, family):
         torch.cuda.synchronize()
     finally:
         capi.lib.fa_set_kernel_policy(0)
-        capi.lib.fa_debug_set(5, 0)
     assert capi.last_kernel() == family.split(":")[-1]
     assert capi.lib.fa_debug_get(2) == 0
     assert_within("out", out.cpu(), lp_o, f_o)

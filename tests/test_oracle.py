@@ -131,3 +131,28 @@ def test_mla_split_equals_unsplit():
     o, l = orc.combine_partials(torch.stack(po), torch.stack(pl))
     assert (o.float() - full.reshape(h, 512).float()).abs().max().item() < 2e-2
     assert (l - lse.reshape(h)).abs().max().item() < 1e-5
+
+
+def test_alibi_backward_of_the_oracle_is_the_derivative_of_its_forward():
+    """The reference holds no golden for alibi in the backward (its backward ignores the slopes), so the restatement
+    is pinned against autograd through the plain formula softmax(scale q k^T - slope |i + sk - sq - j| + mask) v in
+    float64, with the same bottom-right causal mask."""
+    torch.manual_seed(2)
+    b, sq, sk, h, hkv, d = 1, 24, 40, 4, 2, 16
+    q, do = torch.randn(b, sq, h, d, dtype=torch.float64), torch.randn(b, sq, h, d, dtype=torch.float64)
+    k, v = torch.randn(b, sk, hkv, d, dtype=torch.float64), torch.randn(b, sk, hkv, d, dtype=torch.float64)
+    slopes = torch.rand(h) * 0.5
+    scale = 0.3
+    _, lse = orc.attention_fwd(q, k, v, scale, True, data_type=torch.float64, alibi_slopes=slopes)
+    dq, dk, dv = orc.attention_bwd(q, k, v, do, lse, scale, True, alibi_slopes=slopes)
+    qa, ka, va = (t.clone().requires_grad_(True) for t in (q, k, v))
+    kk = ka.repeat_interleave(h // hkv, dim=2)
+    vv = va.repeat_interleave(h // hkv, dim=2)
+    s = torch.einsum("bihd,bjhd->bhij", qa, kk) * scale
+    i, j = torch.arange(sq).view(-1, 1), torch.arange(sk).view(1, -1)
+    s = s - slopes.double().view(1, h, 1, 1) * (i + sk - sq - j).abs().double()
+    s = s.masked_fill(j > i + sk - sq, float("-inf"))
+    out = torch.einsum("bhij,bjhd->bihd", torch.softmax(s, dim=-1), vv)
+    gq, gk, gv = torch.autograd.grad(out, (qa, ka, va), do)
+    for got, ref in ((dq, gq), (dk, gk), (dv, gv)):
+        assert (got - ref).abs().max().item() < 1e-5          # the saved LSE is fp32
