@@ -32,6 +32,11 @@ struct alignas(64) Sm100FwdArgs {
     int b, sq, sk, hq, hkv;
     float scale_log2;
     int causal, wl, wr;
+    // score transforms of the BIAS instantiation: softcap (0 = off) and alibi slopes ((hq) or (b,hq), null = off)
+    float softcap, cap_in;               // cap_in = scale / softcap
+    const float* alibi;
+    int64_t alibi_sb;
+    int kv_box;                          // rows of one K/V copy: 128, or 64 when pages are an odd multiple of 64 tokens
 };
 
 // =================================================================================================
@@ -63,7 +68,7 @@ struct FwdSm100Smem2 {
 #endif
 enum { C_Q = 0, C_KF0, C_KF1, C_KE0, C_KE1, C_VF0, C_VF1, C_VE0, C_VE1, C_SA, C_SB, C_PA, C_PB, C_PA2, C_PB2, C_OA, C_OB, C_COUNT };
 
-template <typename T, int D>
+template <typename T, int D, bool BIAS>
 __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constant__ Sm100FwdArgs a) {
     using L = FwdSm100Smem2<D>;
     constexpr int NSUB = D / 64;
@@ -165,28 +170,43 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
             }
             // where key tile j lives: (row, outermost coordinate) of the K / V maps.  Dense and packed operands: row
             // in the batch entry; cache: row in the cache entry of this batch; paged cache: row inside the page
-            // that the page table names (a tile never straddles pages: the page size is a multiple of 128)
+            // that the page table names (a tile never straddles pages when the page size is a multiple of 128; pages of
+            // an odd multiple of 64 tokens are copied in two boxes of 64 rows, each from its own page)
             const int32_t* btab = a.block_table ? a.block_table + (int64_t)b * a.bt_stride : nullptr;
             const int kbatch = a.cu_q ? 0 : (a.cache_batch_idx ? a.cache_batch_idx[b] : b);
             bool ok = true;
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int st = j & 1, use = j >> 1;
                 int krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128, kouter = kbatch;
+                int krow2 = 0, kouter2 = 0;                       // second half of the tile when it is copied in two boxes of 64 rows
                 if (btab) {
                     const int pos = (t_lo + j) * 128;
                     kouter = btab[pos / a.page_size];
                     krow = pos % a.page_size;
+                    if (a.kv_box == 64) {
+                        // the tile may end in the next page; a half past the table's end is never attended (its
+                        // columns are masked by the length), it is read from the first half's page
+                        const bool in_table = (pos + 64) / a.page_size < a.bt_stride;
+                        kouter2 = in_table ? btab[(pos + 64) / a.page_size] : kouter;
+                        krow2 = in_table ? (pos + 64) % a.page_size : krow;
+                    }
                 }
                 if (use > 0) ok = mbar_wait(bar(C_KE0 + st), (use - 1) & 1, abort_flag, err, 1);
                 if (!ok) break;
                 mbar_expect_tx(bar(C_KF0 + st), L::kKV);
 #pragma unroll
-                for (int s = 0; s < NSUB; ++s) tma_load_4d(sK + st * L::kKV + s * L::kSub, &a.tk, bar(C_KF0 + st), s * 64, hk, krow, kouter);
+                for (int s = 0; s < NSUB; ++s) {
+                    tma_load_4d(sK + st * L::kKV + s * L::kSub, &a.tk, bar(C_KF0 + st), s * 64, hk, krow, kouter);
+                    if (a.kv_box == 64) tma_load_4d(sK + st * L::kKV + s * L::kSub + 64 * 128, &a.tk, bar(C_KF0 + st), s * 64, hk, krow2, kouter2);
+                }
                 if (use > 0) ok = mbar_wait(bar(C_VE0 + st), (use - 1) & 1, abort_flag, err, 2);
                 if (!ok) break;
                 mbar_expect_tx(bar(C_VF0 + st), L::kKV);
 #pragma unroll
-                for (int s = 0; s < NSUB; ++s) tma_load_4d(sV + st * L::kKV + s * L::kSub, &a.tv, bar(C_VF0 + st), s * 64, hk, krow, kouter);
+                for (int s = 0; s < NSUB; ++s) {
+                    tma_load_4d(sV + st * L::kKV + s * L::kSub, &a.tv, bar(C_VF0 + st), s * 64, hk, krow, kouter);
+                    if (a.kv_box == 64) tma_load_4d(sV + st * L::kKV + s * L::kSub + 64 * 128, &a.tv, bar(C_VF0 + st), s * 64, hk, krow2, kouter2);
+                }
             }
         }
     } else if (warp == 9) {
@@ -288,7 +308,12 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
         window_bounds(m0 + x * 128, sq, sk, wl, wr, tmp, hi_f);
         window_bounds(m0 + x * 128 + rows - 1, sq, sk, wl, wr, lo_l, tmp);
         float m_used = -INFINITY, l_run = 0.f;
-        const float sc = a.scale_log2;
+        // BIAS instantiation: the scores are turned into their final log2-domain values in registers (softcap, then
+        // alibi, as the general kernel and the golden do), and the softmax below runs with a unit scale
+        const float sc = BIAS ? 1.f : a.scale_log2;
+        const float cap_out = a.softcap * kLog2e;
+        const float slope = (BIAS && a.alibi) ? a.alibi[(int64_t)b * a.alibi_sb + h] * kLog2e : 0.f;
+        const float rel = (float)(qi + sk - sq);                 // alibi distance of key j is |rel - j|
         bool ok = true;
         const int nt_x = x == 0 ? nt0 : ntiles;
         for (int j = 0; j < nt_x && ok; ++j) {
@@ -308,6 +333,24 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 if (hh == 1) tmem_wait_ld();
+                if constexpr (BIAS) {
+#pragma unroll
+                    for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float xv = __uint_as_float(sreg[c][i]);
+                            if (a.softcap > 0.f) {
+                                // tanh(y) = 1 - 2 / (1 + e^(2y)): two special-function operations, absolute error ~1e-7
+                                const float e2y = ex2_approx(xv * (a.cap_in * 2.f * kLog2e));
+                                xv = cap_out * (1.f - __fdividef(2.f, 1.f + e2y));
+                            } else {
+                                xv *= a.scale_log2;
+                            }
+                            xv -= slope * fabsf(rel - (float)(n0 + c * 32 + i));
+                            sreg[c][i] = __float_as_uint(xv);
+                        }
+                    }
+                }
                 if (!full) {
 #pragma unroll
                     for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
@@ -465,12 +508,11 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
 
 bool fwd_sm100_supported(const fa_fwd_params& p) {
     if (p.d != p.dv || (p.d != 64 && p.d != 128)) return false;
-    if (p.softcap > 0.f || p.alibi_slopes) return false;
     const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
     if (cache) {
         // KV-cache calls (prefill against a cache): lengths and pages are read on the device
         if (p.cu_seqlens_q || p.cu_seqlens_k || !p.seqused_k) return false;
-        if (p.block_table && (p.page_size <= 0 || p.page_size % 128)) return false;
+        if (p.block_table && (p.page_size <= 0 || p.page_size % 64)) return false;
         if (p.sq < 64) return false;                      // short queries belong to the split-KV decode kernels
     }
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
@@ -485,10 +527,10 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
     return encode_fn() != nullptr;
 }
 
-template <typename T, int D>
-static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
+template <typename T, int D, bool BIAS>
+static int launch_sm100_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
-    auto kern = fwd_sm100_kernel2<T, D>;
+    auto kern = fwd_sm100_kernel2<T, D, BIAS>;
     const int smem = FwdSm100Smem2<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
     dim3 grid((p.sq + 255) / 256, p.hq, p.b);
@@ -496,9 +538,14 @@ static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
 }
+template <typename T, int D>
+static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
+    return (p.softcap > 0.f || p.alibi_slopes) ? launch_sm100_b<T, D, true>(p, a) : launch_sm100_b<T, D, false>(p, a);
+}
 
 int launch_fwd_sm100(const fa_fwd_params& p) {
     Sm100FwdArgs a;
+    a.kv_box = 128;
     const bool packed = p.cu_seqlens_q != nullptr;
     const int64_t q_rows = packed ? p.total_q : p.sq;
     const int64_t k_rows = packed ? p.total_k : p.sk;
@@ -511,8 +558,9 @@ int launch_fwd_sm100(const fa_fwd_params& p) {
         // extent is only an upper limit (the page table and cache_batch_idx are valid by contract)
         const int64_t rows = p.block_table ? p.page_size : p.sk;
         const int outer = 1 << 24;
-        if (int e = make_tile_map(&a.tk, p.dtype, p.k.ptr, p.d, p.hkv, rows, outer, p.k.stride_h, p.k.stride_s, p.k.stride_b, 128)) return e;
-        if (int e = make_tile_map(&a.tv, p.dtype, p.v.ptr, p.d, p.hkv, rows, outer, p.v.stride_h, p.v.stride_s, p.v.stride_b, 128)) return e;
+        if (p.block_table && p.page_size % 128) a.kv_box = 64;
+        if (int e = make_tile_map(&a.tk, p.dtype, p.k.ptr, p.d, p.hkv, rows, outer, p.k.stride_h, p.k.stride_s, p.k.stride_b, a.kv_box)) return e;
+        if (int e = make_tile_map(&a.tv, p.dtype, p.v.ptr, p.d, p.hkv, rows, outer, p.v.stride_h, p.v.stride_s, p.v.stride_b, a.kv_box)) return e;
     } else {
         if (int e = make_tile_map(&a.tk, p.dtype, p.k.ptr, p.d, p.hkv, k_rows, nb, p.k.stride_h, p.k.stride_s, bstride(p.k, k_rows), 128)) return e;
         if (int e = make_tile_map(&a.tv, p.dtype, p.v.ptr, p.d, p.hkv, k_rows, nb, p.v.stride_h, p.v.stride_s, bstride(p.v, k_rows), 128)) return e;
@@ -525,6 +573,8 @@ int launch_fwd_sm100(const fa_fwd_params& p) {
     a.cu_q = p.cu_seqlens_q; a.cu_k = p.cu_seqlens_k;
     a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv;
     a.scale_log2 = p.scale * kLog2e;
+    a.softcap = p.softcap; a.cap_in = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
+    a.alibi = p.alibi_slopes; a.alibi_sb = p.alibi_stride_b;
     a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
     note_kernel("sm100_tcgen05_2q");
     if (p.dtype == FA_F16) return p.d == 64 ? launch_sm100_t<__half, 64>(p, a) : launch_sm100_t<__half, 128>(p, a);

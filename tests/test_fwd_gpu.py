@@ -157,6 +157,26 @@ def test_alibi_forward():
         assert_lse(lse, f_l)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("cap,use_alibi", [(3.0, False), (0.0, True), (2.0, True)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_softcap_and_alibi_on_the_tcgen05_forward(d, cap, use_alibi, dt):
+    """softcap (online_softmax.hpp:493-522 applies it in the reference's one forward kernel) and alibi run in the
+    tcgen05 forward: scores are capped with an exact-to-1e-7 tanh and biased in registers before the row maximum.
+    Causal, a window, GQA, ragged tails; scaled scores of standard deviation 2 against caps of 2 and 3, so the cap bites."""
+    import fa_b200_capi as capi
+    torch.manual_seed(17)
+    b, sq, sk, h, hkv = 2, 333, 517, 4, 2
+    q, k, v = (torch.randn(b, sq, h, d) * 2).to(dt), torch.randn(b, sk, hkv, d).to(dt), torch.randn(b, sk, hkv, d).to(dt)
+    slopes = torch.rand(b, h) * 0.2 if use_alibi else None
+    for causal, win in ((True, (-1, -1)), (False, (100, 60))):
+        (lp_o, _), (f_o, f_l) = fwd_refs(q, k, v, d ** -0.5, causal, win, cap, alibi=slopes)
+        out, lse = run_dense(2, q, k, v, d ** -0.5, causal, win, cap, alibi=slopes)
+        assert capi.last_kernel() == "sm100_tcgen05_2q"
+        assert_within("out", out, lp_o, f_o)
+        assert_lse(lse, f_l)
+
+
 def test_strided_inputs_and_packed_variants():
     import flash_attn_npu as m
     torch.manual_seed(6)

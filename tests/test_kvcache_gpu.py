@@ -332,12 +332,13 @@ def test_scheduler_metadata_is_consumed_by_the_decode():
         m3.flash_attn_with_kvcache(qg, kg, vg, cache_seqlens=lg, page_table=tg, causal=True, scheduler_metadata=meta[:16])
 
 
-@pytest.mark.parametrize("paged,page", [(True, 128), (True, 256), (False, 0)])
+@pytest.mark.parametrize("paged,page", [(True, 128), (True, 256), (True, 64), (True, 192), (False, 0)])
 @pytest.mark.parametrize("append", [False, True])
 def test_prefill_against_cache_uses_tcgen05(paged, page, append):
     """A chunk of queries against a KV cache (chunked prefill): ragged device-resident lengths, GQA, optional
     in-place append of the chunk's own keys, cache rows past the lengths filled with NaN (they must not leak
-    into the output); the tcgen05 kernel serves the call."""
+    into the output); the tcgen05 kernel serves the call.  Pages of 64 and 192 tokens make key tiles that span two
+    pages (copied as two boxes of 64 rows)."""
     import flash_attn_npu as m
     import fa_b200_capi as capi
     g = torch.Generator().manual_seed(321)
