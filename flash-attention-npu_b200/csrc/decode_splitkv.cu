@@ -296,14 +296,20 @@ struct alignas(64) DecodeTmaArgs {
     DecodeArgs d;
 };
 
-template <typename T, int HD>
-__global__ void __launch_bounds__(128) decode_tma_kernel(const __grid_constant__ DecodeTmaArgs ta) {
+// WIDE = false: each of the four warps streams the keys of its own KV head and owns a private ring (up to 16 stacked
+// query rows per KV head).  WIDE = true (17-64 stacked rows: several new tokens per step, or large GQA groups): the
+// four warps take 16 rows each of ONE KV head and share one ring, filled by a fifth warp; every tile is fetched
+// once per CTA, a stage is refilled when all four warps have arrived on its "empty" barrier.
+constexpr int kDecWideStages = 6;
+template <typename T, int HD, bool WIDE>
+__global__ void __launch_bounds__(WIDE ? 160 : 128) decode_tma_kernel(const __grid_constant__ DecodeTmaArgs ta) {
     using namespace sm100;
     constexpr int TILE = HD > 128 ? 16 : 32;
     constexpr int NSUB = HD / 64;
     constexpr int SUB_BYTES = TILE * 128;
     constexpr int TILE_BYTES = NSUB * SUB_BYTES;
-    constexpr int WARP_BYTES = 2 * kDecStages * TILE_BYTES;
+    constexpr int STAGES = WIDE ? kDecWideStages : kDecStages;
+    constexpr int WARP_BYTES = 2 * STAGES * TILE_BYTES;
     const DecodeArgs& a = ta.d;
     const fa_fwd_params& p = a.p;
     extern __shared__ unsigned char smem_raw[];
@@ -311,10 +317,11 @@ __global__ void __launch_bounds__(128) decode_tma_kernel(const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, b = blockIdx.z;
-    const int hk = blockIdx.y * 4 + warp;
+    const int hk = WIDE ? blockIdx.y : blockIdx.y * 4 + warp;
     if (hk >= p.hkv) return;
-    const uint32_t sKw = sbase + warp * WARP_BYTES, sVw = sKw + kDecStages * TILE_BYTES;
-    const uint32_t bars = sbase + 4 * WARP_BYTES + warp * 64;
+    const int row_base = WIDE ? warp * 16 : 0;
+    const uint32_t sKw = sbase + (WIDE ? 0 : warp * WARP_BYTES), sVw = sKw + STAGES * TILE_BYTES;
+    const uint32_t bars = sbase + (WIDE ? WARP_BYTES : 4 * WARP_BYTES + warp * 64);     // full[STAGES], then (WIDE) empty[STAGES]
     unsigned char* gen_base = smem_raw + (sbase - smem_addr(smem_raw));
 
     const int G = p.hq / p.hkv;
@@ -338,7 +345,7 @@ __global__ void __launch_bounds__(128) decode_tma_kernel(const __grid_constant__
     float slope[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        vrow[r] = g + r * 8;
+        vrow[r] = row_base + g + r * 8;
         const bool ok = vrow[r] < rows_total;
         qpos[r] = ok ? vrow[r] / G : 0;
         head[r] = hk * G + (ok ? vrow[r] % G : 0);
@@ -367,14 +374,25 @@ __global__ void __launch_bounds__(128) decode_tma_kernel(const __grid_constant__
         }
     }
     const int32_t* btab = p.block_table ? p.block_table + (int64_t)b * p.block_table_stride : nullptr;
-    if (lane == 0) {
+    if constexpr (WIDE) {
+        if (threadIdx.x == 0) {
 #pragma unroll
-        for (int s = 0; s < kDecStages; ++s) mbar_init(bars + 8 * s, 1);
-        mbar_fence_init();
-        tma_prefetch_desc(&ta.tk);
-        tma_prefetch_desc(&ta.tv);
+            for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (STAGES + s), 4); }
+            mbar_fence_init();
+            tma_prefetch_desc(&ta.tk);
+            tma_prefetch_desc(&ta.tv);
+        }
+        __syncthreads();
+    } else {
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8 * s, 1);
+            mbar_fence_init();
+            tma_prefetch_desc(&ta.tk);
+            tma_prefetch_desc(&ta.tv);
+        }
+        __syncwarp();
     }
-    __syncwarp();
 
     auto issue_tile = [&](int tok0, int stage) {       // lane 0 only
         int c2 = tok0, c3 = kb;
@@ -395,10 +413,33 @@ __global__ void __launch_bounds__(128) decode_tma_kernel(const __grid_constant__
     for (int i = 0; i < HD / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
     float m_i[2] = {-INFINITY, -INFINITY}, l_i[2] = {0.f, 0.f};
     const int ntiles = t_end > t_begin ? (t_end - t_begin + TILE - 1) / TILE : 0;
-    if (lane == 0) {
+    if constexpr (WIDE) {
+        if (warp == 4) {                                      // producer: refills a stage once its four readers have left it
+            if (lane == 0) {
+                for (int it = 0; it < ntiles; ++it) {
+                    const int stage = it % STAGES, use = it / STAGES;
+                    if (use > 0) {
+                        const uint32_t bar = bars + 8 * (STAGES + stage), parity = (use - 1) & 1;
+                        if (!mbar_try_wait(bar, parity)) {
+                            const long long t0 = clock64();
+                            bool alive = true;
+                            while (!mbar_try_wait(bar, parity)) {
+                                if (clock64() - t0 > kWaitCycles) { alive = false; break; }
+                            }
+                            if (!alive) { atomicCAS(&g_decode_error, 0, 42); break; }     // the readers time out on their side
+                        }
+                    }
+                    issue_tile(t_begin + it * TILE, stage);
+                }
+            }
+            return;
+        }
+    } else {
+        if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < kDecStages - 1; ++s)
-            if (s < ntiles) issue_tile(t_begin + s * TILE, s);
+            for (int s = 0; s < STAGES - 1; ++s)
+                if (s < ntiles) issue_tile(t_begin + s * TILE, s);
+        }
     }
     const float scale_log2 = p.scale * kLog2e;
     const bool has_cap = p.softcap > 0.f;
@@ -407,11 +448,15 @@ __global__ void __launch_bounds__(128) decode_tma_kernel(const __grid_constant__
     bool alive = true;
 
     for (int it = 0; it < ntiles && alive; ++it) {
-        const int stage = it % kDecStages;
+        const int stage = it % STAGES;
         __syncwarp();                                         // everyone is done with the stage refilled next
-        if (lane == 0 && it + kDecStages - 1 < ntiles) issue_tile(t_begin + (it + kDecStages - 1) * TILE, (it + kDecStages - 1) % kDecStages);
+        if constexpr (WIDE) {
+            if (it > 0 && lane == 0) mbar_arrive(bars + 8 * (STAGES + (it - 1) % STAGES));
+        } else {
+            if (lane == 0 && it + STAGES - 1 < ntiles) issue_tile(t_begin + (it + STAGES - 1) * TILE, (it + STAGES - 1) % STAGES);
+        }
         {   // bounded wait for this tile
-            const uint32_t bar = bars + 8 * stage, parity = (it / kDecStages) & 1;
+            const uint32_t bar = bars + 8 * stage, parity = (it / STAGES) & 1;
             if (!mbar_try_wait(bar, parity)) {
                 const long long t0 = clock64();
                 while (!mbar_try_wait(bar, parity)) {
@@ -537,6 +582,7 @@ template <typename T, int HD>
 static int launch_decode_tma_t(const DecodeArgs& a, cudaStream_t st) {
     const fa_fwd_params& p = a.p;
     constexpr int TILE = HD > 128 ? 16 : 32;
+    const bool wide = p.sq * (p.hq / p.hkv) > 16;
     DecodeTmaArgs ta;
     ta.d = a;
     // rows: tokens of a page (paged) or of the cache (dense); the outermost extent is not known to the
@@ -545,11 +591,19 @@ static int launch_decode_tma_t(const DecodeArgs& a, cudaStream_t st) {
     const int outer = 1 << 24;
     if (int e = make_tile_map(&ta.tk, p.dtype, p.k.ptr, p.d, p.hkv, rows, outer, p.k.stride_h, p.k.stride_s, p.k.stride_b, TILE)) return e;
     if (int e = make_tile_map(&ta.tv, p.dtype, p.v.ptr, p.dv, p.hkv, rows, outer, p.v.stride_h, p.v.stride_s, p.v.stride_b, TILE)) return e;
-    const size_t smem = (size_t)4 * 2 * kDecStages * TILE * HD * 2 + 4 * 64 + 1024;
-    auto kern = decode_tma_kernel<T, HD>;
-    if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "cudaFuncSetAttribute")) return e;
-    dim3 grid(a.nsplit, (p.hkv + 3) / 4, p.b);
-    kern<<<grid, 128, smem, st>>>(ta);
+    if (wide) {
+        const size_t smem = (size_t)2 * kDecWideStages * TILE * HD * 2 + 2 * kDecWideStages * 8 + 1024;
+        auto kern = decode_tma_kernel<T, HD, true>;
+        if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "cudaFuncSetAttribute")) return e;
+        dim3 grid(a.nsplit, p.hkv, p.b);
+        kern<<<grid, 160, smem, st>>>(ta);
+    } else {
+        const size_t smem = (size_t)4 * 2 * kDecStages * TILE * HD * 2 + 4 * 64 + 1024;
+        auto kern = decode_tma_kernel<T, HD, false>;
+        if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "cudaFuncSetAttribute")) return e;
+        dim3 grid(a.nsplit, (p.hkv + 3) / 4, p.b);
+        kern<<<grid, 128, smem, st>>>(ta);
+    }
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "decode_tma launch");
 }
@@ -578,10 +632,11 @@ void decode_set_use_tma(int v) { g_decode_use_tma = v; }
 
 bool fwd_decode_supported(const fa_fwd_params& p) {
     const int G = p.hq / p.hkv;
-    if (p.sq * G > 16) return false;
     if (!(p.seqused_k || p.block_table)) return false;       // KV-cache calls only
     if (p.cu_seqlens_k) return false;
-    return true;
+    if (p.sq * G <= 16) return true;
+    // 17-64 stacked rows: only the TMA kernel has the form in which four warps share a KV head's tiles
+    return p.sq * G <= 64 && g_decode_use_tma && decode_tma_ok(p);
 }
 
 int launch_fwd_decode(const fa_fwd_params& p, const FwdPlan& plan, float* o_part, float* lse_part) {

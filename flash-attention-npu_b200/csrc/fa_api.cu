@@ -83,8 +83,9 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
     else if (p.num_splits == 0 && plan.use_decode && nblocks > 1) {
         // decode kernel: the unit of parallelism is a warp per (sequence, KV head, split); aim at about
         // 1024 keys per split, at least four waves of warps, and never fewer than 256 keys per split
+        // (with 17-64 stacked rows a whole CTA streams one KV head: four waves of CTAs)
         const long base = (long)p.hkv * (p.b > 0 ? p.b : 1);
-        const long target = 16L * sm_count();
+        const long target = (p.sq * G > 16 ? 4L : 16L) * sm_count();
         const long by_occ = (target + base - 1) / base;
         const long by_bal = (p.sk + 1023) / 1024;
         const long cap = (p.sk + 255) / 256;

@@ -93,6 +93,60 @@ def test_kvcache_matrix(case):
     assert_lse(lse, f_l)
 
 
+# (dtype, B, H, Hkv, Sq, D, paged, causal, window, softcap): 17 to 64 stacked rows (Sq x group) a KV head
+WIDE_CASES = [
+    (torch.bfloat16, 3, 32, 4, 4, 128, True, True, (-1, -1), 0.0),       # 32 rows: four new tokens a step, group of 8
+    (torch.bfloat16, 2, 32, 1, 1, 128, False, False, (-1, -1), 0.0),     # 32 rows: one token, group of 32 (multi-query)
+    (torch.float16, 2, 16, 2, 5, 64, True, True, (-1, -1), 0.0),         # 40 rows: the last warp is half empty
+    (torch.bfloat16, 2, 16, 2, 8, 128, True, True, (300, 0), 0.0),       # 64 rows, sliding window
+    (torch.bfloat16, 1, 48, 3, 3, 256, False, True, (-1, -1), 0.0),      # 48 rows, head dim 256 (16-token tiles)
+    (torch.bfloat16, 2, 24, 8, 6, 128, True, False, (-1, -1), 25.0),     # 18 rows, softcap
+]
+
+
+@pytest.mark.parametrize("case", WIDE_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+@pytest.mark.parametrize("num_splits", [0, 1, 5])
+def test_decode_with_17_to_64_stacked_rows_runs_on_the_tma_kernel(case, num_splits):
+    """Several new tokens a step and large query groups stack more than 16 rows on a KV head: four warps share the
+    head's tiles, 16 rows each.  Ragged device-resident lengths (one shorter than a tile), NaN past the lengths."""
+    import flash_attn_npu as m
+    import fa_b200_capi as capi
+    dt, b, h, hkv, sq, d, paged, causal, win, cap = case
+    gen = torch.Generator().manual_seed(5 + h + sq)
+    lens = [1500, 9, 777][:b]
+    page, capacity = 64, 2048
+    q = torch.randn(b, sq, h, d, generator=gen).to(dt)
+    if paged:
+        kc, vc, table = paged_setup(gen, b, [capacity - 1] * b, hkv, d, page, dt)
+        for i, L in enumerate(lens):
+            for j in range(table.shape[1]):
+                lo = max(0, L - j * page)
+                if lo < page:
+                    kc[table[i, j], lo:] = float("nan")
+                    vc[table[i, j], lo:] = float("nan")
+    else:
+        kc, vc, table = torch.randn(b, capacity, hkv, d, generator=gen).to(dt), torch.randn(b, capacity, hkv, d, generator=gen).to(dt), None
+        for i, L in enumerate(lens):
+            kc[i, L:] = float("nan")
+            vc[i, L:] = float("nan")
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    scale = d ** -0.5
+    rk, rv = torch.nan_to_num(kc.clone()), torch.nan_to_num(vc.clone())
+    lp_o, _ = orc.kvcache_fwd(q, rk.clone(), rv.clone(), lens_t, scale, block_table=table, causal=causal, window=win, softcap=cap)
+    f_o, f_l = orc.kvcache_fwd(q.float(), rk.float(), rv.float(), lens_t, scale, block_table=table, causal=causal, window=win,
+                               softcap=cap)
+    out, lse = m.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=lens_t.cuda(),
+                                         block_table=None if table is None else table.cuda(), softmax_scale=scale,
+                                         causal=causal, window_size=win, softcap=cap, num_splits=num_splits,
+                                         return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert capi.last_kernel() == "decode_splitkv_tma"
+    assert capi.lib.fa_debug_get(2) == 0
+    assert torch.isfinite(out).all()
+    assert_within("out", out.cpu(), lp_o, f_o)
+    assert_lse(lse, f_l)
+
+
 @pytest.mark.parametrize("interleaved", [False, True])
 @pytest.mark.parametrize("paged", [True, False])
 @pytest.mark.parametrize("s_new,sq,causal", [(1, 1, True), (3, 3, True), (2, 5, False)])
