@@ -196,20 +196,13 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
             const uint64_t dQk = umma_desc(sQ, 16, 1024), dOk = umma_desc(sdO, 16, 1024);           // K-major views
             const uint64_t dQm = umma_desc(sQ, L::kSub, 1024), dOm = umma_desc(sdO, L::kSub, 1024); // MN-major views
             auto issue_scores = [&](uint32_t d_t, uint64_t a0, uint64_t b0, int st) {
-                const uint64_t bt = umma_desc_at(b0, st * L::kTileB);
-                umma_ss_w<0>(d_t, a0, bt, IDESC_ST);
-#pragma unroll
-                for (int kk = 1; kk < KSTEPS; ++kk) {
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss_w<1>(d_t, umma_desc_at(a0, off), umma_desc_at(bt, off), IDESC_ST);
-                }
+                umma_ss_scores<KSTEPS, L::kSub>(d_t, a0, umma_desc_at(b0, st * L::kTileB), IDESC_ST);
             };
             // acc += A (tensor memory: 16 queries in 8 columns at a stride of 16) x B (query-major tile of stage st)
             auto issue_acc = [&](uint32_t d_t, uint32_t a_t, uint64_t b0, int st, bool first) {
                 const uint64_t bt = umma_desc_at(b0, st * L::kTileB);
-                if (!first) umma_ts_w<1>(d_t, a_t, bt, IDESC_ACC); else umma_ts_w<0>(d_t, a_t, bt, IDESC_ACC);
-#pragma unroll
-                for (int kk = 1; kk < 8; ++kk) umma_ts_w<1>(d_t, a_t + kk * 16, umma_desc_at(bt, kk * 2048), IDESC_ACC);
+                umma_ts_group4<0, 16, 0, 128>(d_t, a_t, bt, IDESC_ACC, !first);
+                umma_ts_group4<64, 16, 512, 128>(d_t, a_t, bt, IDESC_ACC, 1);
             };
             bool ok = mbar_wait(bar(E_FIX), 0, abort_flag, err, 22);
             if (ok) ok = mbar_wait(bar(E_RF0), 0, abort_flag, err, 23);
@@ -473,13 +466,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
             const uint64_t dKm = umma_desc(sK, L::kSub, 1024);
             // [128 queries x 128 keys] = A (Q or dO, K-major) x B (K or V tile of stage st, K-major)
             auto issue_scores = [&](uint32_t d_t, uint64_t a0, uint64_t b0, int stage) {
-                const uint64_t bt = umma_desc_at(b0, stage * L::kTileB);
-                umma_ss_w<0>(d_t, a0, bt, IDESC_S);
-#pragma unroll
-                for (int kk = 1; kk < KSTEPS; ++kk) {
-                    const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-                    umma_ss_w<1>(d_t, umma_desc_at(a0, off), umma_desc_at(bt, off), IDESC_S);
-                }
+                umma_ss_scores<KSTEPS, L::kSub>(d_t, a0, umma_desc_at(b0, stage * L::kTileB), IDESC_S);
             };
             bool ok = mbar_wait(bar(G_FIX), 0, abort_flag, err, 32);
             if (ok) ok = mbar_wait(bar(G_KF0), 0, abort_flag, err, 33);
@@ -513,9 +500,8 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
                 tc_fence_after();
                 // dQ += dS (tensor memory, 16 keys in 8 columns at a stride of 16) x K tile read key-major
                 const uint64_t bk = umma_desc_at(dKm, ks * L::kTileB);
-                if (t > 0) umma_ts_w<1>(tmem + COL_DQ, tmem + COL_DP, bk, IDESC_ACC); else umma_ts_w<0>(tmem + COL_DQ, tmem + COL_DP, bk, IDESC_ACC);
-#pragma unroll
-                for (int kk = 1; kk < 8; ++kk) umma_ts_w<1>(tmem + COL_DQ, tmem + COL_DP + kk * 16, umma_desc_at(bk, kk * 2048), IDESC_ACC);
+                umma_ts_group4<0, 16, 0, 128>(tmem + COL_DQ, tmem + COL_DP, bk, IDESC_ACC, t > 0);
+                umma_ts_group4<64, 16, 512, 128>(tmem + COL_DQ, tmem + COL_DP, bk, IDESC_ACC, 1);
                 umma_commit_w(bar(G_KE0 + ks));
             }
             if (ok) umma_commit_w(bar(G_ACC));
@@ -707,9 +693,8 @@ __global__ void __launch_bounds__(192, 1) bwd_dq_from_ds_sm100_kernel(const __gr
             // A: the dS^T tile as stored ([chunk][key][16 B], no swizzle): 8 keys of a chunk are 128 contiguous bytes,
             // chunks are 2048 bytes apart, a K step of 16 keys is 256 bytes further on; B: the K tile (128-byte swizzle)
             const uint64_t dA = umma_desc_mn_noswizzle(s0, 128, 2048), dB = umma_desc(s0 + 2 * L::kSub, L::kSub, 1024);
-            if (j > 0) umma_ss_w<1>(tmem, dA, dB, IDESC); else umma_ss_w<0>(tmem, dA, dB, IDESC);
-#pragma unroll
-            for (int kk = 1; kk < 8; ++kk) umma_ss_w<1>(tmem, umma_desc_at(dA, kk * 256), umma_desc_at(dB, kk * 2048), IDESC);
+            umma_ss_group4<0, 16, 32, 48, 0, 128, 256, 384>(tmem, dA, dB, IDESC, j > 0);
+            umma_ss_group4<64, 80, 96, 112, 512, 640, 768, 896>(tmem, dA, dB, IDESC, 1);
             umma_commit_w(bar(H_KE0 + st));
         }
         if (ok) umma_commit_w(bar(H_ACC));

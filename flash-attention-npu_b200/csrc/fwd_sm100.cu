@@ -152,12 +152,12 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     const int qb = a.cu_q ? 0 : b;
 
     // Register file split by warp group: the copy/MMA group (warps 8-11, of which 10 and 11 only
-    // exist to complete the group) keeps 48 registers a thread, the two softmax groups take 224.  The sum
+    // exist to complete the group) keeps 56 registers a thread, the two softmax groups take 224.  The sum
     // 128*48 + 256*224 must stay within what the CTA was launched with (384 threads * 168 registers): an
     // increase beyond the CTA's pool would block forever.
-    static_assert(128 * 48 + 256 * 224 <= 384 * 168, "register split exceeds the CTA's allocation");
+    static_assert(128 * 56 + 256 * 224 <= 384 * 168, "register split exceeds the CTA's allocation");
     if (warp >= 8) {
-    reg_dealloc<48>();
+    reg_dealloc<56>();
     if (warp == 8) {
         if (lane == 0) {
             tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
@@ -211,27 +211,21 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
         }
     } else if (warp == 9) {
         {   // whole warp, one elected lane issues (see umma_ss_w)
-            // descriptors of the tile origins, built once; every MMA adds a compile-time offset
+            // descriptors of the tile origins, built once; the grouped issue adds compile-time offsets
             const uint64_t dQ0 = umma_desc(sQ, 16, 1024), dK0 = umma_desc(sK, 16, 1024), dV0 = umma_desc(sV, L::kSub, 1024);
             auto issue_qk = [&](int x, int st) {
-                const uint32_t d_s = tmem + x * 128;
-                const uint64_t aq = umma_desc_at(dQ0, x * L::kQ), bk = umma_desc_at(dK0, st * L::kKV);
-                umma_ss_wo<0, 0, 0>(d_s, aq, bk, IDESC_QK);
-                static_for<1, KSTEPS>([&](auto kk) {
-                    constexpr uint32_t off = (kk.value >> 2) * L::kSub + (kk.value & 3) * 32;
-                    umma_ss_wo<1, off, off>(d_s, aq, bk, IDESC_QK);
-                });
+                umma_ss_scores<KSTEPS, L::kSub>(tmem + x * 128, umma_desc_at(dQ0, x * L::kQ), umma_desc_at(dK0, st * L::kKV), IDESC_QK);
                 umma_commit_w(bar(C_SA + x));
             };
-            // P·V of tile x in two halves of 64 keys: the second half waits for its own barrier
+            // P·V of tile x in two halves of 64 keys (16 keys = 8 columns of P, 2048 bytes of V a step): the second
+            // half waits for its own barrier
             auto issue_pv = [&](int x, int st, int j) -> bool {
                 const uint64_t bv = umma_desc_at(dV0, st * L::kKV);
                 const uint32_t d_o = tmem + 256 + x * 128, a_p = tmem + x * 128;
-                if (j > 0) umma_ts_wo<1, 0, 0>(d_o, a_p, bv, IDESC_PV); else umma_ts_wo<0, 0, 0>(d_o, a_p, bv, IDESC_PV);
-                static_for<1, 4>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
+                umma_ts_group4<0, 8, 0, 128>(d_o, a_p, bv, IDESC_PV, j > 0);
                 if (!mbar_wait(bar(C_PA2 + x), j & 1, abort_flag, err, 11)) return false;
                 tc_fence_after();
-                static_for<4, 8>([&](auto kk) { umma_ts_wo<1, kk.value * 8, kk.value * 2048>(d_o, a_p, bv, IDESC_PV); });
+                umma_ts_group4<32, 8, 512, 128>(d_o, a_p, bv, IDESC_PV, 1);
                 return true;
             };
             bool ok = mbar_wait(bar(C_Q), 0, abort_flag, err, 3);

@@ -159,18 +159,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
                 tc_fence_after();
                 const uint32_t d_s = tmem + 256 + s * 64;
                 const uint64_t dK = umma_desc(sK + kb * kKBuf, 16, 1024);
-                umma_ts_wo<0, 0, 0>(d_s, tmem + 384, dK, IDESC_QK);
-                static_for<1, 16>([&](auto kk) {
-                    constexpr uint32_t off = (kk.value >> 2) * kKSub + (kk.value & 3) * 32;
-                    umma_ts_wo<1, kk.value * 8, off>(d_s, tmem + 384, dK, IDESC_QK);
-                });
-                if (rank == 0) {
-                    const uint64_t bk = umma_desc_at(dK, 4 * kKSub);
-                    umma_ss_wo<1, 0, 0>(d_s, dQr, bk, IDESC_QK);
-                    umma_ss_wo<1, 32, 32>(d_s, dQr, bk, IDESC_QK);
-                    umma_ss_wo<1, 64, 64>(d_s, dQr, bk, IDESC_QK);
-                    umma_ss_wo<1, 96, 96>(d_s, dQr, bk, IDESC_QK);
-                }
+                // 16 dims = 8 columns of Q and 32 bytes of the tile a step; the four 64-dim sub-tiles lie kKSub apart
+                constexpr uint32_t KS = kKSub >> 4;
+                umma_ts_group4<0, 8, 0, 2>(d_s, tmem + 384, dK, IDESC_QK, 0);
+                umma_ts_group4<32, 8, KS, 2>(d_s, tmem + 384, dK, IDESC_QK, 1);
+                umma_ts_group4<64, 8, 2 * KS, 2>(d_s, tmem + 384, dK, IDESC_QK, 1);
+                umma_ts_group4<96, 8, 3 * KS, 2>(d_s, tmem + 384, dK, IDESC_QK, 1);
+                if (rank == 0) umma_ss_group4<0, 2, 4, 6, 0, 2, 4, 6>(d_s, dQr, umma_desc_at(dK, 4 * kKSub), IDESC_QK, 1);
                 umma_commit_w(bar(P_S0 + s));
                 return true;
             };
@@ -180,10 +175,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) mla_pai
                 tc_fence_after();
                 const uint32_t a_p = tmem + 256 + s * 64;
                 const uint64_t dV = umma_desc(sK + kb * kKBuf, kKSub, 1024);  // MN-major: four 64-column groups kKSub apart
-                if (j > 0) umma_ts_wo<1, 0, 0>(tmem, a_p, dV, IDESC_PV); else umma_ts_wo<0, 0, 0>(tmem, a_p, dV, IDESC_PV);
-                umma_ts_wo<1, 8, 2048>(tmem, a_p, dV, IDESC_PV);
-                umma_ts_wo<1, 16, 4096>(tmem, a_p, dV, IDESC_PV);
-                umma_ts_wo<1, 24, 6144>(tmem, a_p, dV, IDESC_PV);
+                umma_ts_group4<0, 8, 0, 128>(tmem, a_p, dV, IDESC_PV, j > 0);
                 umma_commit_w(bar(P_KE0 + kb));
                 return true;
             };
