@@ -241,8 +241,11 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                 const bool more = j + 1 < ntiles;
                 const int st1 = (j + 1) & 1, use1 = (j + 1) >> 1;
                 const bool a_on = j < nt0, a_more = j + 1 < nt0;          // the first 128 rows take part in tile j / j+1
-                if (a_on) ok = mbar_wait(bar(C_PA), j & 1, abort_flag, err, 5);
-                if (ok) ok = mbar_wait(bar(C_VF0 + st), use & 1, abort_flag, err, 6);
+                // The copies of V(j) and K(j+1) were started a whole tile ago: their barriers are passed first, so that
+                // nothing but the MMAs themselves stands between "P is ready" and the tensor core (this warp's
+                // instructions are on the critical path of both query tiles).
+                ok = mbar_wait(bar(C_VF0 + st), use & 1, abort_flag, err, 6);
+                if (ok && more) ok = mbar_wait(bar(C_KF0 + st1), use1 & 1, abort_flag, err, 7);
                 if (!ok) break;
                 if (a.seqused_k && (t_lo + j) * 128 + 128 > sk) {
                     // Rows of a cache past the sequence hold whatever was there before (possibly NaN patterns): their
@@ -256,17 +259,14 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                     fence_proxy_async_smem();
                     __syncwarp();
                 }
-                tc_fence_after();
                 if (a_on) {
+                    ok = mbar_wait(bar(C_PA), j & 1, abort_flag, err, 5);
+                    if (!ok) break;
+                    tc_fence_after();
                     ok = issue_pv(0, st, j);
                     if (!ok) break;
                     if (!a_more) umma_commit_w(bar(C_OA));
-                }
-                if (more) {
-                    ok = mbar_wait(bar(C_KF0 + st1), use1 & 1, abort_flag, err, 7);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (a_more) issue_qk(0, st1);
+                    else issue_qk(0, st1);
                 }
                 if (has_b) {
                     ok = mbar_wait(bar(C_PB), j & 1, abort_flag, err, 8);
