@@ -59,6 +59,10 @@ struct alignas(64) Sm100BwdArgs {
     // stored as [16 chunks of 8 queries][128 keys][8 queries]
     void* ds_tiles;
     int nkb, nqb;
+    // score transforms of the BIAS instantiation of the dK/dV kernel: softcap (0 = off) and alibi slopes (null = off)
+    float softcap, cap_in2, cap_out;     // cap_in2 = 2 log2(e) scale / softcap, cap_out = softcap log2(e)
+    const float* alibi;
+    int64_t alibi_sb;
 };
 
 template <int D>
@@ -95,7 +99,7 @@ __device__ __forceinline__ void store_row_scaled(T* dst, const uint32_t (&r)[32]
 // ------------------------------------------------------------------------------------------------------
 // dK / dV
 // ------------------------------------------------------------------------------------------------------
-template <typename T, int D>
+template <typename T, int D, bool BIAS>
 __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
     using L = BwdSm100Smem<D>;
     constexpr int NSUB = D / 64, KSTEPS = D / 16;
@@ -281,11 +285,35 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
             tmem_ld32(tmem + lane_base + COL_ST + cg * 32, pr);
             tmem_wait_ld();
             const bool inside = __all_sync(0xffffffffu, i0 >= qi_lo && i0 + 31 <= qi_hi);
+            float slope = 0.f;
+            if constexpr (BIAS) { if (a.alibi) slope = a.alibi[(int64_t)b * a.alibi_sb + hk * G + s / nmb] * kLog2e; }
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
                 const float4 nl = *reinterpret_cast<const float4*>(vec + i);
-                const float2 x01 = fma2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), sc2, make_float2(nl.x, nl.y));
-                const float2 x23 = fma2(make_float2(__uint_as_float(pr[i + 2]), __uint_as_float(pr[i + 3])), sc2, make_float2(nl.z, nl.w));
+                float2 x01, x23;
+                float fac[4] = {1.f, 1.f, 1.f, 1.f};                      // d(capped score) / d(scaled score)
+                if constexpr (BIAS) {
+                    // scores -> their final log2-domain values: softcap (tanh(y) = 1 - 2 / (1 + e^(2y))), then the alibi
+                    // bias -slope |query position + sk - sq - key|, as the forward did
+                    float xv[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float v = __uint_as_float(pr[i + e]);
+                        if (a.softcap > 0.f) {
+                            const float th = 1.f - __fdividef(2.f, 1.f + ex2_approx(v * a.cap_in2));
+                            v = a.cap_out * th;
+                            fac[e] = 1.f - th * th;
+                        } else {
+                            v *= a.scale_log2;
+                        }
+                        xv[e] = v - slope * fabsf((float)(i0 + i + e + sk - sq - n));
+                    }
+                    x01 = make_float2(xv[0] + nl.x, xv[1] + nl.y);
+                    x23 = make_float2(xv[2] + nl.z, xv[3] + nl.w);
+                } else {
+                    x01 = fma2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), sc2, make_float2(nl.x, nl.y));
+                    x23 = fma2(make_float2(__uint_as_float(pr[i + 2]), __uint_as_float(pr[i + 3])), sc2, make_float2(nl.z, nl.w));
+                }
                 float2 p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
                 float2 p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
                 if (!inside) {
@@ -295,8 +323,9 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
                     p23.x = (qi + 2 >= qi_lo && qi + 2 <= qi_hi) ? p23.x : 0.f;
                     p23.y = (qi + 3 >= qi_lo && qi + 3 <= qi_hi) ? p23.y : 0.f;
                 }
-                pr[i] = __float_as_uint(p01.x); pr[i + 1] = __float_as_uint(p01.y);
-                pr[i + 2] = __float_as_uint(p23.x); pr[i + 3] = __float_as_uint(p23.y);
+                // kept for phase B: P (times the softcap derivative, which then multiplies dS)
+                pr[i] = __float_as_uint(p01.x * fac[0]); pr[i + 1] = __float_as_uint(p01.y * fac[1]);
+                pr[i + 2] = __float_as_uint(p23.x * fac[2]); pr[i + 3] = __float_as_uint(p23.y * fac[3]);
                 const uint32_t w0 = Elem<T>::pack(p01.x, p01.y), w1 = Elem<T>::pack(p23.x, p23.y);
                 if (i < 16) { lo8[i / 2] = w0; lo8[i / 2 + 1] = w1; } else { hi8[(i - 16) / 2] = w0; hi8[(i - 16) / 2 + 1] = w1; }
             }
@@ -779,9 +808,13 @@ __global__ void __launch_bounds__(256) bwd_delta_sm100_kernel(const fa_bwd_param
 static std::atomic<int> g_ds_spill{1};
 void bwd_sm100_set_ds_spill(int v) { g_ds_spill = v; }
 
+static size_t ds_tiles_bytes(const fa_bwd_params& p);
+
 bool bwd_sm100_supported(const fa_bwd_params& p) {
     if (p.d != p.dv_dim || (p.d != 64 && p.d != 128)) return false;
-    if (p.softcap > 0.f || p.alibi_slopes || !(p.scale > 0.f)) return false;
+    if (!(p.scale > 0.f)) return false;
+    // softcap and alibi live in the dK/dV kernel only: such calls need the five-GEMM path (dense, dS tiles in the workspace)
+    if ((p.softcap > 0.f || p.alibi_slopes) && !(g_ds_spill && ds_tiles_bytes(p) > 0)) return false;
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
     if (p.sq <= 0 || p.sk <= 0) return false;
     if (p.cu_seqlens_q && (p.total_q <= 0 || p.total_k <= 0)) return false;
@@ -818,7 +851,8 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
         bwd_delta_sm100_kernel<T, D><<<blocks, 256, 0, st>>>(p, delta);
     }
     mark_kernel(st);
-    auto k1 = bwd_dkdv_sm100_kernel<T, D>;
+    const bool bias = p.softcap > 0.f || p.alibi_slopes;
+    auto k1 = bias ? bwd_dkdv_sm100_kernel<T, D, true> : bwd_dkdv_sm100_kernel<T, D, false>;
     auto k2 = bwd_dq_sm100_kernel<T, D>;
     const int smem = BwdSm100Smem<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
@@ -834,6 +868,7 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
         mark_kernel(st);
         return cuda_ok(cudaGetLastError(), "bwd_sm100 launch");
     }
+    if (bias) return fail(FA_ERR_WORKSPACE, "softcap / alibi in the backward need the workspace fa_bwd_workspace_bytes() asks for");
     const int smem_dq = 7 * BwdSm100Smem<D>::kTileB + 256 + 1024;     // Q, dO, three K stages, two V stages, barriers
     if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq), "cudaFuncSetAttribute")) return e;
     dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g2((p.sq + 127) / 128, p.hq, p.b);
@@ -869,6 +904,8 @@ int launch_bwd_sm100(const fa_bwd_params& p) {
     a.cu_q = p.cu_seqlens_q; a.cu_k = p.cu_seqlens_k;
     a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv;
     a.scale = p.scale; a.scale_log2 = p.scale * kLog2e;
+    a.softcap = p.softcap; a.cap_in2 = p.softcap > 0.f ? 2.f * kLog2e * p.scale / p.softcap : 0.f; a.cap_out = p.softcap * kLog2e;
+    a.alibi = p.alibi_slopes; a.alibi_sb = p.alibi_stride_b;
     a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
     float* delta = reinterpret_cast<float*>(p.workspace);

@@ -24,8 +24,6 @@ struct DecodeArgs {
     float* o_part;
     float* lse_part;
     const int32_t* meta;          // scheduler-metadata blob or null
-    int fuse_append;              // TMA kernel only: append k_new / v_new (with rotary) and rotate q inside the kernel
-    int rotate_by_pos;
 };
 
 // Keys per split for sequence b: the blob's per-sequence figure when the blob was built for this launch (same batch
@@ -336,41 +334,6 @@ __global__ void __launch_bounds__(WIDE ? 160 : 128) decode_tma_kernel(const __gr
     const int wl = p.window_left, wr = p.causal ? 0 : p.window_right;
     const int rb = max(0, p.kv_begin), re = p.kv_end > 0 ? min(sk, p.kv_end) : sk;
     const int tps = keys_per_split(a, b, sk);
-    const bool rot_q = a.fuse_append && p.rotary_cos && p.rotary_sin;
-    const int len_raw = p.seqused_k ? p.seqused_k[b] : 0;
-    if (a.fuse_append && p.k_new.ptr && p.s_new > 0 && (!WIDE || warp == 0)) {
-        // In-place append of the step's new keys and values (keys with rotary embedding), by the one warp whose split
-        // reads the position: split ranges partition the cache in multiples of 64 keys and tiles never straddle
-        // them, so no other CTA copies these rows.  The rows are stored before this CTA's first bulk copy of them:
-        // every storing lane fences its stores towards the asynchronous proxy, then the warp (CTA) synchronises.
-        const int rd = p.rotary_cos ? p.rotary_dim : 0;
-        for (int i = 0; i < p.s_new; ++i) {
-            const int pos = len_raw + i;
-            if (pos < 0 || pos >= p.sk) continue;                 // a length outside the cache appends nothing
-            if (min(pos / tps, a.nsplit - 1) != split) continue;
-            int64_t koff, voff;
-            if (p.block_table) {
-                const int blk = p.block_table[(int64_t)b * p.block_table_stride + pos / p.page_size];
-                const int rin = pos % p.page_size;
-                koff = (int64_t)blk * p.k.stride_b + (int64_t)rin * p.k.stride_s + (int64_t)hk * p.k.stride_h;
-                voff = (int64_t)blk * p.v.stride_b + (int64_t)rin * p.v.stride_s + (int64_t)hk * p.v.stride_h;
-            } else {
-                koff = (int64_t)kb * p.k.stride_b + (int64_t)pos * p.k.stride_s + (int64_t)hk * p.k.stride_h;
-                voff = (int64_t)kb * p.v.stride_b + (int64_t)pos * p.v.stride_s + (int64_t)hk * p.v.stride_h;
-            }
-            const T* ksrc = reinterpret_cast<const T*>(p.k_new.ptr) + (int64_t)b * p.k_new.stride_b + (int64_t)i * p.k_new.stride_s + (int64_t)hk * p.k_new.stride_h;
-            const T* vsrc = reinterpret_cast<const T*>(p.v_new.ptr) + (int64_t)b * p.v_new.stride_b + (int64_t)i * p.v_new.stride_s + (int64_t)hk * p.v_new.stride_h;
-            T* kdst = reinterpret_cast<T*>(p.k.ptr) + koff;
-            T* vdst = reinterpret_cast<T*>(p.v.ptr) + voff;
-            const int cpos = max(0, min(pos, p.seqlen_ro - 1));
-            const T* cr = reinterpret_cast<const T*>(p.rotary_cos) + (int64_t)cpos * (rd / 2);
-            const T* sr = reinterpret_cast<const T*>(p.rotary_sin) + (int64_t)cpos * (rd / 2);
-            for (int e = lane; e < p.d; e += 32) kdst[e] = rd ? rotate_elem<T>(ksrc, e, rd, p.rotary_interleaved, cr, sr) : ksrc[e];
-            for (int e = lane; e < p.dv; e += 32) vdst[e] = vsrc[e];
-        }
-        fence_proxy_async_all();
-        __syncwarp();
-    }
     int lo_any, hi_any, tmp;
     window_bounds(0, sq, sk, wl, wr, lo_any, tmp);
     window_bounds(sq - 1, sq, sk, wl, wr, tmp, hi_any);
@@ -393,6 +356,22 @@ __global__ void __launch_bounds__(WIDE ? 160 : 128) decode_tma_kernel(const __gr
             khi[r] = min(min(khi[r], re - 1), rb + (split + 1) * tps - 1);
         }
         slope[r] = p.alibi_slopes ? p.alibi_slopes[(int64_t)b * p.alibi_stride_b + head[r]] * kLog2e : 0.f;
+    }
+    const T* qbase = reinterpret_cast<const T*>(p.q.ptr) + (p.cu_seqlens_q ? 0 : (int64_t)b * p.q.stride_b);
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int col = kk * 16 + hf * 8 + 2 * t;
+                uint32_t v = 0;
+                if (vrow[r] < rows_total)
+                    v = *reinterpret_cast<const uint32_t*>(qbase + (int64_t)(q_off + qpos[r]) * p.q.stride_s + (int64_t)head[r] * p.q.stride_h + col);
+                qf[kk][hf * 2 + r] = v;
+            }
+        }
     }
     const int32_t* btab = p.block_table ? p.block_table + (int64_t)b * p.block_table_stride : nullptr;
     if constexpr (WIDE) {
@@ -460,35 +439,6 @@ __global__ void __launch_bounds__(WIDE ? 160 : 128) decode_tma_kernel(const __gr
 #pragma unroll
             for (int s = 0; s < STAGES - 1; ++s)
                 if (s < ntiles) issue_tile(t_begin + s * TILE, s);
-        }
-    }
-    // the query fragments are fetched (and rotated) while the first cache tiles are already on their way
-    const T* qbase = reinterpret_cast<const T*>(p.q.ptr) + (p.cu_seqlens_q ? 0 : (int64_t)b * p.q.stride_b);
-    uint32_t qf[HD / 16][4];
-#pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-#pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                const int col = kk * 16 + hf * 8 + 2 * t;
-                uint32_t v = 0;
-                if (vrow[r] < rows_total) {
-                    const T* qrow = qbase + (int64_t)(q_off + qpos[r]) * p.q.stride_s + (int64_t)head[r] * p.q.stride_h;
-                    if (rot_q) {
-                        // rotary embedding applied while the fragment is loaded (same arithmetic as the append kernel)
-                        const int pos = max(0, min(len_raw + (a.rotate_by_pos ? qpos[r] : 0), p.seqlen_ro - 1));
-                        const T* cr = reinterpret_cast<const T*>(p.rotary_cos) + (int64_t)pos * (p.rotary_dim / 2);
-                        const T* sr = reinterpret_cast<const T*>(p.rotary_sin) + (int64_t)pos * (p.rotary_dim / 2);
-                        T two[2] = {rotate_elem<T>(qrow, col, p.rotary_dim, p.rotary_interleaved, cr, sr),
-                                    rotate_elem<T>(qrow, col + 1, p.rotary_dim, p.rotary_interleaved, cr, sr)};
-                        v = *reinterpret_cast<const uint32_t*>(two);
-                    } else {
-                        v = *reinterpret_cast<const uint32_t*>(qrow + col);
-                    }
-                }
-                qf[kk][hf * 2 + r] = v;
-            }
         }
     }
     const float scale_log2 = p.scale * kLog2e;
@@ -689,12 +639,6 @@ bool fwd_decode_supported(const fa_fwd_params& p) {
     return p.sq * G <= 64 && g_decode_use_tma && decode_tma_ok(p);
 }
 
-bool fwd_decode_fuses_append(const fa_fwd_params& p) {
-    // the TMA kernel, a call over whole sequences (a key range restricted to one GPU's share keeps the separate launch:
-    // the rank that holds the new position is not known to the kernel), dense q
-    return fwd_decode_supported(p) && g_decode_use_tma && decode_tma_ok(p) && p.kv_begin <= 0 && p.kv_end <= 0 && !p.cu_seqlens_q;
-}
-
 int launch_fwd_decode(const fa_fwd_params& p, const FwdPlan& plan, float* o_part, float* lse_part) {
     DecodeArgs a;
     a.p = p;
@@ -704,8 +648,6 @@ int launch_fwd_decode(const fa_fwd_params& p, const FwdPlan& plan, float* o_part
     a.lse_part = lse_part;
     // the blob plans whole sequences; a call restricted to a key range keeps the host's uniform plan
     a.meta = (p.kv_begin <= 0 && p.kv_end <= 0) ? reinterpret_cast<const int32_t*>(p.sched_meta) : nullptr;
-    a.fuse_append = plan.fuse_append;
-    a.rotate_by_pos = plan.rotate_by_pos;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
     const int dmax = p.d > p.dv ? p.d : p.dv;
     if (g_decode_use_tma && decode_tma_ok(p)) {

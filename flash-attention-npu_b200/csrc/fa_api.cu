@@ -144,14 +144,9 @@ static int run_forward(const fa_fwd_params& pin, bool allow_fast) {
     float* o_part = plan.nsplit > 1 ? reinterpret_cast<float*>(ws + plan.q_rot_bytes) : nullptr;
     float* lse_part = plan.nsplit > 1 ? reinterpret_cast<float*>(ws + plan.q_rot_bytes + plan.o_part_bytes) : nullptr;
 
-    const bool takes_sm100 = allow_fast && g_policy == 0 && plan.nsplit == 1 && !p.partials_only && fwd_sm100_supported(p);
-    const int by_pos = (p.causal || p.window_left >= 0 || p.window_right >= 0) ? 1 : 0;
-    // The split-KV decode kernel appends the new rows and rotates q itself (one launch fewer a step); every other
-    // kernel gets the in-place append (and rotary) as a launch of its own first and then sees the updated cache.
-    if ((p.s_new > 0 || plan.rotate_q) && !takes_sm100 && g_policy == 0 && plan.use_decode && fwd_decode_fuses_append(p)) {
-        plan.fuse_append = 1;
-        plan.rotate_by_pos = by_pos;
-    } else if (p.s_new > 0 || plan.rotate_q) {
+    // in-place append (and rotary) first; the attention kernels then see the updated cache
+    if (p.s_new > 0 || plan.rotate_q) {
+        const int by_pos = (p.causal || p.window_left >= 0 || p.window_right >= 0) ? 1 : 0;
         if (int e = launch_append_rotary(p, q_rot, by_pos)) return e;
         if (plan.rotate_q) {
             p.q.ptr = q_rot;
@@ -160,7 +155,8 @@ static int run_forward(const fa_fwd_params& pin, bool allow_fast) {
             p.q.stride_b = (int64_t)p.sq * p.hq * p.d;
         }
     }
-    if (takes_sm100) return launch_fwd_sm100(p);
+    if (allow_fast && g_policy == 0 && plan.nsplit == 1 && !p.partials_only && fwd_sm100_supported(p))
+        return launch_fwd_sm100(p);
 
     if (p.partials_only && plan.nsplit == 1) { o_part = p.o_partial; lse_part = p.lse_partial; }
     int e = (g_policy == 0 && plan.use_decode) ? launch_fwd_decode(p, plan, o_part, lse_part)

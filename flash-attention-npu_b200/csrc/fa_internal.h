@@ -23,8 +23,6 @@ struct FwdPlan {
     size_t q_rot_bytes, o_part_bytes, lse_part_bytes;
     int use_sm100;       // tcgen05 kernel eligible
     int use_decode;      // warp-per-split decode kernel eligible
-    int fuse_append;     // the decode kernel itself appends the new k/v rows and rotates q (no separate launch)
-    int rotate_by_pos;   // query i sits at position length + i (causal / windowed calls), else at length
 };
 
 // scheduler-metadata blob (sched_meta.cu): header, then kSchedSeqInts entries per sequence
@@ -42,8 +40,6 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan);
 int launch_fwd_generic(const fa_fwd_params& p, const FwdPlan& plan, float* o_part, float* lse_part);
 int launch_fwd_decode(const fa_fwd_params& p, const FwdPlan& plan, float* o_part, float* lse_part);
 bool fwd_decode_supported(const fa_fwd_params& p);
-// the decode kernel that will serve this call can append the new rows and rotate q itself
-bool fwd_decode_fuses_append(const fa_fwd_params& p);
 void decode_set_use_tma(int v);
 int decode_error_flag(bool clear);
 int launch_fwd_sm100(const fa_fwd_params& p);

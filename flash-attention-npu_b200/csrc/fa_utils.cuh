@@ -37,23 +37,6 @@ template <> struct Elem<__nv_bfloat16> {
     static constexpr int kDtype = FA_BF16;
 };
 
-// One element of a row after rotary embedding (flash_attn_npu_interface.py:1469-1474 gives the positions): fp32
-// arithmetic with separately rounded products and one round-to-nearest-even, so the result is bit-identical to the
-// CPU restatement.  `cosr` / `sinr` are the table rows of the element's position (rotary_dim / 2 entries).
-template <typename T>
-__device__ __forceinline__ T rotate_elem(const T* x, int e, int rd, int interleaved, const T* cosr, const T* sinr) {
-    if (e >= rd) return x[e];
-    int j, partner;
-    bool first;
-    if (interleaved) { j = e >> 1; first = (e & 1) == 0; partner = first ? e + 1 : e - 1; }
-    else { first = e < rd / 2; j = first ? e : e - rd / 2; partner = first ? e + rd / 2 : e - rd / 2; }
-    const float c = Elem<T>::to_float(cosr[j]), s = Elem<T>::to_float(sinr[j]);
-    const float xe = Elem<T>::to_float(x[e]), xp = Elem<T>::to_float(x[partner]);
-    const float r = first ? __fsub_rn(__fmul_rn(xe, c), __fmul_rn(xp, s))
-                          : __fadd_rn(__fmul_rn(xp, s), __fmul_rn(xe, c));
-    return Elem<T>::from_float(r);
-}
-
 // ---- async copies ----------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

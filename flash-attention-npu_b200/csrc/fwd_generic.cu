@@ -348,6 +348,20 @@ int launch_fwd_generic(const fa_fwd_params& p, const FwdPlan& plan, float* o_par
 // is bit-identical to the CPU restatement.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
+__device__ __forceinline__ T rotate_elem(const T* x, int e, int rd, int interleaved, const T* cosr, const T* sinr) {
+    if (e >= rd) return x[e];
+    int j, partner;
+    bool first;
+    if (interleaved) { j = e >> 1; first = (e & 1) == 0; partner = first ? e + 1 : e - 1; }
+    else { first = e < rd / 2; j = first ? e : e - rd / 2; partner = first ? e + rd / 2 : e - rd / 2; }
+    const float c = Elem<T>::to_float(cosr[j]), s = Elem<T>::to_float(sinr[j]);
+    const float xe = Elem<T>::to_float(x[e]), xp = Elem<T>::to_float(x[partner]);
+    const float r = first ? __fsub_rn(__fmul_rn(xe, c), __fmul_rn(xp, s))
+                          : __fadd_rn(__fmul_rn(xp, s), __fmul_rn(xe, c));
+    return Elem<T>::from_float(r);
+}
+
+template <typename T>
 __global__ void append_rotary_kernel(const fa_fwd_params p, T* q_rot, int rotate_q_by_pos) {
     const int b = blockIdx.z;
     const int L = p.seqused_k[b];

@@ -177,6 +177,16 @@ def test_alibi_backward(per_batch, causal, window, cap):
     grads = torch.autograd.grad(out, (qc, kc, vc), do.cuda())
     for name, got, a, b_ in zip(("dq", "dk", "dv"), grads, lp, f32):
         assert_within(name, got.cpu(), a, b_, roundings=3)
+    # the same call straight through the extension module (autograd runs it on a worker thread, the kernel name is
+    # kept per calling thread): the tcgen05 dK/dV kernel applies cap and bias itself, bit-identical results
+    import fa_b200_capi as capi
+    from flash_attn_npu import flash_attn_npu as ext
+    dq, dk, dv = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
+    ext.bwd(do.cuda(), qc.detach(), kc.detach(), vc.detach(), out.detach(), lse, dq, dk, dv, slopes.cuda(), 0.0, scale, causal,
+            window[0], window[1], cap, False, None, None)
+    torch.cuda.synchronize()
+    assert capi.last_kernel() == "sm100_tcgen05_bwd_5gemm"
+    assert all(torch.equal(x, y) for x, y in zip((dq, dk, dv), grads))
     # without the slopes the gradients differ by far more than the tolerance: the bias is really applied
     plain = orc.attention_bwd(q.float(), k.float(), v.float(), do.float(), f_l, scale, causal, window, cap)
     assert (plain[0] - f32[0]).abs().max() > 0.05
