@@ -377,12 +377,13 @@ __global__ void __launch_bounds__(WIDE ? 160 : 128) decode_tma_kernel(const __gr
     if constexpr (WIDE) {
         if (threadIdx.x == 0) {
 #pragma unroll
-            for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (STAGES + s), 4); }
+            for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (STAGES + s), (rows_total + 15) / 16); }
             mbar_fence_init();
             tma_prefetch_desc(&ta.tk);
             tma_prefetch_desc(&ta.tv);
         }
         __syncthreads();
+        if (warp < 4 && row_base >= rows_total) return;      // a warp without rows (17-48 rows): the stages are released by the others
     } else {
         if (lane == 0) {
 #pragma unroll
