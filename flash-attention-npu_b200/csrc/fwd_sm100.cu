@@ -452,6 +452,352 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     }
 }
 
+// =================================================================================================
+// Head dims 192 and 256: one 128-row query tile per CTA.  The output accumulator alone takes up to 256 tensor-memory
+// columns, so instead of a second query tile the CTA keeps TWO score buffers of the same tile (columns 0-127 and
+// 128-255): Q K^T of key tile j + 1 is issued before P V of tile j and runs while tile j is in its softmax.  K and V
+// have one shared-memory buffer each (Q + K + V = 192 KiB at D = 256): K(j + 1) is requested as soon as the scores of
+// tile j are done, V(j + 1) as soon as P V of tile j is done.  One softmax warp group (warps 0-3, thread = row);
+// warp 8 TMA producer, warp 9 MMA issue.  Same arithmetic as the two-tile kernel.
+// =================================================================================================
+template <int D>
+struct FwdSm100SmemWide {
+    static constexpr int kSub = 128 * 128;
+    static constexpr int kTile = (D / 64) * kSub;           // Q, K or V tile
+    static constexpr int oQ = 0, oK = kTile, oV = 2 * kTile;
+    static constexpr int oBar = 3 * kTile;
+    static constexpr int kBytes = oBar + 320;
+};
+enum { W_Q = 0, W_KF, W_KE, W_VF, W_VE, W_S0, W_S1, W_P0, W_P1, W_P0B, W_P1B, W_O, W_COUNT };
+
+template <typename T, int D, bool BIAS>
+__global__ void __launch_bounds__(384, 1) fwd_sm100_kernel_wide(const __grid_constant__ Sm100FwdArgs a) {
+    using L = FwdSm100SmemWide<D>;
+    constexpr int NSUB = D / 64;
+    constexpr uint32_t TMEM_COLS = 512, COL_O = 256;
+    constexpr int FMT = Elem<T>::kDtype == FA_BF16 ? 1 : 0;
+    constexpr uint32_t IDESC_QK = umma_idesc(FMT, 128, 128, 0, 0);
+    constexpr uint32_t IDESC_PV = umma_idesc(FMT, 128, D, 0, 1);
+    constexpr float kRescaleThreshold = 8.f;
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t sbase = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    unsigned char* sgen = smem_raw + (sbase - smem_addr(smem_raw));
+    const uint32_t sQ = sbase + L::oQ, sK = sbase + L::oK, sV = sbase + L::oV;
+    const uint32_t bars = sbase + L::oBar;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sgen + L::oBar + 8 * W_COUNT);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sgen + L::oBar + 8 * W_COUNT + 8);
+    auto bar = [&](int i) { return bars + 8u * i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int mblk = gridDim.x - 1 - blockIdx.x;
+    int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
+    if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
+    if (a.seqused_k) sk = (int)max(0LL, min((long long)a.seqused_k[b] + a.s_new, (long long)a.sk));
+    const int m0 = mblk * 128;
+    if (m0 >= sq) return;
+    if (g_fwd_sm100_error) return;
+    const int hk = h / (a.hq / a.hkv);
+    const int wl = a.wl, wr = a.causal ? 0 : a.wr;
+    const int rows = min(128, sq - m0);
+
+    int lo_first, hi_first, lo_last, hi_last;
+    window_bounds(m0, sq, sk, wl, wr, lo_first, hi_first);
+    window_bounds(m0 + rows - 1, sq, sk, wl, wr, lo_last, hi_last);
+    int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
+    if (sk <= 0 || lo_first >= sk) { t_lo = 0; t_hi = 0; }
+    const int ntiles = max(0, t_hi - t_lo);
+
+    T* obase = reinterpret_cast<T*>(a.o) + (a.cu_q ? 0 : (int64_t)b * a.o_sb) + (int64_t)(q_off + m0) * a.o_ss + (int64_t)h * a.o_sh;
+    float* lbase = a.lse ? a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + (int64_t)(q_off + m0) * a.lse_ss : nullptr;
+
+    if (ntiles == 0) {
+        if (tid < rows) {
+            uint4 z = make_uint4(0, 0, 0, 0);
+            T* orow = obase + (int64_t)tid * a.o_ss;
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
+            if (lbase) lbase[(int64_t)tid * a.lse_ss] = INFINITY;
+        }
+        return;
+    }
+
+    if (tid == 0) {
+        for (int i = 0; i < W_COUNT; ++i) mbar_init(bar(i), (i >= W_P0 && i <= W_P1B) ? 128u : 1u);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    int* err = &g_fwd_sm100_error;
+    const int qrow0 = (a.cu_q ? q_off : 0) + m0;
+    const int qb = a.cu_q ? 0 : b;
+
+    static_assert(128 * 56 + 256 * 224 <= 384 * 168, "register split exceeds the CTA's allocation");
+    if (warp >= 8) {
+    reg_dealloc<56>();
+    if (warp == 8) {
+        if (lane == 0) {
+            tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
+            mbar_expect_tx(bar(W_Q), L::kTile);
+#pragma unroll
+            for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + s * L::kSub, &a.tq, bar(W_Q), s * 64, h, qrow0, qb);
+            const int32_t* btab = a.block_table ? a.block_table + (int64_t)b * a.bt_stride : nullptr;
+            const int kbatch = a.cu_q ? 0 : (a.cache_batch_idx ? a.cache_batch_idx[b] : b);
+            // where key tile j lives: (row, outermost coordinate), second half of the tile when it is copied in two boxes
+            auto place = [&](int j, int& krow, int& kouter, int& krow2, int& kouter2) {
+                krow = (a.cu_q ? k_off : 0) + (t_lo + j) * 128; kouter = kbatch; krow2 = 0; kouter2 = 0;
+                if (btab) {
+                    const int pos = (t_lo + j) * 128;
+                    kouter = btab[pos / a.page_size];
+                    krow = pos % a.page_size;
+                    if (a.kv_box == 64) {
+                        const bool in_table = (pos + 64) / a.page_size < a.bt_stride;
+                        kouter2 = in_table ? btab[(pos + 64) / a.page_size] : kouter;
+                        krow2 = in_table ? (pos + 64) % a.page_size : krow;
+                    }
+                }
+            };
+            auto load = [&](const CUtensorMap* map, uint32_t dst, int full_bar, int j) {
+                int krow, kouter, krow2, kouter2;
+                place(j, krow, kouter, krow2, kouter2);
+                mbar_expect_tx(bar(full_bar), L::kTile);
+#pragma unroll
+                for (int s = 0; s < NSUB; ++s) {
+                    tma_load_4d(dst + s * L::kSub, map, bar(full_bar), s * 64, hk, krow, kouter);
+                    if (a.kv_box == 64) tma_load_4d(dst + s * L::kSub + 64 * 128, map, bar(full_bar), s * 64, hk, krow2, kouter2);
+                }
+            };
+            // order of the requests: K(0) V(0) K(1) | K(2) V(1) | K(3) V(2) ...: K(j) follows the scores of tile j - 1,
+            // V(j - 1) follows P V of tile j - 2
+            bool ok = true;
+            for (int j = 0; j <= ntiles && ok; ++j) {
+                if (j < ntiles) {
+                    if (j > 0) ok = mbar_wait(bar(W_KE), (j - 1) & 1, abort_flag, err, 1);
+                    if (!ok) break;
+                    load(&a.tk, sK, W_KF, j);
+                }
+                const int jv = j == 0 ? 0 : j - 1;           // V(0) right after K(0); afterwards V lags one tile
+                if (j == 0 || j >= 2) {
+                    if (jv >= 1) ok = mbar_wait(bar(W_VE), (jv - 1) & 1, abort_flag, err, 2);
+                    if (!ok) break;
+                    if (jv < ntiles) load(&a.tv, sV, W_VF, jv);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        const uint64_t dQ = umma_desc(sQ, 16, 1024), dK = umma_desc(sK, 16, 1024), dV = umma_desc(sV, L::kSub, 1024);
+        auto issue_qk = [&](int j) {
+            const uint32_t d_s = tmem + (j & 1) * 128;
+            static_for<0, NSUB>([&](auto sub) {
+                constexpr uint32_t o = sub.value * (L::kSub >> 4);
+                umma_ss_group4<o, o + 2, o + 4, o + 6, o, o + 2, o + 4, o + 6>(d_s, dQ, dK, IDESC_QK, sub.value > 0);
+            });
+            umma_commit_w(bar(W_S0 + (j & 1)));
+            umma_commit_w(bar(W_KE));
+        };
+        bool ok = mbar_wait(bar(W_Q), 0, abort_flag, err, 3);
+        if (ok) ok = mbar_wait(bar(W_KF), 0, abort_flag, err, 4);
+        if (ok) { tc_fence_after(); issue_qk(0); }
+        for (int j = 0; j < ntiles && ok; ++j) {
+            if (j + 1 < ntiles) {
+                ok = mbar_wait(bar(W_KF), (j + 1) & 1, abort_flag, err, 7);
+                if (!ok) break;
+                tc_fence_after();
+                issue_qk(j + 1);
+            }
+            ok = mbar_wait(bar(W_VF), j & 1, abort_flag, err, 6);
+            if (!ok) break;
+            if (a.seqused_k && (t_lo + j) * 128 + 128 > sk) {
+                // stale cache rows past the sequence may hold NaN patterns: 0 x NaN is NaN, so the V rows are cleared
+                const int first = max(0, sk - (t_lo + j) * 128);
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub)
+                    for (int idx = first * 8 + lane; idx < 128 * 8; idx += 32)
+                        *reinterpret_cast<uint4*>(sgen + L::oV + sub * L::kSub + idx * 16) = make_uint4(0, 0, 0, 0);
+                fence_proxy_async_smem();
+                __syncwarp();
+            }
+            const int buf = j & 1;
+            ok = mbar_wait(bar(W_P0 + buf), (j >> 1) & 1, abort_flag, err, 5);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_o = tmem + COL_O, a_p = tmem + buf * 128;
+            umma_ts_group4<0, 8, 0, 128>(d_o, a_p, dV, IDESC_PV, j > 0);
+            ok = mbar_wait(bar(W_P0B + buf), (j >> 1) & 1, abort_flag, err, 11);
+            if (!ok) break;
+            tc_fence_after();
+            umma_ts_group4<32, 8, 512, 128>(d_o, a_p, dV, IDESC_PV, 1);
+            umma_commit_w(bar(W_VE));
+            if (j + 1 == ntiles) umma_commit_w(bar(W_O));
+        }
+    }
+    } else {
+    reg_alloc<224>();
+    if (warp < 4) {
+        const int r = tid & 127;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t t_o = tmem + lane_base + COL_O;
+        const int qi = m0 + r;
+        int klo = 1, khi = 0;
+        if (r < rows) window_bounds(qi, sq, sk, wl, wr, klo, khi);
+        int lo_l, hi_f, tmp;
+        window_bounds(m0, sq, sk, wl, wr, tmp, hi_f);
+        window_bounds(m0 + rows - 1, sq, sk, wl, wr, lo_l, tmp);
+        float m_used = -INFINITY, l_run = 0.f;
+        const float sc = BIAS ? 1.f : a.scale_log2;
+        const float cap_out = a.softcap * kLog2e;
+        const float slope = (BIAS && a.alibi) ? a.alibi[(int64_t)b * a.alibi_sb + h] * kLog2e : 0.f;
+        const float rel = (float)(qi + sk - sq);
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int n0 = (t_lo + j) * 128, buf = j & 1;
+            const uint32_t t_s = tmem + lane_base + buf * 128;
+            ok = mbar_wait(bar(W_S0 + buf), (j >> 1) & 1, abort_flag, err, 9);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sreg[4][32];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 2; c < 4; ++c) tmem_ld32(t_s + c * 32, sreg[c]);
+            const bool full = n0 >= lo_l && n0 + 127 <= hi_f;
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                if (hh == 1) tmem_wait_ld();
+                if constexpr (BIAS) {
+#pragma unroll
+                    for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float xv = __uint_as_float(sreg[c][i]);
+                            if (a.softcap > 0.f) {
+                                const float e2y = ex2_approx(xv * (a.cap_in * 2.f * kLog2e));
+                                xv = cap_out * (1.f - __fdividef(2.f, 1.f + e2y));
+                            } else {
+                                xv *= a.scale_log2;
+                            }
+                            xv -= slope * fabsf(rel - (float)(n0 + c * 32 + i));
+                            sreg[c][i] = __float_as_uint(xv);
+                        }
+                    }
+                }
+                if (!full) {
+#pragma unroll
+                    for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int col = n0 + c * 32 + i;
+                            if (col < klo || col > khi) sreg[c][i] = 0xff800000u;     // -inf
+                        }
+                    }
+                }
+#pragma unroll
+                for (int c = 2 * hh; c < 2 * hh + 2; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        mx0 = fmaxf(fmaxf(mx0, __uint_as_float(sreg[c][i])), __uint_as_float(sreg[c][i + 1]));
+                        mx1 = fmaxf(fmaxf(mx1, __uint_as_float(sreg[c][i + 2])), __uint_as_float(sreg[c][i + 3]));
+                        mx2 = fmaxf(fmaxf(mx2, __uint_as_float(sreg[c][i + 4])), __uint_as_float(sreg[c][i + 5]));
+                        mx3 = fmaxf(fmaxf(mx3, __uint_as_float(sreg[c][i + 6])), __uint_as_float(sreg[c][i + 7]));
+                    }
+                }
+            }
+            const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;       // log2 domain
+            if (m_used == -INFINITY) m_used = m_new;
+            if (j > 0 && __any_sync(0xffffffffu, m_new > m_used + kRescaleThreshold)) {
+                // P V of tile j - 1 was issued AFTER the scores of this tile: wait for it before touching O
+                ok = mbar_wait(bar(W_VE), (j - 1) & 1, abort_flag, err, 12);
+                if (!ok) break;
+                tc_fence_after();
+                const float m_next = fmaxf(m_used, m_new);
+                const float alpha = m_used == -INFINITY ? 1.f : ex2_approx(m_used - m_next);
+                m_used = m_next;
+                l_run *= alpha;
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t oreg[32];
+                    tmem_ld32(t_o + c * 32, oreg);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                    tmem_st32(t_o + c * 32, oreg);
+                }
+            }
+            const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+            const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(neg_m, neg_m);
+            float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+            auto exp_phase = [&](auto npoly_c) {
+                constexpr int NPOLY = decltype(npoly_c)::value;
+#pragma unroll
+                for (int hlf = 0; hlf < 2; ++hlf) {
+                    uint32_t preg[32];
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const uint32_t* src = &sreg[2 * hlf + (g >> 1)][(g & 1) * 16];
+                        static_for<0, 8>([&](auto pi) {
+                            constexpr bool poly = (pi.value * NPOLY) % 8 < NPOLY;
+                            const float2 xv = fma2(make_float2(__uint_as_float(src[2 * pi.value]), __uint_as_float(src[2 * pi.value + 1])), sc2, nm2);
+                            float2 pv;
+                            if constexpr (poly) pv = ex2_poly2(xv);
+                            else pv = make_float2(ex2_approx(xv.x), ex2_approx(xv.y));
+                            if constexpr (pi.value & 1) sum_b = add2(sum_b, pv); else sum_a = add2(sum_a, pv);
+                            preg[g * 8 + pi.value] = Elem<T>::pack(pv.x, pv.y);
+                        });
+                    }
+                    tmem_st32(t_s + hlf * 32, preg);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(bar((hlf ? W_P0B : W_P0) + buf));
+                }
+            };
+            if (full) exp_phase(std::integral_constant<int, FA_FWD_POLY>{});
+            else exp_phase(std::integral_constant<int, 0>{});
+            l_run += (sum_a.x + sum_b.x) + (sum_a.y + sum_b.y);
+        }
+        if (ok) ok = mbar_wait(bar(W_O), 0, abort_flag, err, 10);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            T* orow = obase + (int64_t)r * a.o_ss;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t oreg[32];
+                tmem_ld32(t_o + c * 32, oreg);
+                tmem_wait_ld();
+                if (r < rows) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 pk;
+                        pk.x = Elem<T>::pack(__uint_as_float(oreg[8 * v + 0]) * inv, __uint_as_float(oreg[8 * v + 1]) * inv);
+                        pk.y = Elem<T>::pack(__uint_as_float(oreg[8 * v + 2]) * inv, __uint_as_float(oreg[8 * v + 3]) * inv);
+                        pk.z = Elem<T>::pack(__uint_as_float(oreg[8 * v + 4]) * inv, __uint_as_float(oreg[8 * v + 5]) * inv);
+                        pk.w = Elem<T>::pack(__uint_as_float(oreg[8 * v + 6]) * inv, __uint_as_float(oreg[8 * v + 7]) * inv);
+                        reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
+                    }
+                }
+            }
+            if (r < rows && lbase) lbase[(int64_t)r * a.lse_ss] = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : INFINITY;
+        }
+    }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -501,7 +847,7 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
 }
 
 bool fwd_sm100_supported(const fa_fwd_params& p) {
-    if (p.d != p.dv || (p.d != 64 && p.d != 128)) return false;
+    if (p.d != p.dv || (p.d != 64 && p.d != 128 && p.d != 192 && p.d != 256)) return false;
     const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
     if (cache) {
         // KV-cache calls (prefill against a cache): lengths and pages are read on the device
@@ -535,6 +881,21 @@ static int launch_sm100_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
 template <typename T, int D>
 static int launch_sm100_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
     return (p.softcap > 0.f || p.alibi_slopes) ? launch_sm100_b<T, D, true>(p, a) : launch_sm100_b<T, D, false>(p, a);
+}
+template <typename T, int D, bool BIAS>
+static int launch_sm100_wide_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
+    auto kern = fwd_sm100_kernel_wide<T, D, BIAS>;
+    const int smem = FwdSm100SmemWide<D>::kBytes + 1024;
+    if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
+    dim3 grid((p.sq + 127) / 128, p.hq, p.b);
+    kern<<<grid, 384, smem, st>>>(a);
+    mark_kernel(st);
+    return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
+}
+template <typename T, int D>
+static int launch_sm100_wide_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
+    return (p.softcap > 0.f || p.alibi_slopes) ? launch_sm100_wide_b<T, D, true>(p, a) : launch_sm100_wide_b<T, D, false>(p, a);
 }
 
 int launch_fwd_sm100(const fa_fwd_params& p) {
@@ -570,6 +931,11 @@ int launch_fwd_sm100(const fa_fwd_params& p) {
     a.softcap = p.softcap; a.cap_in = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
     a.alibi = p.alibi_slopes; a.alibi_sb = p.alibi_stride_b;
     a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
+    if (p.d > 128) {
+        note_kernel("sm100_tcgen05_wide");
+        if (p.dtype == FA_F16) return p.d == 192 ? launch_sm100_wide_t<__half, 192>(p, a) : launch_sm100_wide_t<__half, 256>(p, a);
+        return p.d == 192 ? launch_sm100_wide_t<__nv_bfloat16, 192>(p, a) : launch_sm100_wide_t<__nv_bfloat16, 256>(p, a);
+    }
     note_kernel("sm100_tcgen05_2q");
     if (p.dtype == FA_F16) return p.d == 64 ? launch_sm100_t<__half, 64>(p, a) : launch_sm100_t<__half, 128>(p, a);
     return p.d == 64 ? launch_sm100_t<__nv_bfloat16, 64>(p, a) : launch_sm100_t<__nv_bfloat16, 128>(p, a);

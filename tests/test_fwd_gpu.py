@@ -177,6 +177,41 @@ def test_softcap_and_alibi_on_the_tcgen05_forward(d, cap, use_alibi, dt):
         assert_lse(lse, f_l)
 
 
+@pytest.mark.parametrize("d", [192, 256])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_head_dims_192_and_256_on_the_tcgen05_forward(d, dt):
+    """The reference's kernels bucket head dims up to 256 (fag_kernel.cpp:915-984, test lists with d = 256).  Here a
+    one-tile kernel with two score buffers serves 192 and 256: dense causal with ragged tails and Sq != Sk, a sliding
+    window, GQA, softcap + alibi, a packed call with an empty sequence, long enough for both score buffers and the
+    single K / V buffers to be reused many times."""
+    import flash_attn_npu as m
+    import fa_b200_capi as capi
+    torch.manual_seed(23 + d)
+    b, sq, sk, h, hkv = 2, 700, 1100, 4, 2
+    q, k, v = torch.randn(b, sq, h, d).to(dt), torch.randn(b, sk, hkv, d).to(dt), torch.randn(b, sk, hkv, d).to(dt)
+    slopes = torch.rand(b, h) * 0.1
+    for causal, win, cap, al in ((True, (-1, -1), 0.0, None), (False, (300, 100), 0.0, None), (True, (-1, -1), 3.0, slopes),
+                                 (False, (-1, -1), 0.0, None)):
+        (lp_o, _), (f_o, f_l) = fwd_refs(q, k, v, d ** -0.5, causal, win, cap, alibi=al)
+        out, lse = run_dense(2, q, k, v, d ** -0.5, causal, win, cap, alibi=al)
+        assert capi.last_kernel() == "sm100_tcgen05_wide"
+        assert capi.lib.fa_debug_get(2) == 0
+        assert_within("out", out, lp_o, f_o)
+        assert_lse(lse, f_l)
+    lq, lk = [300, 0, 129, 1], [300, 50, 640, 77]
+    qp, kp, vp = torch.randn(sum(lq), h, d).to(dt), torch.randn(sum(lk), hkv, d).to(dt), torch.randn(sum(lk), hkv, d).to(dt)
+    cu_q = torch.tensor([0] + list(torch.tensor(lq).cumsum(0)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(torch.tensor(lk).cumsum(0)), dtype=torch.int32)
+    lp_o, _ = orc.attention_varlen_fwd(qp, kp, vp, cu_q, cu_k, d ** -0.5, True, (-1, -1), 0.0)
+    f_o, f_l = orc.attention_varlen_fwd(qp.float(), kp.float(), vp.float(), cu_q, cu_k, d ** -0.5, True, (-1, -1), 0.0,
+                                        data_type=torch.float32)
+    out, lse, _ = m.flash_attn_varlen_func(qp.cuda(), kp.cuda(), vp.cuda(), cu_q.cuda(), cu_k.cuda(), max(lq), max(lk),
+                                           softmax_scale=d ** -0.5, causal=True, return_attn_probs=True)
+    assert capi.last_kernel() == "sm100_tcgen05_wide"
+    assert_within("varlen out", out, lp_o, f_o)
+    assert_lse(lse, f_l)
+
+
 def test_strided_inputs_and_packed_variants():
     import flash_attn_npu as m
     torch.manual_seed(6)

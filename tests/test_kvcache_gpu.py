@@ -448,6 +448,43 @@ def test_prefill_against_cache_uses_tcgen05(paged, page, append):
     assert_lse(lse, f_l)
 
 
+@pytest.mark.parametrize("page", [64, 256])
+def test_prefill_against_cache_with_head_dim_256(page):
+    """Chunked prefill at head dim 256 (the one-tile tcgen05 kernel): paged cache, in-place append of the chunk, GQA,
+    ragged lengths, NaN past the appended length."""
+    import flash_attn_npu as m
+    import fa_b200_capi as capi
+    g = torch.Generator().manual_seed(99)
+    dt, b, h, hkv, sq, d = torch.bfloat16, 2, 4, 2, 150, 256
+    lens, cap = [500, 1111], 2048
+    q = torch.randn(b, sq, h, d, generator=g).to(dt)
+    kn, vn = torch.randn(b, sq, hkv, d, generator=g).to(dt), torch.randn(b, sq, hkv, d, generator=g).to(dt)
+    nb = cap // page
+    kc = torch.randn(nb * b + 2, page, hkv, d, generator=g).to(dt)
+    vc = torch.randn(nb * b + 2, page, hkv, d, generator=g).to(dt)
+    table = torch.randperm(nb * b + 2, generator=g)[: nb * b].int().reshape(b, nb)
+    for i, L in enumerate(lens):
+        for j in range(nb):
+            lo = max(0, L + sq - j * page)
+            if lo < page:
+                kc[table[i, j], lo:] = float("nan")
+                vc[table[i, j], lo:] = float("nan")
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    scale = d ** -0.5
+    rk, rv = torch.nan_to_num(kc.clone()), torch.nan_to_num(vc.clone())
+    lp_o, _ = orc.kvcache_fwd(q, rk.clone(), rv.clone(), lens_t, scale, k_new=kn, v_new=vn, block_table=table, causal=True)
+    f_o, f_l = orc.kvcache_fwd(q.float(), rk.float(), rv.float(), lens_t, scale, k_new=kn.float(), v_new=vn.float(),
+                               block_table=table, causal=True)
+    out, lse = m.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), kn.cuda(), vn.cuda(), cache_seqlens=lens_t.cuda(),
+                                         block_table=table.cuda(), softmax_scale=scale, causal=True, return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert capi.last_kernel() == "sm100_tcgen05_wide"
+    assert capi.lib.fa_debug_get(2) == 0
+    assert torch.isfinite(out).all()
+    assert_within("out", out.cpu(), lp_o, f_o)
+    assert_lse(lse, f_l)
+
+
 @pytest.mark.parametrize("paged", [True, False])
 def test_oversized_cache_seqlens_are_truncated_and_append_nothing(paged):
     """A stale or oversized cache_seqlens entry (the host never sees the device-resident lengths) must not make any
