@@ -92,7 +92,7 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
         long n = by_occ > by_bal ? by_occ : by_bal;
         if (n > cap) n = cap;
         nsplit = (int)(n < 1 ? 1 : n);
-    } else if (p.num_splits == 0 && cache_like && nblocks > 1 && p.sq <= 64) {
+    } else if (p.num_splits == 0 && cache_like && nblocks > 1 && p.sq <= 64 && !(g_policy == 0 && fwd_sm100_supported(p))) {
         const long base = (long)mblocks * (plan.pack_gqa ? p.hkv : p.hq) * (p.b > 0 ? p.b : 1);
         const long target = 4L * sm_count();
         long by_occ = base >= target ? 1 : (target + base - 1) / base;

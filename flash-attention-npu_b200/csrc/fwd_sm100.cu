@@ -853,7 +853,15 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
         // KV-cache calls (prefill against a cache): lengths and pages are read on the device
         if (p.cu_seqlens_q || p.cu_seqlens_k || !p.seqused_k) return false;
         if (p.block_table && (p.page_size <= 0 || p.page_size % 64)) return false;
-        if (p.sq < 64) return false;                      // short queries belong to the split-KV decode kernels
+        // Short queries belong to the split-KV decode kernels (up to 64 stacked rows a KV head).  A short chunk with
+        // more stacked rows than that (speculative decoding, small prefill chunks under large query groups) runs
+        // here without split-KV when the (batch x head) CTAs alone fill half of the GPU; otherwise the general
+        // kernel with its splits is the better use of the SMs.
+        if (p.sq < 64) {
+            const int G = p.hq / p.hkv;
+            if (p.sq * G <= 64 || p.sq < 8) return false;
+            if ((long)p.b * p.hq < sm_count() / 2) return false;
+        }
     }
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
     if (p.kv_begin != 0 || p.kv_end > 0 || p.partials_only) return false;

@@ -448,6 +448,39 @@ def test_prefill_against_cache_uses_tcgen05(paged, page, append):
     assert_lse(lse, f_l)
 
 
+def test_short_chunk_with_many_stacked_rows_runs_on_tcgen05():
+    """32 new tokens a sequence under a query group of 8 are 256 stacked rows a KV head: too many for the split-KV
+    decode kernel, fewer than 64 rows a head; with 128 (batch x head) CTAs the tcgen05 forward takes the call (rows past
+    the chunk are zero-filled by the tile copy), otherwise the general kernel would.  Append + causal, ragged lengths."""
+    import flash_attn_npu as m
+    import fa_b200_capi as capi
+    g = torch.Generator().manual_seed(7)
+    dt, b, h, hkv, sq, d, page = torch.bfloat16, 4, 32, 4, 32, 128, 128
+    lens = [900, 17, 2000, 1024]
+    q = torch.randn(b, sq, h, d, generator=g).to(dt)
+    kn, vn = torch.randn(b, sq, hkv, d, generator=g).to(dt), torch.randn(b, sq, hkv, d, generator=g).to(dt)
+    kc, vc, table = paged_setup(g, b, [2200] * b, hkv, d, page, dt)
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    scale = d ** -0.5
+    lp_o, _ = orc.kvcache_fwd(q, kc.clone(), vc.clone(), lens_t, scale, k_new=kn, v_new=vn, block_table=table, causal=True)
+    f_o, f_l = orc.kvcache_fwd(q.float(), kc.float(), vc.float(), lens_t, scale, k_new=kn.float(), v_new=vn.float(),
+                               block_table=table, causal=True)
+    kg, vg = kc.cuda(), vc.cuda()
+    out, lse = m.flash_attn_with_kvcache(q.cuda(), kg, vg, kn.cuda(), vn.cuda(), cache_seqlens=lens_t.cuda(),
+                                         block_table=table.cuda(), softmax_scale=scale, causal=True, return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert capi.last_kernel() == "sm100_tcgen05_2q"
+    assert capi.lib.fa_debug_get(2) == 0
+    assert_within("out", out.cpu(), lp_o, f_o)
+    assert_lse(lse, f_l)
+    # a single sequence with few heads does not fill the GPU: the general kernel with split-KV keeps such calls
+    # (the cache now holds the appended chunk)
+    out1 = m.flash_attn_with_kvcache(q[:1].cuda(), kg, vg, cache_seqlens=lens_t[:1].cuda() + sq,
+                                     block_table=table[:1].cuda(), softmax_scale=scale, causal=True)
+    assert capi.last_kernel() == "generic_mma"
+    assert_within("single sequence", out1.cpu(), lp_o[:1], f_o[:1])
+
+
 @pytest.mark.parametrize("page", [64, 256])
 def test_prefill_against_cache_with_head_dim_256(page):
     """Chunked prefill at head dim 256 (the one-tile tcgen05 kernel): paged cache, in-place append of the chunk, GQA,
