@@ -788,7 +788,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--e2e-kv-heads", type=int, default=0,
                     help="KV heads per chunk of the end-to-end leg's host pipeline (0 = a whole batch entry, contiguous copies)")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "decode", "mla"],
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "decode", "mla", "fwd256", "decode4"],
                     help="run two calls of one kernel on a small case (for a profiler capture) and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -945,8 +945,8 @@ def profile_case(name):
     from flash_attn_npu import flash_attn_npu as ext
     dev = torch.device("cuda", 0)
     g = torch.Generator().manual_seed(11)
-    if name in ("fwd", "bwd"):
-        b, s, h, d = 2, 4096, 32, 128
+    if name in ("fwd", "bwd", "fwd256"):
+        b, s, h, d = (2, 4096, 32, 128) if name != "fwd256" else (2, 4096, 16, 256)
         q, k, v, do = (torch.randn(b, s, h, d, device=dev).bfloat16() for _ in range(4))
         for _ in range(2):
             out, lse, _, _ = ext.fwd(q, k, v, None, None, 0.0, d ** -0.5, True, -1, -1, 0.0, False, None)
@@ -955,15 +955,16 @@ def profile_case(name):
     else:
         page = 256
         b = 16
-        lo, hi = (1024, 32769) if name == "decode" else (4096, 65537)
+        lo, hi = (1024, 32769) if name in ("decode", "decode4") else (4096, 65537)
         lens = torch.randint(lo, hi, (b,), generator=g, dtype=torch.int32)
         table, pool, _ = _paged_tables((lens + 1).tolist(), page, g)
         lens_d, table_d = lens.to(dev), table.to(dev)
-        if name == "decode":
-            hq, hkv, d = 32, 8, 128
+        if name in ("decode", "decode4"):
+            hq, hkv, d = (32, 8, 128) if name == "decode" else (64, 8, 128)
+            sq = 1 if name == "decode" else 4              # decode4: 4 new tokens x group of 8 = 32 stacked rows a KV head
             kc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
             vc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
-            q = torch.randn(b, 1, hq, d, device=dev, dtype=torch.bfloat16)
+            q = torch.randn(b, sq, hq, d, device=dev, dtype=torch.bfloat16)
             print("cached tokens", int(lens.sum()), "algorithmic bytes", int(lens.sum()) * hkv * d * 4)
             for _ in range(2):
                 fa.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=lens_d, block_table=table_d, causal=True)
