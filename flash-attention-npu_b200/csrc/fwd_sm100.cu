@@ -37,6 +37,7 @@ struct alignas(64) Sm100FwdArgs {
     const float* alibi;
     int64_t alibi_sb;
     int kv_box;                          // rows of one K/V copy: 128, or 64 when pages are an odd multiple of 64 tokens
+    int gq;                              // two-tile kernel: 1, or the query group size when a KV head's heads are stacked into the tile rows
 };
 
 // =================================================================================================
@@ -89,24 +90,31 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
+    const int b = blockIdx.z;
+    // Tile rows.  gq = 1: 128 consecutive query positions of head blockIdx.y.  gq = G (short queries under a query
+    // group of G, a power of two up to 128): the G heads of KV head blockIdx.y are stacked, row t of a tile is query
+    // position t / G of head t % G — the tile copy delivers exactly that order from a (dims, G heads, 128 / G rows)
+    // box — so that a short chunk fills the 128-row tiles instead of one tile per head with few rows in it.
+    const int gq = a.gq;
+    const int qpt = 128 / gq;                                // query positions of one 128-row tile
+    const int hk = gq > 1 ? (int)blockIdx.y : (int)blockIdx.y / (a.hq / a.hkv);
+    const int h0 = gq > 1 ? hk * gq : (int)blockIdx.y;       // head of tile row 0
     const int mblk = gridDim.x - 1 - blockIdx.x;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
     if (a.seqused_k) {                                       // cache call: the length lives on the device
         sk = (int)max(0LL, min((long long)a.seqused_k[b] + a.s_new, (long long)a.sk));   // an oversized entry is truncated to the capacity
     }
-    const int m0 = mblk * 256;
+    const int m0 = mblk * 2 * qpt;                           // first query position of the CTA
     if (m0 >= sq) return;
     if (g_fwd_sm100_error) return;
-    const int hk = h / (a.hq / a.hkv);
     const int wl = a.wl, wr = a.causal ? 0 : a.wr;
-    const int rows_cta = min(256, sq - m0);
+    const int rows_cta = min(256, (sq - m0) * gq);           // tile rows in use
     const bool has_b = rows_cta > 128;
 
     int lo_first, hi_first, lo_last, hi_last;
     window_bounds(m0, sq, sk, wl, wr, lo_first, hi_first);
-    window_bounds(m0 + rows_cta - 1, sq, sk, wl, wr, lo_last, hi_last);
+    window_bounds(m0 + (rows_cta - 1) / gq, sq, sk, wl, wr, lo_last, hi_last);
     int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
     if (sk <= 0 || lo_first >= sk) { t_lo = 0; t_hi = 0; }
     const int ntiles = max(0, t_hi - t_lo);
@@ -115,21 +123,26 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     int nt0 = ntiles;
     if (has_b) {
         int lo_a, hi_a;
-        window_bounds(m0 + 127, sq, sk, wl, wr, lo_a, hi_a);
+        window_bounds(m0 + qpt - 1, sq, sk, wl, wr, lo_a, hi_a);
         const int n = min(ntiles, (hi_a < 0 ? 0 : hi_a / 128 + 1) - t_lo);
         if (n >= 1) nt0 = n;
     }
 
-    T* obase = reinterpret_cast<T*>(a.o) + (a.cu_q ? 0 : (int64_t)b * a.o_sb) + (int64_t)(q_off + m0) * a.o_ss + (int64_t)h * a.o_sh;
-    float* lbase = a.lse ? a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)h * a.lse_sh + (int64_t)(q_off + m0) * a.lse_ss : nullptr;
+    // output row and LSE slot of tile row t (0..255) of this CTA
+    auto out_row = [&](int t) -> T* {
+        return reinterpret_cast<T*>(a.o) + (a.cu_q ? 0 : (int64_t)b * a.o_sb) + (int64_t)(q_off + m0 + t / gq) * a.o_ss + (int64_t)(h0 + t % gq) * a.o_sh;
+    };
+    auto lse_slot = [&](int t) -> float* {
+        return a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)(h0 + t % gq) * a.lse_sh + (int64_t)(q_off + m0 + t / gq) * a.lse_ss;
+    };
 
     if (ntiles == 0) {
         if (tid < rows_cta) {
             uint4 z = make_uint4(0, 0, 0, 0);
-            T* orow = obase + (int64_t)tid * a.o_ss;
+            T* orow = out_row(tid);
 #pragma unroll
             for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
-            if (lbase) lbase[(int64_t)tid * a.lse_ss] = INFINITY;
+            if (a.lse) *lse_slot(tid) = INFINITY;
         }
         return;
     }
@@ -163,10 +176,10 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
             tma_prefetch_desc(&a.tq); tma_prefetch_desc(&a.tk); tma_prefetch_desc(&a.tv);
             mbar_expect_tx(bar(C_Q), has_b ? 2 * L::kQ : L::kQ);
 #pragma unroll
-            for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, h, qrow0, qb);
+            for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, h0, qrow0, qb);
             if (has_b) {
 #pragma unroll
-                for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + L::kQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, h, qrow0 + 128, qb);
+                for (int s = 0; s < NSUB; ++s) tma_load_4d(sQ + L::kQ + s * L::kSub, &a.tq, bar(C_Q), s * 64, h0, qrow0 + qpt, qb);
             }
             // where key tile j lives: (row, outermost coordinate) of the K / V maps.  Dense and packed operands: row
             // in the batch entry; cache: row in the cache entry of this batch; paged cache: row inside the page
@@ -295,18 +308,18 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
         const uint32_t t_s = tmem + lane_base + x * 128;
         const uint32_t t_o = tmem + lane_base + 256 + x * 128;
         const int rows = min(128, rows_cta - x * 128);
-        const int qi = m0 + x * 128 + r;
+        const int qi = m0 + (x * 128 + r) / gq;                  // query position of this thread's row
         int klo = 1, khi = 0;
         if (r < rows) window_bounds(qi, sq, sk, wl, wr, klo, khi);
         int lo_l, hi_f, tmp;
-        window_bounds(m0 + x * 128, sq, sk, wl, wr, tmp, hi_f);
-        window_bounds(m0 + x * 128 + rows - 1, sq, sk, wl, wr, lo_l, tmp);
+        window_bounds(m0 + x * qpt, sq, sk, wl, wr, tmp, hi_f);
+        window_bounds(m0 + (x * 128 + rows - 1) / gq, sq, sk, wl, wr, lo_l, tmp);
         float m_used = -INFINITY, l_run = 0.f;
         // BIAS instantiation: the scores are turned into their final log2-domain values in registers (softcap, then
         // alibi, as the general kernel and the golden do), and the softmax below runs with a unit scale
         const float sc = BIAS ? 1.f : a.scale_log2;
         const float cap_out = a.softcap * kLog2e;
-        const float slope = (BIAS && a.alibi) ? a.alibi[(int64_t)b * a.alibi_sb + h] * kLog2e : 0.f;
+        const float slope = (BIAS && a.alibi) ? a.alibi[(int64_t)b * a.alibi_sb + h0 + (x * 128 + r) % gq] * kLog2e : 0.f;
         const float rel = (float)(qi + sk - sq);                 // alibi distance of key j is |rel - j|
         bool ok = true;
         const int nt_x = x == 0 ? nt0 : ntiles;
@@ -422,7 +435,7 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
         if (ok) {
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            T* orow = obase + (int64_t)(x * 128 + r) * a.o_ss;
+            T* orow = out_row(x * 128 + r);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t oreg[32];
@@ -440,7 +453,7 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                     }
                 }
             }
-            if (r < rows && lbase) lbase[(int64_t)(x * 128 + r) * a.lse_ss] = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : INFINITY;
+            if (r < rows && a.lse) *lse_slot(x * 128 + r) = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : INFINITY;
         }
     }
     }
@@ -818,7 +831,7 @@ bool tensor_map_encoder_available() { return encode_fn() != nullptr; }
 
 // (dim, head, row, batch) view with a [64 x 1 x 128 x 1] box and 128-byte swizzle
 int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads, int64_t rows, int batch,
-                  int64_t stride_h, int64_t stride_s, int64_t stride_b, int box_rows) {
+                  int64_t stride_h, int64_t stride_s, int64_t stride_b, int box_rows, int box_heads) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
     // The encoder is a driver call and wants a current context.  A thread that has made no runtime call yet (an
@@ -831,7 +844,7 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
     }
     cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)batch};
     cuuint64_t strides[3] = {(cuuint64_t)stride_h * 2, (cuuint64_t)stride_s * 2, (cuuint64_t)stride_b * 2};
-    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(map, dtype == FA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -881,7 +894,8 @@ static int launch_sm100_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
     auto kern = fwd_sm100_kernel2<T, D, BIAS>;
     const int smem = FwdSm100Smem2<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-    dim3 grid((p.sq + 255) / 256, p.hq, p.b);
+    const int qpc = 256 / a.gq;                              // query positions of a CTA
+    dim3 grid((p.sq + qpc - 1) / qpc, a.gq > 1 ? p.hkv : p.hq, p.b);
     kern<<<grid, 384, smem, st>>>(a);
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
@@ -914,7 +928,10 @@ int launch_fwd_sm100(const fa_fwd_params& p) {
     const int64_t k_rows = packed ? p.total_k : p.sk;
     const int nb = packed ? 1 : p.b;
     auto bstride = [&](const fa_tensor& t, int64_t rows) { return packed || p.b == 1 ? rows * t.stride_s : t.stride_b; };
-    if (int e = make_tile_map(&a.tq, p.dtype, p.q.ptr, p.d, p.hq, q_rows, nb, p.q.stride_h, p.q.stride_s, bstride(p.q, q_rows), 128)) return e;
+    // Short dense queries under a query group: the group's heads are stacked into the tile rows (two-tile kernel)
+    const int G = p.hq / p.hkv;
+    a.gq = (!packed && p.d <= 128 && p.sq < 128 && G > 1 && G <= 128 && (G & (G - 1)) == 0) ? G : 1;
+    if (int e = make_tile_map(&a.tq, p.dtype, p.q.ptr, p.d, p.hq, q_rows, nb, p.q.stride_h, p.q.stride_s, bstride(p.q, q_rows), 128 / a.gq, a.gq)) return e;
     const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
     if (cache) {
         // rows of one page / cache entry; the number of pages or cache entries is not passed down, so the outermost

@@ -492,9 +492,10 @@ __device__ __forceinline__ float2 ex2_poly2(float2 x) {
 
 }  // namespace sm100
 
-// (dim, head, row, batch) view with a [64 x 1 x box_rows x 1] box and 128-byte swizzle (fwd_sm100.cu)
+// (dim, head, row, batch) view with a [64 x box_heads x box_rows x 1] box and 128-byte swizzle (fwd_sm100.cu); the box
+// lands in shared memory as box_rows x box_heads rows of 128 bytes, heads fastest
 int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads, int64_t rows, int batch,
-                  int64_t stride_h, int64_t stride_s, int64_t stride_b, int box_rows);
+                  int64_t stride_h, int64_t stride_s, int64_t stride_b, int box_rows, int box_heads = 1);
 bool tensor_map_encoder_available();
 // code left by a timed-out wait in the backward kernels (bwd_sm100.cu); synchronises
 int bwd_sm100_error_flag(bool clear);

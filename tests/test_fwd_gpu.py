@@ -212,6 +212,25 @@ def test_head_dims_192_and_256_on_the_tcgen05_forward(d, dt):
     assert_lse(lse, f_l)
 
 
+@pytest.mark.parametrize("sq,hkv", [(5, 2), (37, 4), (100, 1), (127, 8)])
+@pytest.mark.parametrize("d", [64, 128])
+def test_short_queries_stack_their_query_group_into_the_tiles(sq, hkv, d):
+    """Fewer than 128 queries under a query group: the tcgen05 forward stacks the group's heads into the tile rows
+    (row = query position x group + head in group), so masks, alibi slopes and output rows are per row, not per CTA.
+    Causal, a sliding window, softcap with per-head alibi slopes; 16 heads over 1 to 8 KV heads."""
+    import fa_b200_capi as capi
+    torch.manual_seed(31 + sq)
+    b, sk, h, dt = 2, 700, 16, torch.bfloat16
+    q, k, v = torch.randn(b, sq, h, d).to(dt), torch.randn(b, sk, hkv, d).to(dt), torch.randn(b, sk, hkv, d).to(dt)
+    slopes = torch.rand(b, h) * 0.2
+    for causal, win, cap, al in ((True, (-1, -1), 0.0, None), (False, (256, 10), 0.0, None), (True, (-1, -1), 2.5, slopes)):
+        (lp_o, _), (f_o, f_l) = fwd_refs(q, k, v, d ** -0.5, causal, win, cap, alibi=al)
+        out, lse = run_dense(2, q, k, v, d ** -0.5, causal, win, cap, alibi=al)
+        assert capi.last_kernel() == "sm100_tcgen05_2q"
+        assert_within("out", out, lp_o, f_o)
+        assert_lse(lse, f_l)
+
+
 def test_strided_inputs_and_packed_variants():
     import flash_attn_npu as m
     torch.manual_seed(6)
