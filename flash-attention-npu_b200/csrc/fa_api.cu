@@ -79,7 +79,10 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
     const int nblocks = (p.sk + kGenericBN - 1) / kGenericBN;
     int nsplit = 1;
     plan.use_decode = fwd_decode_supported(p) ? 1 : 0;
+    // a cache call that the tcgen05 forward takes whole (no split-KV) is planned with one split
+    const bool whole = g_policy == 0 && cache_like && p.num_splits == 0 && !p.partials_only && fwd_sm100_supported(p);
     if (p.num_splits > 1) nsplit = p.num_splits;
+    else if (whole) nsplit = 1;
     else if (p.num_splits == 0 && plan.use_decode && nblocks > 1) {
         // decode kernel: the unit of parallelism is a warp per (sequence, KV head, split); aim at about
         // 1024 keys per split, at least four waves of warps, and never fewer than 256 keys per split
@@ -92,7 +95,7 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
         long n = by_occ > by_bal ? by_occ : by_bal;
         if (n > cap) n = cap;
         nsplit = (int)(n < 1 ? 1 : n);
-    } else if (p.num_splits == 0 && cache_like && nblocks > 1 && p.sq <= 64 && !(g_policy == 0 && fwd_sm100_supported(p))) {
+    } else if (p.num_splits == 0 && cache_like && nblocks > 1 && p.sq <= 64) {
         const long base = (long)mblocks * (plan.pack_gqa ? p.hkv : p.hq) * (p.b > 0 ? p.b : 1);
         const long target = 4L * sm_count();
         long by_occ = base >= target ? 1 : (target + base - 1) / base;

@@ -866,14 +866,19 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
         // KV-cache calls (prefill against a cache): lengths and pages are read on the device
         if (p.cu_seqlens_q || p.cu_seqlens_k || !p.seqused_k) return false;
         if (p.block_table && (p.page_size <= 0 || p.page_size % 64)) return false;
-        // Short queries belong to the split-KV decode kernels (up to 64 stacked rows a KV head).  A short chunk with
-        // more stacked rows than that (speculative decoding, small prefill chunks under large query groups) runs
-        // here without split-KV when the (batch x head) CTAs alone fill half of the GPU; otherwise the general
-        // kernel with its splits is the better use of the SMs.
+        // Short queries (fewer than 64 a head).  Up to 16 stacked rows a KV head belong to the split-KV decode kernel.
+        // Above that this kernel takes the call, without split-KV, when it has enough CTAs — with the query group
+        // stacked into the tile rows a CTA streams a KV head's cache once for all its rows (5.3 TB/s at 32 or 64
+        // stacked rows, B16, against 2.9 TB/s of the decode kernel's 17-64-row form); otherwise the decode kernel
+        // (up to 64 rows) or the general kernel with their splits use the SMs better.
         if (p.sq < 64) {
             const int G = p.hq / p.hkv;
-            if (p.sq * G <= 64 || p.sq < 8) return false;
-            if ((long)p.b * p.hq < sm_count() / 2) return false;
+            if (p.sq * G <= 16) return false;
+            const bool stack = p.d <= 128 && G > 1 && G <= 128 && (G & (G - 1)) == 0;
+            const long ctas = stack ? (long)p.b * p.hkv * ((p.sq * G + 255) / 256) : (long)p.b * p.hq;
+            // up to 64 stacked rows the alternative is the decode kernel at about half of the HBM rate; above, the
+            // general mma.sync kernel at about 70 TFLOP/s, which a handful of these CTAs (10 TFLOP/s each) already match
+            if (ctas < (p.sq * G <= 64 ? sm_count() / 2 : 8)) return false;
         }
     }
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
