@@ -788,7 +788,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--e2e-kv-heads", type=int, default=0,
                     help="KV heads per chunk of the end-to-end leg's host pipeline (0 = a whole batch entry, contiguous copies)")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "decode", "mla", "fwd256", "decode4"],
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "decode", "mla", "fwd256", "decode4", "decode4s"],
                     help="run two calls of one kernel on a small case (for a profiler capture) and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -954,14 +954,16 @@ def profile_case(name):
                 ext.bwd(do, q, k, v, out, lse, None, None, None, None, 0.0, d ** -0.5, True, -1, -1, 0.0, False, None, None)
     else:
         page = 256
-        b = 16
-        lo, hi = (1024, 32769) if name in ("decode", "decode4") else (4096, 65537)
+        # decode4: 8 sequences, too few CTAs for the stacked tcgen05 forward, so the decode kernel's 17-64-row form runs;
+        # decode4s: 16 sequences, the same call shape on the stacked tcgen05 forward
+        b = 8 if name == "decode4" else 16
+        lo, hi = (1024, 32769) if name in ("decode", "decode4", "decode4s") else (4096, 65537)
         lens = torch.randint(lo, hi, (b,), generator=g, dtype=torch.int32)
         table, pool, _ = _paged_tables((lens + 1).tolist(), page, g)
         lens_d, table_d = lens.to(dev), table.to(dev)
-        if name in ("decode", "decode4"):
+        if name in ("decode", "decode4", "decode4s"):
             hq, hkv, d = (32, 8, 128) if name == "decode" else (64, 8, 128)
-            sq = 1 if name == "decode" else 4              # decode4: 4 new tokens x group of 8 = 32 stacked rows a KV head
+            sq = 1 if name == "decode" else 4              # decode4*: 4 new tokens x group of 8 = 32 stacked rows a KV head
             kc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
             vc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
             q = torch.randn(b, sq, hq, d, device=dev, dtype=torch.bfloat16)
