@@ -954,8 +954,8 @@ def profile_case(name):
                 ext.bwd(do, q, k, v, out, lse, None, None, None, None, 0.0, d ** -0.5, True, -1, -1, 0.0, False, None, None)
     else:
         page = 256
-        # decode4: 8 sequences, too few CTAs for the stacked tcgen05 forward, so the decode kernel's 17-64-row form runs;
-        # decode4s: 16 sequences, the same call shape on the stacked tcgen05 forward
+        # decode4 / decode4s: 32 stacked rows a KV head on the decode kernel's 17-64-row form (the cache capacity of
+        # 32768 keys keeps such calls off the stacked tcgen05 forward), 8 and 16 sequences
         b = 8 if name == "decode4" else 16
         lo, hi = (1024, 32769) if name in ("decode", "decode4", "decode4s") else (4096, 65537)
         lens = torch.randint(lo, hi, (b,), generator=g, dtype=torch.int32)

@@ -876,9 +876,12 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
             if (p.sq * G <= 16) return false;
             const bool stack = p.d <= 128 && G > 1 && G <= 128 && (G & (G - 1)) == 0;
             const long ctas = stack ? (long)p.b * p.hkv * ((p.sq * G + 255) / 256) : (long)p.b * p.hq;
-            // up to 64 stacked rows the alternative is the decode kernel at about half of the HBM rate; above, the
-            // general mma.sync kernel at about 70 TFLOP/s, which a handful of these CTAs (10 TFLOP/s each) already match
-            if (ctas < (p.sq * G <= 64 ? sm_count() / 2 : 8)) return false;
+            // Up to 64 stacked rows the alternative is the decode kernel at about half of the HBM rate, and it splits
+            // long sequences over CTAs, which this kernel does not: with lengths the host cannot see, one long sequence
+            // among short ones would set the time of the whole call, so this kernel only takes such calls when the
+            // cache capacity bounds a CTA's walk (64 key tiles).  Above 64 rows the alternative is the general mma.sync
+            // kernel at about 70 TFLOP/s, which a handful of these CTAs (10 TFLOP/s each) already match.
+            if (p.sq * G <= 64 ? (ctas < sm_count() / 2 || p.sk > 8192) : ctas < 8) return false;
         }
     }
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
