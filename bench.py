@@ -954,16 +954,17 @@ def profile_case(name):
                 ext.bwd(do, q, k, v, out, lse, None, None, None, None, 0.0, d ** -0.5, True, -1, -1, 0.0, False, None, None)
     else:
         page = 256
-        # decode4 / decode4s: 32 stacked rows a KV head on the decode kernel's 17-64-row form (the cache capacity of
-        # 32768 keys keeps such calls off the stacked tcgen05 forward), 8 and 16 sequences
-        b = 8 if name == "decode4" else 16
+        # decode4: 4 new tokens under a query group of 6 (24 stacked rows a KV head; the group cannot be stacked into
+        # the tcgen05 tiles) on the decode kernel's 17-64-row form; decode4s: a group of 8 (32 stacked rows) on the
+        # tcgen05 forward with the group in the tile rows and the keys split over CTAs
+        b = 16
         lo, hi = (1024, 32769) if name in ("decode", "decode4", "decode4s") else (4096, 65537)
         lens = torch.randint(lo, hi, (b,), generator=g, dtype=torch.int32)
         table, pool, _ = _paged_tables((lens + 1).tolist(), page, g)
         lens_d, table_d = lens.to(dev), table.to(dev)
         if name in ("decode", "decode4", "decode4s"):
-            hq, hkv, d = (32, 8, 128) if name == "decode" else (64, 8, 128)
-            sq = 1 if name == "decode" else 4              # decode4*: 4 new tokens x group of 8 = 32 stacked rows a KV head
+            hq, hkv, d = (32, 8, 128) if name == "decode" else ((48, 8, 128) if name == "decode4" else (64, 8, 128))
+            sq = 1 if name == "decode" else 4
             kc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
             vc = torch.randn(pool, page, hkv, d, device=dev, dtype=torch.bfloat16)
             q = torch.randn(b, sq, hq, d, device=dev, dtype=torch.bfloat16)

@@ -79,11 +79,20 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
     const int nblocks = (p.sk + kGenericBN - 1) / kGenericBN;
     int nsplit = 1;
     plan.use_decode = fwd_decode_supported(p) ? 1 : 0;
-    // a cache call that the tcgen05 forward takes whole (no split-KV) is planned with one split
-    const bool whole = g_policy == 0 && cache_like && p.num_splits == 0 && !p.partials_only && fwd_sm100_supported(p);
+    // A cache call that the tcgen05 forward takes: prefill chunks (64 or more rows a head) and head dims above 128 run
+    // whole; short chunks are split over the keys so that about two waves of CTAs exist and one long sequence among
+    // short ones does not set the call's time (the lengths are not known here: the split is by the cache capacity).
+    plan.use_sm100 = (g_policy == 0 && cache_like && !p.partials_only && fwd_sm100_supported(p) && (p.d <= 128 || p.num_splits <= 1)) ? 1 : 0;
     if (p.num_splits > 1) nsplit = p.num_splits;
-    else if (whole) nsplit = 1;
-    else if (p.num_splits == 0 && plan.use_decode && nblocks > 1) {
+    else if (plan.use_sm100 && (p.num_splits == 1 || p.sq >= 64 || p.d > 128)) nsplit = 1;
+    else if (plan.use_sm100) {
+        const bool stack = G > 1 && G <= 128 && (G & (G - 1)) == 0;
+        const long ctas = (long)(p.b > 0 ? p.b : 1) * (stack ? p.hkv : p.hq) * (stack ? (p.sq * G + 255) / 256 : 1);
+        long n = (2L * sm_count() + ctas - 1) / ctas;
+        const long cap = (p.sk + 511) / 512;                 // at least 512 keys a split
+        if (n > cap) n = cap;
+        nsplit = (int)(n < 1 ? 1 : n);
+    } else if (p.num_splits == 0 && plan.use_decode && nblocks > 1) {
         // decode kernel: the unit of parallelism is a warp per (sequence, KV head, split); aim at about
         // 1024 keys per split, at least four waves of warps, and never fewer than 256 keys per split
         // (with 17-64 stacked rows a whole CTA streams one KV head: four waves of CTAs)
@@ -106,6 +115,7 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
     if (nsplit > 256) nsplit = 256;
     if (nsplit < 1) nsplit = 1;
     plan.blocks_per_split = nblocks > 0 ? (nblocks + nsplit - 1) / nsplit : 1;
+    if (plan.use_sm100) plan.blocks_per_split += plan.blocks_per_split & 1;      // whole 128-key tiles a split
     plan.nsplit = nblocks > 0 ? (nblocks + plan.blocks_per_split - 1) / plan.blocks_per_split : 1;
     plan.rotate_q = (p.rotary_cos && p.rotary_sin) ? 1 : 0;
     const size_t rows_all = (size_t)(p.cu_seqlens_q ? p.total_q : (int64_t)p.b * p.sq) * p.hq;
@@ -158,8 +168,12 @@ static int run_forward(const fa_fwd_params& pin, bool allow_fast) {
             p.q.stride_b = (int64_t)p.sq * p.hq * p.d;
         }
     }
-    if (allow_fast && g_policy == 0 && plan.nsplit == 1 && !p.partials_only && fwd_sm100_supported(p))
-        return launch_fwd_sm100(p);
+    const bool cache_call = p.seqused_k || p.block_table;
+    if (allow_fast && g_policy == 0 && !p.partials_only && fwd_sm100_supported(p) &&
+        (plan.nsplit == 1 || (cache_call && plan.use_sm100 && p.d <= 128))) {
+        if (int e = launch_fwd_sm100(p, plan.nsplit, plan.blocks_per_split * kGenericBN, o_part, lse_part)) return e;
+        return plan.nsplit > 1 ? launch_fwd_combine(p, plan.nsplit, o_part, lse_part, 0) : FA_OK;
+    }
 
     if (p.partials_only && plan.nsplit == 1) { o_part = p.o_partial; lse_part = p.lse_partial; }
     int e = (g_policy == 0 && plan.use_decode) ? launch_fwd_decode(p, plan, o_part, lse_part)

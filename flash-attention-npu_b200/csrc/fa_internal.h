@@ -42,7 +42,8 @@ int launch_fwd_decode(const fa_fwd_params& p, const FwdPlan& plan, float* o_part
 bool fwd_decode_supported(const fa_fwd_params& p);
 void decode_set_use_tma(int v);
 int decode_error_flag(bool clear);
-int launch_fwd_sm100(const fa_fwd_params& p);
+// nsplit > 1 (two-tile kernel, cache calls): fp32 partials into o_part / lse_part, keys_per_split a multiple of 128
+int launch_fwd_sm100(const fa_fwd_params& p, int nsplit = 1, int keys_per_split = 0, float* o_part = nullptr, float* lse_part = nullptr);
 bool fwd_sm100_supported(const fa_fwd_params& p);
 // reads (and optionally clears) the code a timed-out wait left behind; synchronises
 int sm100_error_flag(bool clear);

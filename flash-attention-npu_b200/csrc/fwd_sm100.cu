@@ -38,6 +38,12 @@ struct alignas(64) Sm100FwdArgs {
     int64_t alibi_sb;
     int kv_box;                          // rows of one K/V copy: 128, or 64 when pages are an odd multiple of 64 tokens
     int gq;                              // two-tile kernel: 1, or the query group size when a KV head's heads are stacked into the tile rows
+    // split-KV (two-tile kernel, cache calls): split s of a sequence takes keys [s * keys_per_split, (s + 1) * ...) and
+    // leaves a normalised fp32 partial output and its LSE for the combine kernel (nsplit = 1: final output directly)
+    int nsplit, keys_per_split;          // keys_per_split is a multiple of 128
+    float* o_part;                       // (nsplit, rows_all, D), rows_all = batch * sq * hq, row = (b * sq + qpos) * hq + head
+    float* lse_part;                     // (nsplit, rows_all)
+    int64_t rows_all;
 };
 
 // =================================================================================================
@@ -99,7 +105,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     const int qpt = 128 / gq;                                // query positions of one 128-row tile
     const int hk = gq > 1 ? (int)blockIdx.y : (int)blockIdx.y / (a.hq / a.hkv);
     const int h0 = gq > 1 ? hk * gq : (int)blockIdx.y;       // head of tile row 0
-    const int mblk = gridDim.x - 1 - blockIdx.x;
+    const int split = blockIdx.x % a.nsplit;
+    const int mblk = gridDim.x / a.nsplit - 1 - blockIdx.x / a.nsplit;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
     if (a.seqused_k) {                                       // cache call: the length lives on the device
@@ -117,6 +124,10 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     window_bounds(m0 + (rows_cta - 1) / gq, sq, sk, wl, wr, lo_last, hi_last);
     int t_lo = lo_first / 128, t_hi = hi_last < 0 ? 0 : hi_last / 128 + 1;
     if (sk <= 0 || lo_first >= sk) { t_lo = 0; t_hi = 0; }
+    if (a.nsplit > 1) {                                      // this split's share of the key tiles
+        t_lo = max(t_lo, split * (a.keys_per_split / 128));
+        t_hi = min(t_hi, (split + 1) * (a.keys_per_split / 128));
+    }
     const int ntiles = max(0, t_hi - t_lo);
     // The first 128 rows of the block may end before the last key tile of the block (under a causal mask they end one
     // tile earlier): they skip the tiles in which every one of their entries is masked.
@@ -135,7 +146,15 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     auto lse_slot = [&](int t) -> float* {
         return a.lse + (a.cu_q ? 0 : (int64_t)b * a.lse_sb) + (int64_t)(h0 + t % gq) * a.lse_sh + (int64_t)(q_off + m0 + t / gq) * a.lse_ss;
     };
+    // split-KV: row of tile row t in the partial buffers
+    auto part_row = [&](int t) -> int64_t {
+        return (int64_t)split * a.rows_all + ((int64_t)b * a.sq + m0 + t / gq) * a.hq + h0 + t % gq;
+    };
 
+    if (ntiles == 0 && a.nsplit > 1) {                       // an empty split: weight zero in the combine, O never read
+        if (tid < rows_cta) a.lse_part[part_row(tid)] = -INFINITY;
+        return;
+    }
     if (ntiles == 0) {
         if (tid < rows_cta) {
             uint4 z = make_uint4(0, 0, 0, 0);
@@ -436,12 +455,18 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             T* orow = out_row(x * 128 + r);
+            float* prow = a.nsplit > 1 ? a.o_part + part_row(x * 128 + r) * D : nullptr;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t oreg[32];
                 tmem_ld32(t_o + c * 32, oreg);
                 tmem_wait_ld();
-                if (r < rows) {
+                if (r < rows && prow) {
+#pragma unroll
+                    for (int v = 0; v < 8; ++v)
+                        reinterpret_cast<float4*>(prow + c * 32)[v] = make_float4(__uint_as_float(oreg[4 * v]) * inv, __uint_as_float(oreg[4 * v + 1]) * inv,
+                                                                                 __uint_as_float(oreg[4 * v + 2]) * inv, __uint_as_float(oreg[4 * v + 3]) * inv);
+                } else if (r < rows) {
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
                         uint4 pk;
@@ -453,7 +478,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                     }
                 }
             }
-            if (r < rows && a.lse) *lse_slot(x * 128 + r) = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : INFINITY;
+            if (r < rows && prow) a.lse_part[part_row(x * 128 + r)] = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : -INFINITY;
+            else if (r < rows && a.lse) *lse_slot(x * 128 + r) = l_run > 0.f ? (m_used + log2f(l_run)) * kLn2 : INFINITY;
         }
     }
     }
@@ -867,21 +893,15 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
         if (p.cu_seqlens_q || p.cu_seqlens_k || !p.seqused_k) return false;
         if (p.block_table && (p.page_size <= 0 || p.page_size % 64)) return false;
         // Short queries (fewer than 64 a head).  Up to 16 stacked rows a KV head belong to the split-KV decode kernel.
-        // Above that this kernel takes the call, without split-KV, when it has enough CTAs — with the query group
-        // stacked into the tile rows a CTA streams a KV head's cache once for all its rows (5.3 TB/s at 32 or 64
-        // stacked rows, B16, against 2.9 TB/s of the decode kernel's 17-64-row form); otherwise the decode kernel
-        // (up to 64 rows) or the general kernel with their splits use the SMs better.
+        // Above that the two-tile kernel takes the call with the query group stacked into the tile rows and the keys
+        // split over CTAs (partials + combine): a CTA streams its share of a KV head's cache once for all the rows.
+        // A group that cannot be stacked (not a power of two) would read the cache once per head: such calls stay
+        // with the decode kernel up to 64 stacked rows and come here above that, where the alternative is mma.sync.
         if (p.sq < 64) {
             const int G = p.hq / p.hkv;
             if (p.sq * G <= 16) return false;
             const bool stack = p.d <= 128 && G > 1 && G <= 128 && (G & (G - 1)) == 0;
-            const long ctas = stack ? (long)p.b * p.hkv * ((p.sq * G + 255) / 256) : (long)p.b * p.hq;
-            // Up to 64 stacked rows the alternative is the decode kernel at about half of the HBM rate, and it splits
-            // long sequences over CTAs, which this kernel does not: with lengths the host cannot see, one long sequence
-            // among short ones would set the time of the whole call, so this kernel only takes such calls when the
-            // cache capacity bounds a CTA's walk (64 key tiles).  Above 64 rows the alternative is the general mma.sync
-            // kernel at about 70 TFLOP/s, which a handful of these CTAs (10 TFLOP/s each) already match.
-            if (p.sq * G <= 64 ? (ctas < sm_count() / 2 || p.sk > 8192) : ctas < 8) return false;
+            if (!stack && (p.sq * G <= 64 || p.d > 128)) return false;
         }
     }
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
@@ -903,7 +923,7 @@ static int launch_sm100_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
     const int smem = FwdSm100Smem2<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
     const int qpc = 256 / a.gq;                              // query positions of a CTA
-    dim3 grid((p.sq + qpc - 1) / qpc, a.gq > 1 ? p.hkv : p.hq, p.b);
+    dim3 grid(((p.sq + qpc - 1) / qpc) * a.nsplit, a.gq > 1 ? p.hkv : p.hq, p.b);
     kern<<<grid, 384, smem, st>>>(a);
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
@@ -928,9 +948,11 @@ static int launch_sm100_wide_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
     return (p.softcap > 0.f || p.alibi_slopes) ? launch_sm100_wide_b<T, D, true>(p, a) : launch_sm100_wide_b<T, D, false>(p, a);
 }
 
-int launch_fwd_sm100(const fa_fwd_params& p) {
+int launch_fwd_sm100(const fa_fwd_params& p, int nsplit, int keys_per_split, float* o_part, float* lse_part) {
     Sm100FwdArgs a;
     a.kv_box = 128;
+    a.nsplit = nsplit > 1 ? nsplit : 1; a.keys_per_split = keys_per_split; a.o_part = o_part; a.lse_part = lse_part;
+    a.rows_all = (int64_t)p.b * p.sq * p.hq;
     const bool packed = p.cu_seqlens_q != nullptr;
     const int64_t q_rows = packed ? p.total_q : p.sq;
     const int64_t k_rows = packed ? p.total_k : p.sk;

@@ -106,9 +106,12 @@ WIDE_CASES = [
 
 @pytest.mark.parametrize("case", WIDE_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
 @pytest.mark.parametrize("num_splits", [0, 1, 5])
-def test_decode_with_17_to_64_stacked_rows_runs_on_the_tma_kernel(case, num_splits):
-    """Several new tokens a step and large query groups stack more than 16 rows on a KV head: four warps share the
-    head's tiles, 16 rows each.  Ragged device-resident lengths (one shorter than a tile), NaN past the lengths."""
+def test_decode_with_17_to_64_stacked_rows(case, num_splits):
+    """Several new tokens a step and large query groups stack more than 16 rows on a KV head.  A power-of-two group at
+    head dim <= 128 runs on the tcgen05 forward with the group stacked into the tile rows and the keys split over CTAs
+    (partials + combine; one split, the planner's count and a forced count of 5); other groups and head dim 256 run on
+    the decode kernel's form in which four warps share a head's tiles.  Ragged device-resident lengths (one shorter
+    than a tile), NaN past the lengths."""
     import flash_attn_npu as m
     import fa_b200_capi as capi
     dt, b, h, hkv, sq, d, paged, causal, win, cap = case
@@ -140,7 +143,9 @@ def test_decode_with_17_to_64_stacked_rows_runs_on_the_tma_kernel(case, num_spli
                                          causal=causal, window_size=win, softcap=cap, num_splits=num_splits,
                                          return_softmax_lse=True)
     torch.cuda.synchronize()
-    assert capi.last_kernel() == "decode_splitkv_tma"
+    g_ = h // hkv
+    stacked = d <= 128 and g_ & (g_ - 1) == 0
+    assert capi.last_kernel() == ("sm100_tcgen05_2q" if stacked else "decode_splitkv_tma")
     assert capi.lib.fa_debug_get(2) == 0
     assert torch.isfinite(out).all()
     assert_within("out", out.cpu(), lp_o, f_o)
@@ -450,8 +455,8 @@ def test_prefill_against_cache_uses_tcgen05(paged, page, append):
 
 def test_short_chunk_with_many_stacked_rows_runs_on_tcgen05():
     """32 new tokens a sequence under a query group of 8 are 256 stacked rows a KV head: too many for the split-KV
-    decode kernel, fewer than 64 rows a head; with 128 (batch x head) CTAs the tcgen05 forward takes the call (rows past
-    the chunk are zero-filled by the tile copy), otherwise the general kernel would.  Append + causal, ragged lengths."""
+    decode kernel, fewer than 64 rows a head; the tcgen05 forward takes the call with the group stacked into its tile
+    rows (rows past the chunk are zero-filled by the tile copy).  Append + causal, ragged lengths."""
     import flash_attn_npu as m
     import fa_b200_capi as capi
     g = torch.Generator().manual_seed(7)
@@ -473,11 +478,11 @@ def test_short_chunk_with_many_stacked_rows_runs_on_tcgen05():
     assert capi.lib.fa_debug_get(2) == 0
     assert_within("out", out.cpu(), lp_o, f_o)
     assert_lse(lse, f_l)
-    # a single sequence with few heads does not fill the GPU: the general kernel with split-KV keeps such calls
-    # (the cache now holds the appended chunk)
+    # a single sequence does not fill the GPU with (sequence, KV head) CTAs: the same kernel then splits the keys over
+    # CTAs and the partials are combined (the cache now holds the appended chunk)
     out1 = m.flash_attn_with_kvcache(q[:1].cuda(), kg, vg, cache_seqlens=lens_t[:1].cuda() + sq,
                                      block_table=table[:1].cuda(), softmax_scale=scale, causal=True)
-    assert capi.last_kernel() == "generic_mma"
+    assert capi.last_kernel() == "sm100_tcgen05_2q"
     assert_within("single sequence", out1.cpu(), lp_o[:1], f_o[:1])
 
 
