@@ -79,17 +79,18 @@ void plan_forward(const fa_fwd_params& p, FwdPlan& plan) {
     const int nblocks = (p.sk + kGenericBN - 1) / kGenericBN;
     int nsplit = 1;
     plan.use_decode = fwd_decode_supported(p) ? 1 : 0;
-    // A cache call that the tcgen05 forward takes: prefill chunks (64 or more rows a head) and head dims above 128 run
-    // whole; short chunks are split over the keys so that about two waves of CTAs exist and one long sequence among
-    // short ones does not set the call's time (the lengths are not known here: the split is by the cache capacity).
+    // A cache call that the tcgen05 forward takes is split over the keys (two-tile kernel, head dim <= 128) until
+    // about two waves of CTAs exist, with at least 512 keys a split for short chunks and 2048 for prefill chunks of
+    // 64 or more rows a head; the split is by the cache capacity (the lengths are not known here), so one long sequence
+    // among short ones does not set the call's time either.
     plan.use_sm100 = (g_policy == 0 && cache_like && !p.partials_only && fwd_sm100_supported(p) && (p.d <= 128 || p.num_splits <= 1)) ? 1 : 0;
     if (p.num_splits > 1) nsplit = p.num_splits;
-    else if (plan.use_sm100 && (p.num_splits == 1 || p.sq >= 64 || p.d > 128)) nsplit = 1;
+    else if (plan.use_sm100 && (p.num_splits == 1 || p.d > 128)) nsplit = 1;
     else if (plan.use_sm100) {
-        const bool stack = G > 1 && G <= 128 && (G & (G - 1)) == 0;
-        const long ctas = (long)(p.b > 0 ? p.b : 1) * (stack ? p.hkv : p.hq) * (stack ? (p.sq * G + 255) / 256 : 1);
+        const long ctas = fwd_sm100_ctas(p);
         long n = (2L * sm_count() + ctas - 1) / ctas;
-        const long cap = (p.sk + 511) / 512;                 // at least 512 keys a split
+        const int min_keys = p.sq >= 64 ? 2048 : 512;
+        const long cap = (p.sk + min_keys - 1) / min_keys;
         if (n > cap) n = cap;
         nsplit = (int)(n < 1 ? 1 : n);
     } else if (p.num_splits == 0 && plan.use_decode && nblocks > 1) {

@@ -45,6 +45,7 @@ int decode_error_flag(bool clear);
 // nsplit > 1 (two-tile kernel, cache calls): fp32 partials into o_part / lse_part, keys_per_split a multiple of 128
 int launch_fwd_sm100(const fa_fwd_params& p, int nsplit = 1, int keys_per_split = 0, float* o_part = nullptr, float* lse_part = nullptr);
 bool fwd_sm100_supported(const fa_fwd_params& p);
+long fwd_sm100_ctas(const fa_fwd_params& p);         // CTAs of one key split of the call
 // reads (and optionally clears) the code a timed-out wait left behind; synchronises
 int sm100_error_flag(bool clear);
 int launch_append_rotary(const fa_fwd_params& p, void* q_rot, int rotate_q_by_pos);

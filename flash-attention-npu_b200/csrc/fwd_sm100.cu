@@ -948,6 +948,18 @@ static int launch_sm100_wide_t(const fa_fwd_params& p, Sm100FwdArgs& a) {
     return (p.softcap > 0.f || p.alibi_slopes) ? launch_sm100_wide_b<T, D, true>(p, a) : launch_sm100_wide_b<T, D, false>(p, a);
 }
 
+// query group stacked into the tile rows of the two-tile kernel (dense q shorter than 128, power-of-two group)
+static int sm100_stack_factor(const fa_fwd_params& p) {
+    const int G = p.hq / p.hkv;
+    return (!p.cu_seqlens_q && p.d <= 128 && p.sq < 128 && G > 1 && G <= 128 && (G & (G - 1)) == 0) ? G : 1;
+}
+// CTAs of one split of a dense / cache call
+long fwd_sm100_ctas(const fa_fwd_params& p) {
+    const int gq = sm100_stack_factor(p);
+    const int rows_cta = p.d > 128 ? 128 : 256;
+    return (long)(p.b > 0 ? p.b : 1) * (gq > 1 ? p.hkv : p.hq) * (((long)p.sq * gq + rows_cta - 1) / rows_cta);
+}
+
 int launch_fwd_sm100(const fa_fwd_params& p, int nsplit, int keys_per_split, float* o_part, float* lse_part) {
     Sm100FwdArgs a;
     a.kv_box = 128;
@@ -959,8 +971,7 @@ int launch_fwd_sm100(const fa_fwd_params& p, int nsplit, int keys_per_split, flo
     const int nb = packed ? 1 : p.b;
     auto bstride = [&](const fa_tensor& t, int64_t rows) { return packed || p.b == 1 ? rows * t.stride_s : t.stride_b; };
     // Short dense queries under a query group: the group's heads are stacked into the tile rows (two-tile kernel)
-    const int G = p.hq / p.hkv;
-    a.gq = (!packed && p.d <= 128 && p.sq < 128 && G > 1 && G <= 128 && (G & (G - 1)) == 0) ? G : 1;
+    a.gq = sm100_stack_factor(p);
     if (int e = make_tile_map(&a.tq, p.dtype, p.q.ptr, p.d, p.hq, q_rows, nb, p.q.stride_h, p.q.stride_s, bstride(p.q, q_rows), 128 / a.gq, a.gq)) return e;
     const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
     if (cache) {
