@@ -52,6 +52,8 @@ struct alignas(64) Sm100BwdArgs {
     const int32_t* cu_q;
     const int32_t* cu_k;
     int b, sq, sk, hq, hkv;
+    int d;                              // the call's head dim (a multiple of 8, at most the kernels' 64 / 128): tile copies zero-fill
+                                        // the columns past it, the epilogues store d columns
     float scale, scale_log2;
     int causal, wl, wr;
     // dS^T tiles handed from the dK/dV kernel to the dQ kernel through global memory (dense calls within the
@@ -83,10 +85,13 @@ enum { E_FIX = 0, E_RF0, E_RF1, E_RE0, E_RE1, E_S0, E_S1, E_P0, E_P1, E_F0, E_F1
 enum { G_FIX = 0, G_KF0, G_KF1, G_KF2, G_KE0, G_KE1, G_KE2, G_VF0, G_VF1, G_VE0, G_VE1, G_S0, G_S1, G_SA0, G_SA1, G_DP, G_DS,
        G_ACC, G_COUNT };
 
+// 32 accumulator columns -> the row, scaled and rounded; `left` = columns of the row that remain from dst on (the
+// kernels run a head dim padded to 64 / 128, the row holds the call's own head dim)
 template <typename T>
-__device__ __forceinline__ void store_row_scaled(T* dst, const uint32_t (&r)[32], float s) {
+__device__ __forceinline__ void store_row_scaled(T* dst, const uint32_t (&r)[32], float s, int left) {
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
+        if (v * 8 >= left) break;
         uint4 pk;
         pk.x = Elem<T>::pack(__uint_as_float(r[8 * v + 0]) * s, __uint_as_float(r[8 * v + 1]) * s);
         pk.y = Elem<T>::pack(__uint_as_float(r[8 * v + 2]) * s, __uint_as_float(r[8 * v + 3]) * s);
@@ -385,7 +390,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
                 uint32_t acc[32];
                 tmem_ld32(tmem + lane_base + col + cc * 32, acc);
                 tmem_wait_ld();
-                if (r < krows) store_row_scaled<T>(row + cc * 32, acc, sc);
+                if (r < krows) store_row_scaled<T>(row + cc * 32, acc, sc, a.d - cc * 32);
             }
         }
     }
@@ -613,7 +618,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
                 uint32_t acc[32];
                 tmem_ld32(tmem + lane_base + COL_DQ + cg * 32, acc);
                 tmem_wait_ld();
-                if (r < rows) store_row_scaled<T>(row + cg * 32, acc, a.scale);
+                if (r < rows) store_row_scaled<T>(row + cg * 32, acc, a.scale, a.d - cg * 32);
             }
         }
     }
@@ -739,7 +744,7 @@ __global__ void __launch_bounds__(192, 1) bwd_dq_from_ds_sm100_kernel(const __gr
                 uint32_t acc[32];
                 tmem_ld32(tmem + lane_base + c * 32, acc);
                 tmem_wait_ld();
-                if (r < rows) store_row_scaled<T>(row + c * 32, acc, a.scale);
+                if (r < rows) store_row_scaled<T>(row + c * 32, acc, a.scale, a.d - c * 32);
             }
         }
     }
@@ -772,7 +777,7 @@ __global__ void __launch_bounds__(256) bwd_delta_sm100_kernel(const fa_bwd_param
             const int64_t row = base + u * RPW + sub;
             ov[u] = make_uint4(0, 0, 0, 0);
             dv[u] = make_uint4(0, 0, 0, 0);
-            if (row < rows) {
+            if (row < rows && c < p.d) {
                 int64_t tok, bb = 0, i;
                 int h;
                 if (small) { const uint32_t r32 = (uint32_t)row; tok = r32 / (uint32_t)p.hq; h = (int)(r32 % (uint32_t)p.hq); }
@@ -811,7 +816,7 @@ void bwd_sm100_set_ds_spill(int v) { g_ds_spill = v; }
 static size_t ds_tiles_bytes(const fa_bwd_params& p);
 
 bool bwd_sm100_supported(const fa_bwd_params& p) {
-    if (p.d != p.dv_dim || (p.d != 64 && p.d != 128)) return false;
+    if (p.d != p.dv_dim || p.d % 8 != 0 || p.d <= 0 || p.d > 128) return false;       // any head dim up to 128: padded to 64 / 128
     if (!(p.scale > 0.f)) return false;
     // softcap and alibi live in the dK/dV kernel only: such calls need the five-GEMM path (dense, dS tiles in the workspace)
     if ((p.softcap > 0.f || p.alibi_slopes) && !(g_ds_spill && ds_tiles_bytes(p) > 0)) return false;
@@ -902,7 +907,7 @@ int launch_bwd_sm100(const fa_bwd_params& p) {
         a.ds_tiles = reinterpret_cast<unsigned char*>(p.workspace) + delta_bytes(p);
     }
     a.cu_q = p.cu_seqlens_q; a.cu_k = p.cu_seqlens_k;
-    a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv;
+    a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv; a.d = p.d;
     a.scale = p.scale; a.scale_log2 = p.scale * kLog2e;
     a.softcap = p.softcap; a.cap_in2 = p.softcap > 0.f ? 2.f * kLog2e * p.scale / p.softcap : 0.f; a.cap_out = p.softcap * kLog2e;
     a.alibi = p.alibi_slopes; a.alibi_sb = p.alibi_stride_b;
@@ -910,8 +915,8 @@ int launch_bwd_sm100(const fa_bwd_params& p) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
     float* delta = reinterpret_cast<float*>(p.workspace);
     note_kernel(a.ds_tiles ? "sm100_tcgen05_bwd_5gemm" : "sm100_tcgen05_bwd");
-    if (p.dtype == FA_F16) return p.d == 64 ? launch_bwd_sm100_t<__half, 64>(p, a, delta, st) : launch_bwd_sm100_t<__half, 128>(p, a, delta, st);
-    return p.d == 64 ? launch_bwd_sm100_t<__nv_bfloat16, 64>(p, a, delta, st) : launch_bwd_sm100_t<__nv_bfloat16, 128>(p, a, delta, st);
+    if (p.dtype == FA_F16) return p.d <= 64 ? launch_bwd_sm100_t<__half, 64>(p, a, delta, st) : launch_bwd_sm100_t<__half, 128>(p, a, delta, st);
+    return p.d <= 64 ? launch_bwd_sm100_t<__nv_bfloat16, 64>(p, a, delta, st) : launch_bwd_sm100_t<__nv_bfloat16, 128>(p, a, delta, st);
 }
 
 }  // namespace fa

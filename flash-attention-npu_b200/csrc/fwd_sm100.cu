@@ -30,6 +30,8 @@ struct alignas(64) Sm100FwdArgs {
     int64_t bt_stride;
     int page_size, s_new;
     int b, sq, sk, hq, hkv;
+    int d;                               // the call's head dim (a multiple of 8): the kernels run the next of 64 / 128 / 192 / 256, the tile copies
+                                         // zero-fill the columns past d and the epilogue stores d columns
     float scale_log2;
     int causal, wl, wr;
     // score transforms of the BIAS instantiation: softcap (0 = off) and alibi slopes ((hq) or (b,hq), null = off)
@@ -160,7 +162,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
             uint4 z = make_uint4(0, 0, 0, 0);
             T* orow = out_row(tid);
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
+            for (int c = 0; c < D / 8; ++c)
+                if (c * 8 < a.d) reinterpret_cast<uint4*>(orow)[c] = z;
             if (a.lse) *lse_slot(tid) = INFINITY;
         }
         return;
@@ -455,7 +458,7 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             T* orow = out_row(x * 128 + r);
-            float* prow = a.nsplit > 1 ? a.o_part + part_row(x * 128 + r) * D : nullptr;
+            float* prow = a.nsplit > 1 ? a.o_part + part_row(x * 128 + r) * a.d : nullptr;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t oreg[32];
@@ -464,8 +467,9 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                 if (r < rows && prow) {
 #pragma unroll
                     for (int v = 0; v < 8; ++v)
-                        reinterpret_cast<float4*>(prow + c * 32)[v] = make_float4(__uint_as_float(oreg[4 * v]) * inv, __uint_as_float(oreg[4 * v + 1]) * inv,
-                                                                                 __uint_as_float(oreg[4 * v + 2]) * inv, __uint_as_float(oreg[4 * v + 3]) * inv);
+                        if (c * 32 + v * 4 < a.d)
+                            reinterpret_cast<float4*>(prow + c * 32)[v] = make_float4(__uint_as_float(oreg[4 * v]) * inv, __uint_as_float(oreg[4 * v + 1]) * inv,
+                                                                                     __uint_as_float(oreg[4 * v + 2]) * inv, __uint_as_float(oreg[4 * v + 3]) * inv);
                 } else if (r < rows) {
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
@@ -474,7 +478,7 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                         pk.y = Elem<T>::pack(__uint_as_float(oreg[8 * v + 2]) * inv, __uint_as_float(oreg[8 * v + 3]) * inv);
                         pk.z = Elem<T>::pack(__uint_as_float(oreg[8 * v + 4]) * inv, __uint_as_float(oreg[8 * v + 5]) * inv);
                         pk.w = Elem<T>::pack(__uint_as_float(oreg[8 * v + 6]) * inv, __uint_as_float(oreg[8 * v + 7]) * inv);
-                        reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
+                        if (c * 32 + v * 8 < a.d) reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
                     }
                 }
             }
@@ -556,7 +560,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel_wide(const __grid_con
             uint4 z = make_uint4(0, 0, 0, 0);
             T* orow = obase + (int64_t)tid * a.o_ss;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
+            for (int c = 0; c < D / 8; ++c)
+                if (c * 8 < a.d) reinterpret_cast<uint4*>(orow)[c] = z;
             if (lbase) lbase[(int64_t)tid * a.lse_ss] = INFINITY;
         }
         return;
@@ -821,7 +826,7 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel_wide(const __grid_con
                         pk.y = Elem<T>::pack(__uint_as_float(oreg[8 * v + 2]) * inv, __uint_as_float(oreg[8 * v + 3]) * inv);
                         pk.z = Elem<T>::pack(__uint_as_float(oreg[8 * v + 4]) * inv, __uint_as_float(oreg[8 * v + 5]) * inv);
                         pk.w = Elem<T>::pack(__uint_as_float(oreg[8 * v + 6]) * inv, __uint_as_float(oreg[8 * v + 7]) * inv);
-                        reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
+                        if (c * 32 + v * 8 < a.d) reinterpret_cast<uint4*>(orow + c * 32)[v] = pk;
                     }
                 }
             }
@@ -886,7 +891,7 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
 }
 
 bool fwd_sm100_supported(const fa_fwd_params& p) {
-    if (p.d != p.dv || (p.d != 64 && p.d != 128 && p.d != 192 && p.d != 256)) return false;
+    if (p.d != p.dv || p.d % 8 != 0 || p.d <= 0 || p.d > 256) return false;      // any head dim: the kernels pad it to 64 / 128 / 192 / 256
     const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
     if (cache) {
         // KV-cache calls (prefill against a cache): lengths and pages are read on the device
@@ -997,14 +1002,15 @@ int launch_fwd_sm100(const fa_fwd_params& p, int nsplit, int keys_per_split, flo
     a.softcap = p.softcap; a.cap_in = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
     a.alibi = p.alibi_slopes; a.alibi_sb = p.alibi_stride_b;
     a.causal = p.causal; a.wl = p.window_left; a.wr = p.window_right;
+    a.d = p.d;
     if (p.d > 128) {
         note_kernel("sm100_tcgen05_wide");
-        if (p.dtype == FA_F16) return p.d == 192 ? launch_sm100_wide_t<__half, 192>(p, a) : launch_sm100_wide_t<__half, 256>(p, a);
-        return p.d == 192 ? launch_sm100_wide_t<__nv_bfloat16, 192>(p, a) : launch_sm100_wide_t<__nv_bfloat16, 256>(p, a);
+        if (p.dtype == FA_F16) return p.d <= 192 ? launch_sm100_wide_t<__half, 192>(p, a) : launch_sm100_wide_t<__half, 256>(p, a);
+        return p.d <= 192 ? launch_sm100_wide_t<__nv_bfloat16, 192>(p, a) : launch_sm100_wide_t<__nv_bfloat16, 256>(p, a);
     }
     note_kernel("sm100_tcgen05_2q");
-    if (p.dtype == FA_F16) return p.d == 64 ? launch_sm100_t<__half, 64>(p, a) : launch_sm100_t<__half, 128>(p, a);
-    return p.d == 64 ? launch_sm100_t<__nv_bfloat16, 64>(p, a) : launch_sm100_t<__nv_bfloat16, 128>(p, a);
+    if (p.dtype == FA_F16) return p.d <= 64 ? launch_sm100_t<__half, 64>(p, a) : launch_sm100_t<__half, 128>(p, a);
+    return p.d <= 64 ? launch_sm100_t<__nv_bfloat16, 64>(p, a) : launch_sm100_t<__nv_bfloat16, 128>(p, a);
 }
 
 int sm100_error_flag(bool clear) {

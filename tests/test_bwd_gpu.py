@@ -190,3 +190,42 @@ def test_alibi_backward(per_batch, causal, window, cap):
     # without the slopes the gradients differ by far more than the tolerance: the bias is really applied
     plain = orc.attention_bwd(q.float(), k.float(), v.float(), do.float(), f_l, scale, causal, window, cap)
     assert (plain[0] - f32[0]).abs().max() > 0.05
+
+
+@pytest.mark.parametrize("d", [8, 40, 72, 96, 112])
+def test_any_head_dim_runs_on_the_tcgen05_kernels(d):
+    """Head dims that are not 64 or 128 (the reference's lists hold 111 -> 112, 1 and 4 -> 8 after the interface's padding):
+    the tcgen05 kernels run the next size up, the tile copies zero-fill the columns past the head dim and the epilogues
+    store the head dim's columns only.  Forward and backward, GQA, causal with ragged tails; tensors with guard columns
+    behind every row so that a store past the head dim would be seen."""
+    import fa_b200_capi as capi
+    from flash_attn_npu import flash_attn_npu as ext
+    torch.manual_seed(140 + d)
+    b, sq, sk, h, hkv, dt = 2, 333, 400, 4, 2, torch.bfloat16
+    pad = 8                                                     # guard columns (row stride d + 8)
+    def make(n, heads):
+        full = torch.randn(b, n, heads, d + pad).to(dt)
+        return full, full[..., :d]
+    qf, q = make(sq, h); kf, k = make(sk, hkv); vf, v = make(sk, hkv); dof, do = make(sq, h)
+    scale = d ** -0.5
+    lp_o, _ = orc.attention_fwd(q, k, v, scale, True)
+    f_o, f_l = orc.attention_fwd(q.float(), k.float(), v.float(), scale, True, data_type=torch.float32)
+    lp = orc.attention_bwd(q, k, v, do, f_l, scale, True)
+    f32 = orc.attention_bwd(q.float(), k.float(), v.float(), do.float(), f_l, scale, True)
+    qg, kg, vg, dog = (t.cuda()[..., :d] for t in (qf, kf, vf, dof))
+    sentinel = 7.0
+    outf = torch.full((b, sq, h, d + pad), sentinel, dtype=dt, device="cuda")
+    out, lse, _, _ = ext.fwd(qg, kg, vg, outf[..., :d], None, 0.0, scale, True, -1, -1, 0.0, False, None)
+    torch.cuda.synchronize()
+    assert capi.last_kernel() == "sm100_tcgen05_2q"
+    assert (outf[..., d:] == sentinel).all()
+    assert_within("out", out.cpu(), lp_o, f_o)
+    grads = [torch.full((b, n, heads, d + pad), sentinel, dtype=dt, device="cuda") for n, heads in ((sq, h), (sk, hkv), (sk, hkv))]
+    ext.bwd(dog, qg, kg, vg, out, lse, grads[0][..., :d], grads[1][..., :d], grads[2][..., :d], None, 0.0, scale, True, -1, -1, 0.0,
+            False, None, None)
+    torch.cuda.synchronize()
+    assert capi.last_kernel().startswith("sm100_tcgen05_bwd")
+    assert capi.lib.fa_debug_get(2) == 0
+    for name, g, a, b_ in zip(("dq", "dk", "dv"), grads, lp, f32):
+        assert (g[..., d:] == sentinel).all(), name
+        assert_within(name, g[..., :d].cpu(), a, b_, roundings=3)
