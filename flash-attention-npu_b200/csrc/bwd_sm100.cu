@@ -402,7 +402,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
 // ------------------------------------------------------------------------------------------------------
 // dQ
 // ------------------------------------------------------------------------------------------------------
-template <typename T, int D>
+template <typename T, int D, bool BIAS>
 __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_constant__ Sm100BwdArgs a) {
     using L = BwdSm100Smem<D>;
     constexpr int NSUB = D / 64, KSTEPS = D / 16;
@@ -557,6 +557,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
             dl = a.delta[((a.cu_q ? tok : (int64_t)b * a.sq + qi)) * a.hq + h];
         }
         const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dl, -dl);
+        const float slope = (BIAS && a.alibi) ? a.alibi[(int64_t)b * a.alibi_sb + h] * kLog2e : 0.f;
         bool ok = true;
         uint32_t pr[32];                                     // P of the tile in flight (fp32 bits)
         // phase A: P = exp2(S * c - LSE) of tile t into registers
@@ -573,15 +574,32 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
             const bool inside = __all_sync(0xffffffffu, c0 >= klo && c0 + 31 <= khi);
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                const float2 x = fma2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), sc2, nl2);
+                float2 x;
+                float f0 = 1.f, f1 = 1.f;                     // d(capped score) / d(scaled score)
+                if constexpr (BIAS) {
+                    // scores -> their final log2-domain values as in the forward: softcap, then the alibi bias
+                    float v0 = __uint_as_float(pr[i]), v1 = __uint_as_float(pr[i + 1]);
+                    if (a.softcap > 0.f) {
+                        const float t0 = 1.f - __fdividef(2.f, 1.f + ex2_approx(v0 * a.cap_in2));
+                        const float t1 = 1.f - __fdividef(2.f, 1.f + ex2_approx(v1 * a.cap_in2));
+                        v0 = a.cap_out * t0; v1 = a.cap_out * t1;
+                        f0 = 1.f - t0 * t0; f1 = 1.f - t1 * t1;
+                    } else {
+                        v0 *= a.scale_log2; v1 *= a.scale_log2;
+                    }
+                    const float rel = (float)(qi + sk - sq - (c0 + i));
+                    x = make_float2(v0 - slope * fabsf(rel) - lse2, v1 - slope * fabsf(rel - 1.f) - lse2);
+                } else {
+                    x = fma2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), sc2, nl2);
+                }
                 float2 p = make_float2(ex2_approx(x.x), ex2_approx(x.y));
                 if (!inside) {
                     const int col = c0 + i;
                     p.x = (col >= klo && col <= khi) ? p.x : 0.f;
                     p.y = (col + 1 >= klo && col + 1 <= khi) ? p.y : 0.f;
                 }
-                pr[i] = __float_as_uint(p.x);
-                pr[i + 1] = __float_as_uint(p.y);
+                pr[i] = __float_as_uint(p.x * f0);          // kept for phase B: P times the softcap derivative
+                pr[i + 1] = __float_as_uint(p.y * f1);
             }
         };
         phase_a(0);
@@ -818,8 +836,7 @@ static size_t ds_tiles_bytes(const fa_bwd_params& p);
 bool bwd_sm100_supported(const fa_bwd_params& p) {
     if (p.d != p.dv_dim || p.d % 8 != 0 || p.d <= 0 || p.d > 128) return false;       // any head dim up to 128: padded to 64 / 128
     if (!(p.scale > 0.f)) return false;
-    // softcap and alibi live in the dK/dV kernel only: such calls need the five-GEMM path (dense, dS tiles in the workspace)
-    if ((p.softcap > 0.f || p.alibi_slopes) && !(g_ds_spill && ds_tiles_bytes(p) > 0)) return false;
+
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
     if (p.sq <= 0 || p.sk <= 0) return false;
     if (p.cu_seqlens_q && (p.total_q <= 0 || p.total_k <= 0)) return false;
@@ -858,7 +875,7 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
     mark_kernel(st);
     const bool bias = p.softcap > 0.f || p.alibi_slopes;
     auto k1 = bias ? bwd_dkdv_sm100_kernel<T, D, true> : bwd_dkdv_sm100_kernel<T, D, false>;
-    auto k2 = bwd_dq_sm100_kernel<T, D>;
+    auto k2 = bias ? bwd_dq_sm100_kernel<T, D, true> : bwd_dq_sm100_kernel<T, D, false>;
     const int smem = BwdSm100Smem<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
     if (a.ds_tiles) {
@@ -873,7 +890,6 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
         mark_kernel(st);
         return cuda_ok(cudaGetLastError(), "bwd_sm100 launch");
     }
-    if (bias) return fail(FA_ERR_WORKSPACE, "softcap / alibi in the backward need the workspace fa_bwd_workspace_bytes() asks for");
     const int smem_dq = 7 * BwdSm100Smem<D>::kTileB + 256 + 1024;     // Q, dO, three K stages, two V stages, barriers
     if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq), "cudaFuncSetAttribute")) return e;
     dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g2((p.sq + 127) / 128, p.hq, p.b);

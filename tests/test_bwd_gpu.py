@@ -229,3 +229,58 @@ def test_any_head_dim_runs_on_the_tcgen05_kernels(d):
     for name, g, a, b_ in zip(("dq", "dk", "dv"), grads, lp, f32):
         assert (g[..., d:] == sentinel).all(), name
         assert_within(name, g[..., :d].cpu(), a, b_, roundings=3)
+
+
+def test_softcap_backward_of_packed_sequences_on_tcgen05():
+    """Packed (varlen) backward with softcap: the dQ kernel that recomputes S and dP caps the scores itself, so packed
+    calls stay on the tcgen05 kernels too.  Ragged sequences including an empty one, GQA, causal."""
+    import fa_b200_capi as capi
+    from flash_attn_npu import flash_attn_npu as ext
+    torch.manual_seed(77)
+    lq, lk, h, hkv, d, dt, cap = [300, 0, 129, 77], [300, 64, 400, 77], 4, 2, 128, torch.bfloat16, 3.0
+    q, do = (torch.randn(sum(lq), h, d) * 2).to(dt), torch.randn(sum(lq), h, d).to(dt)
+    k, v = torch.randn(sum(lk), hkv, d).to(dt), torch.randn(sum(lk), hkv, d).to(dt)
+    cu_q = torch.tensor([0] + torch.tensor(lq).cumsum(0).tolist(), dtype=torch.int32)
+    cu_k = torch.tensor([0] + torch.tensor(lk).cumsum(0).tolist(), dtype=torch.int32)
+    scale = d ** -0.5
+    _, lse32 = orc.attention_varlen_fwd(q.float(), k.float(), v.float(), cu_q, cu_k, scale, True, (-1, -1), cap, data_type=torch.float32)
+    lp = orc.attention_varlen_bwd(q, k, v, do, lse32, cu_q, cu_k, scale, True, (-1, -1), cap)
+    f32 = orc.attention_varlen_bwd(q.float(), k.float(), v.float(), do.float(), lse32, cu_q, cu_k, scale, True, (-1, -1), cap)
+    qg, kg, vg, dog = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse, _, _ = ext.varlen_fwd(qg, kg, vg, None, cu_q.cuda(), cu_k.cuda(), None, None, None, None, max(lq), max(lk), 0.0, scale,
+                                    False, True, -1, -1, cap, False, None)
+    dq, dk, dv = torch.empty_like(qg), torch.empty_like(kg), torch.empty_like(vg)
+    ext.varlen_bwd(dog, qg, kg, vg, out, lse, dq, dk, dv, cu_q.cuda(), cu_k.cuda(), None, max(lq), max(lk), 0.0, scale, False, True,
+                   -1, -1, cap, False, None, None)
+    torch.cuda.synchronize()
+    assert capi.last_kernel() == "sm100_tcgen05_bwd"
+    assert capi.lib.fa_debug_get(2) == 0
+    for name, got, a, b_ in zip(("dq", "dk", "dv"), (dq, dk, dv), lp, f32):
+        assert_within(name, got.cpu(), a, b_, roundings=3)
+
+
+def test_alibi_backward_without_the_ds_workspace():
+    """The same dense alibi + softcap backward with the dS hand-off switched off: the recomputing dQ kernel applies cap
+    and bias itself and gives the gradients of the five-GEMM path within rounding."""
+    import fa_b200_capi as capi
+    from flash_attn_npu import flash_attn_npu as ext
+    torch.manual_seed(3)
+    b, sq, sk, h, hkv, d, cap = 2, 200, 264, 4, 2, 128, 4.0
+    q, do = torch.randn(b, sq, h, d).bfloat16().cuda(), torch.randn(b, sq, h, d).bfloat16().cuda()
+    k, v = torch.randn(b, sk, hkv, d).bfloat16().cuda(), torch.randn(b, sk, hkv, d).bfloat16().cuda()
+    slopes = (torch.rand(b, h) * 0.3).cuda()
+    scale = d ** -0.5
+    out, lse, _, _ = ext.fwd(q, k, v, None, slopes, 0.0, scale, True, -1, -1, cap, False, None)
+    res = []
+    for spill in (1, 0):
+        capi.lib.fa_debug_set(7, spill)
+        try:
+            g = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+            ext.bwd(do, q, k, v, out, lse, g[0], g[1], g[2], slopes, 0.0, scale, True, -1, -1, cap, False, None, None)
+            torch.cuda.synchronize()
+            assert capi.last_kernel() == ("sm100_tcgen05_bwd_5gemm" if spill else "sm100_tcgen05_bwd")
+            res.append(g)
+        finally:
+            capi.lib.fa_debug_set(7, 1)
+    for name, x, y in zip(("dq", "dk", "dv"), res[0], res[1]):
+        assert (x.float() - y.float()).abs().max().item() <= 2.0 ** -7 * max(1.0, x.float().abs().max().item()), name
