@@ -52,6 +52,7 @@ struct alignas(64) Sm100BwdArgs {
     const int32_t* cu_q;
     const int32_t* cu_k;
     int b, sq, sk, hq, hkv;
+    int lpt;                            // grid order: 1 = (head, batch entry, block), the launch's heaviest blocks first
     int d;                              // the call's head dim (a multiple of 8, at most the kernels' 64 / 128): tile copies zero-fill
                                         // the columns past it, the epilogues store d columns
     float scale, scale_log2;
@@ -124,7 +125,12 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z, hk = blockIdx.y, n0 = blockIdx.x * 128;
+    // Grid order.  lpt = 0: (key block, KV head, batch entry): the key blocks of a head run together and share its Q and
+    // dO in L2.  lpt = 1, for launches whose Q and dO all fit in L2 anyway: (KV head, batch entry, key block): the
+    // blocks with the most query blocks to walk (the first ones under a causal mask) of EVERY head start before any
+    // light one, which is what a launch of only a few waves needs.
+    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
+    const int b = bi.z, hk = bi.y, n0 = bi.x * 128;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
     if (n0 >= sk) return;
@@ -365,7 +371,7 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
             if (a.ds_tiles) {
                 // the same rounded dS^T goes to global memory for the dQ kernel, which then needs one GEMM a tile
                 // instead of recomputing S and dP.  Issued after the hand-off so that the stores are off the chain.
-                const int64_t tile = (((int64_t)b * a.hq + (hk * G + s / nmb)) * a.nkb + blockIdx.x) * a.nqb + (mb_lo + s % nmb);
+                const int64_t tile = (((int64_t)b * a.hq + (hk * G + s / nmb)) * a.nkb + bi.x) * a.nqb + (mb_lo + s % nmb);
                 // tile layout [16 chunks of 8 queries][128 keys][16 bytes]: a warp's 32 rows of one chunk are 512
                 // contiguous bytes (one fully coalesced store instruction), and the tile is at the same time the
                 // unswizzled operand layout the dQ kernel's MMA reads
@@ -426,8 +432,9 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int mblk = gridDim.x - 1 - blockIdx.x;
+    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
+    const int b = bi.z, h = bi.y;                            // grid order as in the dK/dV kernel
+    const int mblk = (a.lpt ? gridDim.z : gridDim.x) - 1 - bi.x;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
     const int m0 = mblk * 128;
@@ -674,8 +681,9 @@ __global__ void __launch_bounds__(192, 1) bwd_dq_from_ds_sm100_kernel(const __gr
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int mblk = gridDim.x - 1 - blockIdx.x;
+    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
+    const int b = bi.z, h = bi.y;                            // grid order as in the dK/dV kernel
+    const int mblk = (a.lpt ? gridDim.z : gridDim.x) - 1 - bi.x;
     const int sq = a.sq, sk = a.sk;
     const int m0 = mblk * 128;
     if (m0 >= sq) return;
@@ -883,7 +891,8 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
         auto k3 = bwd_dq_from_ds_sm100_kernel<T, D>;
         const int smem3 = 3 * (2 * BwdSm100Smem<D>::kSub + BwdSm100Smem<D>::kTileB) + 256 + 1024;
         if (int e = cuda_ok(cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, smem3), "cudaFuncSetAttribute")) return e;
-        dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g3((p.sq + 127) / 128, p.hq, p.b);
+        const unsigned nk = (unsigned)((p.sk + 127) / 128), nq = (unsigned)((p.sq + 127) / 128);
+        dim3 g1 = a.lpt ? dim3(p.hkv, p.b, nk) : dim3(nk, p.hkv, p.b), g3 = a.lpt ? dim3(p.hq, p.b, nq) : dim3(nq, p.hq, p.b);
         k1<<<g1, 608, smem, st>>>(a);
         mark_kernel(st);
         k3<<<g3, 192, smem3, st>>>(a);
@@ -892,7 +901,8 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
     }
     const int smem_dq = 7 * BwdSm100Smem<D>::kTileB + 256 + 1024;     // Q, dO, three K stages, two V stages, barriers
     if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq), "cudaFuncSetAttribute")) return e;
-    dim3 g1((p.sk + 127) / 128, p.hkv, p.b), g2((p.sq + 127) / 128, p.hq, p.b);
+    const unsigned nk = (unsigned)((p.sk + 127) / 128), nq = (unsigned)((p.sq + 127) / 128);
+    dim3 g1 = a.lpt ? dim3(p.hkv, p.b, nk) : dim3(nk, p.hkv, p.b), g2 = a.lpt ? dim3(p.hq, p.b, nq) : dim3(nq, p.hq, p.b);
     // packed calls and calls beyond the workspace limit: the dQ kernel recomputes S and dP; both kernels on the
     // caller's stream, one after the other
     k1<<<g1, 608, smem, st>>>(a);
@@ -924,6 +934,9 @@ int launch_bwd_sm100(const fa_bwd_params& p) {
     }
     a.cu_q = p.cu_seqlens_q; a.cu_k = p.cu_seqlens_k;
     a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv; a.d = p.d;
+    // all of Q and dO within half of L2, and grid extents inside the y / z limits: heaviest blocks of the launch first
+    a.lpt = ((int64_t)p.b * p.hq * p.sq * p.d * 4 <= (48ll << 20) && p.b <= 65535 && (p.sk + 127) / 128 <= 65535 &&
+             (p.sq + 127) / 128 <= 65535) ? 1 : 0;
     a.scale = p.scale; a.scale_log2 = p.scale * kLog2e;
     a.softcap = p.softcap; a.cap_in2 = p.softcap > 0.f ? 2.f * kLog2e * p.scale / p.softcap : 0.f; a.cap_out = p.softcap * kLog2e;
     a.alibi = p.alibi_slopes; a.alibi_sb = p.alibi_stride_b;

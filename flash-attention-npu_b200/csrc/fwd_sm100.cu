@@ -46,6 +46,7 @@ struct alignas(64) Sm100FwdArgs {
     float* o_part;                       // (nsplit, rows_all, D), rows_all = batch * sq * hq, row = (b * sq + qpos) * hq + head
     float* lse_part;                     // (nsplit, rows_all)
     int64_t rows_all;
+    int lpt;                             // grid order, see the kernels
 };
 
 // =================================================================================================
@@ -98,17 +99,24 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z;
-    // Tile rows.  gq = 1: 128 consecutive query positions of head blockIdx.y.  gq = G (short queries under a query
-    // group of G, a power of two up to 128): the G heads of KV head blockIdx.y are stacked, row t of a tile is query
+    // Grid order.  CTAs are dispatched in the order of their linear index.  lpt = 0: (query block x split, head, batch
+    // entry) — the query blocks of one head run together and share its K and V in L2, last block (the one with the
+    // most key tiles under a causal mask) first.  lpt = 1, for launches whose K and V all fit in L2 anyway: (head, batch
+    // entry, query block x split) — the heavy blocks of EVERY head start before any light one (longest job first over
+    // the whole launch), which is what a launch of only a few waves needs.
+    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
+    const int nbx = a.lpt ? gridDim.z : gridDim.x;          // bi = (query block x split, head, batch entry)
+    const int b = bi.z;
+    // Tile rows.  gq = 1: 128 consecutive query positions of one head.  gq = G (short queries under a query
+    // group of G, a power of two up to 128): the G heads of one KV head are stacked, row t of a tile is query
     // position t / G of head t % G — the tile copy delivers exactly that order from a (dims, G heads, 128 / G rows)
     // box — so that a short chunk fills the 128-row tiles instead of one tile per head with few rows in it.
     const int gq = a.gq;
     const int qpt = 128 / gq;                                // query positions of one 128-row tile
-    const int hk = gq > 1 ? (int)blockIdx.y : (int)blockIdx.y / (a.hq / a.hkv);
-    const int h0 = gq > 1 ? hk * gq : (int)blockIdx.y;       // head of tile row 0
-    const int split = blockIdx.x % a.nsplit;
-    const int mblk = gridDim.x / a.nsplit - 1 - blockIdx.x / a.nsplit;
+    const int hk = gq > 1 ? (int)bi.y : (int)bi.y / (a.hq / a.hkv);
+    const int h0 = gq > 1 ? hk * gq : (int)bi.y;             // head of tile row 0
+    const int split = bi.x % a.nsplit;
+    const int mblk = nbx / a.nsplit - 1 - bi.x / a.nsplit;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
     if (a.seqused_k) {                                       // cache call: the length lives on the device
@@ -533,8 +541,9 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel_wide(const __grid_con
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int mblk = gridDim.x - 1 - blockIdx.x;
+    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
+    const int b = bi.z, h = bi.y;                            // grid order as in the two-tile kernel
+    const int mblk = (a.lpt ? gridDim.z : gridDim.x) - 1 - bi.x;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
     if (a.seqused_k) sk = (int)max(0LL, min((long long)a.seqused_k[b] + a.s_new, (long long)a.sk));
@@ -928,7 +937,8 @@ static int launch_sm100_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
     const int smem = FwdSm100Smem2<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
     const int qpc = 256 / a.gq;                              // query positions of a CTA
-    dim3 grid(((p.sq + qpc - 1) / qpc) * a.nsplit, a.gq > 1 ? p.hkv : p.hq, p.b);
+    const unsigned nbx = (unsigned)(((p.sq + qpc - 1) / qpc) * a.nsplit), nhy = (unsigned)(a.gq > 1 ? p.hkv : p.hq);
+    dim3 grid = a.lpt ? dim3(nhy, p.b, nbx) : dim3(nbx, nhy, p.b);
     kern<<<grid, 384, smem, st>>>(a);
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
@@ -943,7 +953,7 @@ static int launch_sm100_wide_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
     auto kern = fwd_sm100_kernel_wide<T, D, BIAS>;
     const int smem = FwdSm100SmemWide<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-    dim3 grid((p.sq + 127) / 128, p.hq, p.b);
+    dim3 grid = a.lpt ? dim3(p.hq, p.b, (p.sq + 127) / 128) : dim3((p.sq + 127) / 128, p.hq, p.b);
     kern<<<grid, 384, smem, st>>>(a);
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
@@ -970,6 +980,8 @@ int launch_fwd_sm100(const fa_fwd_params& p, int nsplit, int keys_per_split, flo
     a.kv_box = 128;
     a.nsplit = nsplit > 1 ? nsplit : 1; a.keys_per_split = keys_per_split; a.o_part = o_part; a.lse_part = lse_part;
     a.rows_all = (int64_t)p.b * p.sq * p.hq;
+    // all of K and V within half of L2, and grid extents that fit the y / z limits: heaviest blocks of the launch first
+    a.lpt = ((int64_t)p.b * p.hkv * p.sk * p.d * 4 <= (48ll << 20) && p.b <= 65535 && (int64_t)((p.sq + 127) / 128) * a.nsplit <= 65535) ? 1 : 0;
     const bool packed = p.cu_seqlens_q != nullptr;
     const int64_t q_rows = packed ? p.total_q : p.sq;
     const int64_t k_rows = packed ? p.total_k : p.sk;
