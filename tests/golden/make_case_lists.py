@@ -53,7 +53,9 @@ def extract(path):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_case_lists.py <checkout of the reference project>")
+    ref = sys.argv[1]
     out = {}
     for name in FILES:
         out[name[:-3]] = extract(os.path.join(ref, "tests", name))
