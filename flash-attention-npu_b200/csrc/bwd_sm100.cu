@@ -52,7 +52,7 @@ struct alignas(64) Sm100BwdArgs {
     const int32_t* cu_q;
     const int32_t* cu_k;
     int b, sq, sk, hq, hkv;
-    int lpt;                            // grid order: 1 = (head, batch entry, block), the launch's heaviest blocks first
+    int chunk_kv, chunk_q;              // grid order: (batch entry, KV head) pairs a chunk of the dK/dV grid, (batch entry, head) pairs of the dQ grids
     int d;                              // the call's head dim (a multiple of 8, at most the kernels' 64 / 128): tile copies zero-fill
                                         // the columns past it, the epilogues store d columns
     float scale, scale_log2;
@@ -125,11 +125,12 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // Grid order.  lpt = 0: (key block, KV head, batch entry): the key blocks of a head run together and share its Q and
-    // dO in L2.  lpt = 1, for launches whose Q and dO all fit in L2 anyway: (KV head, batch entry, key block): the
-    // blocks with the most query blocks to walk (the first ones under a causal mask) of EVERY head start before any
-    // light one, which is what a launch of only a few waves needs.
-    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
+    // Grid order: (pair in chunk, key block, chunk) over chunks of (batch entry, KV head) pairs, as in the forward: inside
+    // a chunk the key blocks with the most query blocks to walk (the first ones under a causal mask) of ALL its pairs
+    // start before any lighter one, and a chunk's Q and dO stay in L2 while its key blocks run.
+    const int pair = blockIdx.z * a.chunk_kv + blockIdx.x;
+    if (pair >= a.b * a.hkv) return;
+    const uint3 bi = make_uint3(blockIdx.y, pair % a.hkv, pair / a.hkv);     // (key block, KV head, batch entry)
     const int b = bi.z, hk = bi.y, n0 = bi.x * 128;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
@@ -432,9 +433,10 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
-    const int b = bi.z, h = bi.y;                            // grid order as in the dK/dV kernel
-    const int mblk = (a.lpt ? gridDim.z : gridDim.x) - 1 - bi.x;
+    const int pair = blockIdx.z * a.chunk_q + blockIdx.x;    // grid order as in the dK/dV kernel, over (batch entry, head) pairs
+    if (pair >= a.b * a.hq) return;
+    const int b = pair / a.hq, h = pair % a.hq;
+    const int mblk = gridDim.y - 1 - blockIdx.y;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
     const int m0 = mblk * 128;
@@ -681,9 +683,10 @@ __global__ void __launch_bounds__(192, 1) bwd_dq_from_ds_sm100_kernel(const __gr
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
-    const int b = bi.z, h = bi.y;                            // grid order as in the dK/dV kernel
-    const int mblk = (a.lpt ? gridDim.z : gridDim.x) - 1 - bi.x;
+    const int pair = blockIdx.z * a.chunk_q + blockIdx.x;    // grid order as in the dK/dV kernel, over (batch entry, head) pairs
+    if (pair >= a.b * a.hq) return;
+    const int b = pair / a.hq, h = pair % a.hq;
+    const int mblk = gridDim.y - 1 - blockIdx.y;
     const int sq = a.sq, sk = a.sk;
     const int m0 = mblk * 128;
     if (m0 >= sq) return;
@@ -843,6 +846,7 @@ static size_t ds_tiles_bytes(const fa_bwd_params& p);
 
 bool bwd_sm100_supported(const fa_bwd_params& p) {
     if (p.d != p.dv_dim || p.d % 8 != 0 || p.d <= 0 || p.d > 128) return false;       // any head dim up to 128: padded to 64 / 128
+    if ((p.sq + 127) / 128 > 65535 || (p.sk + 127) / 128 > 65535) return false;       // blocks stay inside a grid dimension
     if (!(p.scale > 0.f)) return false;
 
     if ((p.cu_seqlens_q != nullptr) != (p.cu_seqlens_k != nullptr)) return false;
@@ -892,7 +896,8 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
         const int smem3 = 3 * (2 * BwdSm100Smem<D>::kSub + BwdSm100Smem<D>::kTileB) + 256 + 1024;
         if (int e = cuda_ok(cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, smem3), "cudaFuncSetAttribute")) return e;
         const unsigned nk = (unsigned)((p.sk + 127) / 128), nq = (unsigned)((p.sq + 127) / 128);
-        dim3 g1 = a.lpt ? dim3(p.hkv, p.b, nk) : dim3(nk, p.hkv, p.b), g3 = a.lpt ? dim3(p.hq, p.b, nq) : dim3(nq, p.hq, p.b);
+        dim3 g1(a.chunk_kv, nk, (unsigned)(((int64_t)p.b * p.hkv + a.chunk_kv - 1) / a.chunk_kv));
+        dim3 g3(a.chunk_q, nq, (unsigned)(((int64_t)p.b * p.hq + a.chunk_q - 1) / a.chunk_q));
         k1<<<g1, 608, smem, st>>>(a);
         mark_kernel(st);
         k3<<<g3, 192, smem3, st>>>(a);
@@ -902,7 +907,8 @@ static int launch_bwd_sm100_t(const fa_bwd_params& p, Sm100BwdArgs& a, float* de
     const int smem_dq = 7 * BwdSm100Smem<D>::kTileB + 256 + 1024;     // Q, dO, three K stages, two V stages, barriers
     if (int e = cuda_ok(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq), "cudaFuncSetAttribute")) return e;
     const unsigned nk = (unsigned)((p.sk + 127) / 128), nq = (unsigned)((p.sq + 127) / 128);
-    dim3 g1 = a.lpt ? dim3(p.hkv, p.b, nk) : dim3(nk, p.hkv, p.b), g2 = a.lpt ? dim3(p.hq, p.b, nq) : dim3(nq, p.hq, p.b);
+    dim3 g1(a.chunk_kv, nk, (unsigned)(((int64_t)p.b * p.hkv + a.chunk_kv - 1) / a.chunk_kv));
+    dim3 g2(a.chunk_q, nq, (unsigned)(((int64_t)p.b * p.hq + a.chunk_q - 1) / a.chunk_q));
     // packed calls and calls beyond the workspace limit: the dQ kernel recomputes S and dP; both kernels on the
     // caller's stream, one after the other
     k1<<<g1, 608, smem, st>>>(a);
@@ -934,9 +940,9 @@ int launch_bwd_sm100(const fa_bwd_params& p) {
     }
     a.cu_q = p.cu_seqlens_q; a.cu_k = p.cu_seqlens_k;
     a.b = p.b; a.sq = p.sq; a.sk = p.sk; a.hq = p.hq; a.hkv = p.hkv; a.d = p.d;
-    // all of Q and dO within half of L2, and grid extents inside the y / z limits: heaviest blocks of the launch first
-    a.lpt = ((int64_t)p.b * p.hq * p.sq * p.d * 4 <= (48ll << 20) && p.b <= 65535 && (p.sk + 127) / 128 <= 65535 &&
-             (p.sq + 127) / 128 <= 65535) ? 1 : 0;
+    // a dK/dV chunk streams the Q and dO of its pairs' query groups, a dQ chunk the K (and V) of its pairs
+    a.chunk_kv = grid_chunk((int64_t)p.b * p.hkv, (int64_t)(p.hq / p.hkv) * p.sq * p.d * 4);
+    a.chunk_q = grid_chunk((int64_t)p.b * p.hq, (int64_t)p.sk * p.d * 4);
     a.scale = p.scale; a.scale_log2 = p.scale * kLog2e;
     a.softcap = p.softcap; a.cap_in2 = p.softcap > 0.f ? 2.f * kLog2e * p.scale / p.softcap : 0.f; a.cap_out = p.softcap * kLog2e;
     a.alibi = p.alibi_slopes; a.alibi_sb = p.alibi_stride_b;

@@ -46,7 +46,7 @@ struct alignas(64) Sm100FwdArgs {
     float* o_part;                       // (nsplit, rows_all, D), rows_all = batch * sq * hq, row = (b * sq + qpos) * hq + head
     float* lse_part;                     // (nsplit, rows_all)
     int64_t rows_all;
-    int lpt;                             // grid order, see the kernels
+    int chunk, nheads_grid;              // grid order, see the kernels: (batch entry, head) pairs a chunk; heads of the grid
 };
 
 // =================================================================================================
@@ -99,13 +99,17 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // Grid order.  CTAs are dispatched in the order of their linear index.  lpt = 0: (query block x split, head, batch
-    // entry) — the query blocks of one head run together and share its K and V in L2, last block (the one with the
-    // most key tiles under a causal mask) first.  lpt = 1, for launches whose K and V all fit in L2 anyway: (head, batch
-    // entry, query block x split) — the heavy blocks of EVERY head start before any light one (longest job first over
-    // the whole launch), which is what a launch of only a few waves needs.
-    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
-    const int nbx = a.lpt ? gridDim.z : gridDim.x;          // bi = (query block x split, head, batch entry)
+    // Grid order.  CTAs are dispatched in the order of their linear index, and under a causal mask the last query block
+    // of a head has the most key tiles.  The grid is (pair in chunk, query block x split, chunk) over chunks of `chunk`
+    // (batch entry, head) pairs: inside a chunk the heaviest blocks of ALL its pairs start before any lighter one
+    // (longest job first; with one head after the other the last head's heavy blocks would start when the launch is
+    // almost over: 7 % of a forward of 2048 CTAs by list-scheduling arithmetic), and a chunk is small enough for the K
+    // and V of its pairs to stay in L2 while its query blocks run (a launch in longest-first order over everything
+    // lost 20 % at 128 pairs of 2 MiB).  Pairs past the end of the last chunk leave.
+    const int pair = blockIdx.z * a.chunk + blockIdx.x;
+    if (pair >= a.b * a.nheads_grid) return;
+    const uint3 bi = make_uint3(blockIdx.y, pair % a.nheads_grid, pair / a.nheads_grid);   // (query block x split, head, batch entry)
+    const int nbx = gridDim.y;
     const int b = bi.z;
     // Tile rows.  gq = 1: 128 consecutive query positions of one head.  gq = G (short queries under a query
     // group of G, a power of two up to 128): the G heads of one KV head are stacked, row t of a tile is query
@@ -541,9 +545,10 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel_wide(const __grid_con
     auto bar = [&](int i) { return bars + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint3 bi = a.lpt ? make_uint3(blockIdx.z, blockIdx.x, blockIdx.y) : make_uint3(blockIdx.x, blockIdx.y, blockIdx.z);
-    const int b = bi.z, h = bi.y;                            // grid order as in the two-tile kernel
-    const int mblk = (a.lpt ? gridDim.z : gridDim.x) - 1 - bi.x;
+    const int pair = blockIdx.z * a.chunk + blockIdx.x;      // grid order as in the two-tile kernel
+    if (pair >= a.b * a.nheads_grid) return;
+    const int b = pair / a.nheads_grid, h = pair % a.nheads_grid;
+    const int mblk = gridDim.y - 1 - blockIdx.y;
     int q_off = 0, k_off = 0, sq = a.sq, sk = a.sk;
     if (a.cu_q) { q_off = a.cu_q[b]; sq = a.cu_q[b + 1] - q_off; k_off = a.cu_k[b]; sk = a.cu_k[b + 1] - k_off; }
     if (a.seqused_k) sk = (int)max(0LL, min((long long)a.seqused_k[b] + a.s_new, (long long)a.sk));
@@ -901,6 +906,7 @@ int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads
 
 bool fwd_sm100_supported(const fa_fwd_params& p) {
     if (p.d != p.dv || p.d % 8 != 0 || p.d <= 0 || p.d > 256) return false;      // any head dim: the kernels pad it to 64 / 128 / 192 / 256
+    if ((p.sq + 127) / 128 > 8192) return false;                                 // query blocks x splits stay inside a grid dimension
     const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
     if (cache) {
         // KV-cache calls (prefill against a cache): lengths and pages are read on the device
@@ -930,6 +936,16 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
     return encode_fn() != nullptr;
 }
 
+// (batch entry, head) pairs of one chunk of the grid: the largest power of two whose streamed operands (bytes_per_pair
+// each) stay within 16 MiB, the whole launch if it is smaller than that
+int grid_chunk(int64_t pairs, int64_t bytes_per_pair) {
+    int64_t c = 1;
+    const int64_t cap = 16ll << 20;          // measured 4-192 MiB at configuration 2 and at an eighth of it: flat up to 48, worse above
+    while (c * 2 <= pairs && c * 2 * bytes_per_pair <= cap && c * 2 <= 1024) c *= 2;
+    if (pairs * bytes_per_pair <= cap && pairs <= 1024) c = pairs;
+    return (int)(c < 1 ? 1 : c);
+}
+
 template <typename T, int D, bool BIAS>
 static int launch_sm100_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(p.stream);
@@ -937,8 +953,10 @@ static int launch_sm100_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
     const int smem = FwdSm100Smem2<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
     const int qpc = 256 / a.gq;                              // query positions of a CTA
-    const unsigned nbx = (unsigned)(((p.sq + qpc - 1) / qpc) * a.nsplit), nhy = (unsigned)(a.gq > 1 ? p.hkv : p.hq);
-    dim3 grid = a.lpt ? dim3(nhy, p.b, nbx) : dim3(nbx, nhy, p.b);
+    const unsigned nbx = (unsigned)(((p.sq + qpc - 1) / qpc) * a.nsplit);
+    a.nheads_grid = a.gq > 1 ? p.hkv : p.hq;
+    a.chunk = grid_chunk((int64_t)p.b * a.nheads_grid, (int64_t)p.sk * p.d * 4);
+    dim3 grid(a.chunk, nbx, (unsigned)(((int64_t)p.b * a.nheads_grid + a.chunk - 1) / a.chunk));
     kern<<<grid, 384, smem, st>>>(a);
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
@@ -953,7 +971,9 @@ static int launch_sm100_wide_b(const fa_fwd_params& p, Sm100FwdArgs& a) {
     auto kern = fwd_sm100_kernel_wide<T, D, BIAS>;
     const int smem = FwdSm100SmemWide<D>::kBytes + 1024;
     if (int e = cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute")) return e;
-    dim3 grid = a.lpt ? dim3(p.hq, p.b, (p.sq + 127) / 128) : dim3((p.sq + 127) / 128, p.hq, p.b);
+    a.nheads_grid = p.hq;
+    a.chunk = grid_chunk((int64_t)p.b * p.hq, (int64_t)p.sk * p.d * 4);
+    dim3 grid(a.chunk, (p.sq + 127) / 128, (unsigned)(((int64_t)p.b * p.hq + a.chunk - 1) / a.chunk));
     kern<<<grid, 384, smem, st>>>(a);
     mark_kernel(st);
     return cuda_ok(cudaGetLastError(), "fwd_sm100 launch");
@@ -980,8 +1000,6 @@ int launch_fwd_sm100(const fa_fwd_params& p, int nsplit, int keys_per_split, flo
     a.kv_box = 128;
     a.nsplit = nsplit > 1 ? nsplit : 1; a.keys_per_split = keys_per_split; a.o_part = o_part; a.lse_part = lse_part;
     a.rows_all = (int64_t)p.b * p.sq * p.hq;
-    // all of K and V within half of L2, and grid extents that fit the y / z limits: heaviest blocks of the launch first
-    a.lpt = ((int64_t)p.b * p.hkv * p.sk * p.d * 4 <= (48ll << 20) && p.b <= 65535 && (int64_t)((p.sq + 127) / 128) * a.nsplit <= 65535) ? 1 : 0;
     const bool packed = p.cu_seqlens_q != nullptr;
     const int64_t q_rows = packed ? p.total_q : p.sq;
     const int64_t k_rows = packed ? p.total_k : p.sk;

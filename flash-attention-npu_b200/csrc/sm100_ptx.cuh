@@ -497,6 +497,8 @@ __device__ __forceinline__ float2 ex2_poly2(float2 x) {
 int make_tile_map(CUtensorMap* map, int dtype, const void* ptr, int d, int heads, int64_t rows, int batch,
                   int64_t stride_h, int64_t stride_s, int64_t stride_b, int box_rows, int box_heads = 1);
 bool tensor_map_encoder_available();
+// (batch entry, head) pairs of one chunk of a tcgen05 kernel's grid (fwd_sm100.cu)
+int grid_chunk(int64_t pairs, int64_t bytes_per_pair);
 // code left by a timed-out wait in the backward kernels (bwd_sm100.cu); synchronises
 int bwd_sm100_error_flag(bool clear);
 
