@@ -76,7 +76,7 @@ struct FwdSm100Smem2 {
 #ifndef FA_FWD_POLY
 #define FA_FWD_POLY 2      // pairs of every 8 whose exponential runs on the FMA pipe
 #endif
-enum { C_Q = 0, C_KF0, C_KF1, C_KE0, C_KE1, C_VF0, C_VF1, C_VE0, C_VE1, C_SA, C_SB, C_PA, C_PB, C_PA2, C_PB2, C_OA, C_OB, C_COUNT };
+enum { C_Q = 0, C_KF0, C_KF1, C_KE0, C_KE1, C_VF0, C_VF1, C_VE0, C_VE1, C_SA, C_SB, C_PA, C_PB, C_PA2, C_PB2, C_OA, C_OB, C_DRAIN, C_COUNT };
 
 template <typename T, int D, bool BIAS>
 __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constant__ Sm100FwdArgs a) {
@@ -329,6 +329,15 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                 } else if (has_b) {
                     umma_commit_w(bar(C_OB));
                 }
+            }
+            // The release of the last K/V stage has no waiter, and with one query tile in use it is issued after the
+            // commit the epilogue waits for.  An arrive that the tensor core performs after the CTA has left would land
+            // in shared memory the CTA no longer owns (an illegal access when nothing else is resident: seen with a
+            // one-CTA launch, one key tile and 32 output columns, the shortest epilogue there is).  Commits complete in
+            // issue order, so the warp waits for a last one of its own before it leaves.
+            if (ok) {
+                umma_commit_w(bar(C_DRAIN));
+                ok = mbar_wait(bar(C_DRAIN), 0, abort_flag, err, 13);
             }
         }
     }
