@@ -1,6 +1,7 @@
-"""Random ragged shapes: the tcgen05 kernels against the general mma.sync kernels of the same library (both were
-checked against the oracle elsewhere; this sweep looks for shape-dependent slips: partial tiles, windows that cut
-tiles, grouped heads, packed batches with empty sequences)."""
+"""Random ragged shapes: the default routing (tcgen05 forward and backward, split-KV decode) against the general
+mma.sync kernels of the same library (both were checked against the oracle elsewhere; this sweep looks for
+shape-dependent slips: partial tiles, windows that cut tiles, grouped heads, packed batches with empty sequences,
+padded head dims, page sizes, appended chunks, forced split counts, one-CTA launches)."""
 import random
 
 import pytest
@@ -146,3 +147,194 @@ def test_forward_tile_ranges_of_the_two_query_halves(sq, sk, causal, wl, wr):
     assert torch.equal(l1[~fin], l2[~fin])
     if fin.any():
         assert (l1[fin] - l2[fin]).abs().max().item() <= 1e-4 * max(1.0, l2[fin].abs().max().item())
+
+
+def _cache_case(seed):
+    """One random KV-cache call: shapes, features and tensors from the seed."""
+    rnd = random.Random(seed)
+    d = rnd.choice([32, 64, 64, 72, 96, 128, 128, 128, 160, 192, 256])
+    hkv = rnd.choice([1, 2, 4])
+    grp = rnd.choice([1, 2, 3, 4, 6, 8, 16])
+    h = hkv * grp
+    b = rnd.randint(1, 5)
+    sq = rnd.choice([1, 1, 2, 3, 4, 4, 7, 8, 16, 17, 33, 64, 100, 130, 200, 300])
+    paged = rnd.random() < 0.6
+    page = rnd.choice([64, 128, 192, 256])
+    cap = rnd.choice([256, 512, 768, 1024, 2048, 4096, 8192])
+    if paged:
+        cap = (cap + page - 1) // page * page
+    append = rnd.random() < 0.5
+    hi = cap - sq if append else cap
+    if hi < 1:
+        return None
+    lens = [rnd.randint(0 if append else 1, hi) for _ in range(b)]
+    if rnd.random() < 0.3:
+        lens[0] = hi                                   # a sequence that fills the cache to its last row
+    if rnd.random() < 0.2 and not append:
+        lens[-1] = rnd.randint(1, min(hi, 40))         # one that is shorter than a tile (and than the chunk)
+    mode = rnd.choice(["full", "causal", "causal", "window"])
+    causal = mode == "causal"
+    wl, wr = (rnd.randint(0, 600), rnd.choice([0, rnd.randint(0, 100)])) if mode == "window" else (-1, -1)
+    softcap = rnd.choice([0.0, 0.0, 0.0, 20.0])
+    use_alibi = rnd.random() < 0.15
+    rotary = append and rnd.random() < 0.4 and d % 16 == 0
+    nsplit = rnd.choice([0, 0, 0, 1, 3])
+    dt = rnd.choice([torch.bfloat16, torch.bfloat16, torch.float16])
+    g = torch.Generator(device="cuda").manual_seed(5000 + seed)
+    c = {"q": torch.randn(b, sq, h, d, device="cuda", generator=g).to(dt), "table": None, "kn": None, "vn": None,
+         "cos": None, "sin": None, "alibi": None}
+    if paged:
+        nb = cap // page
+        pool = nb * b + 3
+        c["table"] = torch.randperm(pool, device="cuda", generator=g).int()[: nb * b].reshape(b, nb).contiguous()
+        c["kc"] = torch.randn(pool, page, hkv, d, device="cuda", generator=g).to(dt)
+        c["vc"] = torch.randn(pool, page, hkv, d, device="cuda", generator=g).to(dt)
+    else:
+        c["kc"] = torch.randn(b, cap, hkv, d, device="cuda", generator=g).to(dt)
+        c["vc"] = torch.randn(b, cap, hkv, d, device="cuda", generator=g).to(dt)
+    if append:
+        c["kn"] = torch.randn(b, sq, hkv, d, device="cuda", generator=g).to(dt)
+        c["vn"] = torch.randn(b, sq, hkv, d, device="cuda", generator=g).to(dt)
+    c["lens"] = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    if rotary:
+        rd = rnd.choice([d // 2, d]) // 16 * 16
+        ang = torch.rand(cap, rd // 2, device="cuda", generator=g) * 6.28
+        c["cos"], c["sin"] = ang.cos().to(dt), ang.sin().to(dt)
+    c["interleaved"] = rnd.random() < 0.5
+    if use_alibi:
+        c["alibi"] = (torch.rand(h, device="cuda", generator=g) * 0.3).float()
+    c.update(scale=d ** -0.5, causal=causal, wl=wl, wr=wr, softcap=softcap, nsplit=nsplit)
+    c["tag"] = (f"seed {seed}: b{b} sq{sq} h{h}/{hkv} d{d} capacity {cap} paged {paged} page {page} lens {lens} append {append} "
+                f"rotary {rotary} {mode} ({wl},{wr}) softcap {softcap} alibi {use_alibi} num_splits {nsplit} {dt}")
+    return c
+
+
+@pytest.mark.parametrize("block", range(12))
+def test_kvcache_calls_random(block):
+    """25 random flash_attn_with_kvcache calls a block (300 in all; head dims 32-256, query groups 1-16 including groups
+    that cannot be stacked, 1-300 new tokens, dense and paged caches with pages of 64-256 tokens, append, rotary, windows,
+    softcap, alibi, forced split counts): output, LSE and the cache after the call of the default routing against the
+    general kernels.  Among them are launches of a single CTA with one key tile and 32 output columns, the shortest
+    run the two-tile tcgen05 kernel can have (seed 200)."""
+    from flash_attn_npu import flash_attn_npu as ext
+    import fa_b200_capi as capi
+    bad, kernels = [], set()
+    for seed in range(block * 25, block * 25 + 25):
+        c = _cache_case(seed)
+        if c is None:
+            continue
+
+        def call():
+            k2, v2 = c["kc"].clone(), c["vc"].clone()
+            out, lse = ext.fwd_kvcache(c["q"], k2, v2, c["kn"], c["vn"], c["lens"], c["cos"], c["sin"], None, None, c["table"],
+                                       c["alibi"], None, c["scale"], c["causal"], c["wl"], c["wr"], c["softcap"],
+                                       c["interleaved"], c["nsplit"])
+            return out, lse, k2, v2
+
+        (o1, l1, k1, v1), n1 = _run(0, call)
+        (o2, l2, k2, v2), n2 = _run(1, call)
+        kernels.add(n1)
+        assert not n2.startswith(("sm100", "decode")), n2
+        assert capi.lib.fa_debug_get(2) == 0, c["tag"]
+        msgs = []
+        if not torch.equal(k1, k2) or not torch.equal(v1, v2):
+            msgs.append("cache differs")
+        a, r = o1.float(), o2.float()
+        if not torch.equal(torch.isnan(a), torch.isnan(r)):
+            msgs.append("nan pattern differs")
+        mag = max(1.0, r[torch.isfinite(r)].abs().max().item() if torch.isfinite(r).any() else 1.0)
+        err = (a - r).abs().nan_to_num(0).max().item()
+        if err > 4 * 2 ** -8 * mag:
+            msgs.append(f"out err {err:.4g} at magnitude {mag:.3g}")
+        fin = torch.isfinite(l2)
+        if not torch.equal(torch.isfinite(l1), fin):
+            msgs.append("lse finiteness differs")
+        elif fin.any() and (l1[fin] - l2[fin]).abs().max().item() > 1e-4 * max(1.0, l2[fin].abs().max().item()):
+            msgs.append(f"lse err {(l1[fin] - l2[fin]).abs().max().item():.3g}")
+        if msgs:
+            bad.append(f"{c['tag']} [{n1}]: " + "; ".join(msgs))
+    assert not bad, "\n".join(bad)
+    assert kernels, "no case in this block"
+
+
+@pytest.mark.parametrize("block", range(8))
+def test_dense_and_packed_calls_any_head_dim_random(block):
+    """25 random dense or packed forward + backward calls a block (200 in all): every head dim from 8 to 256 (padded by
+    the tile copies), softcap, alibi, windows, packed batches whose query and key lengths differ."""
+    from flash_attn_npu import flash_attn_npu as ext
+    import fa_b200_capi as capi
+    bad = []
+    for seed in range(block * 25, block * 25 + 25):
+        rnd = random.Random(seed)
+        d = rnd.choice([8, 16, 24, 40, 64, 64, 80, 96, 104, 128, 128, 136, 160, 192, 224, 256])
+        hkv = rnd.choice([1, 2, 3])
+        h = hkv * rnd.choice([1, 2, 4, 8])
+        packed = rnd.random() < 0.4
+        mode = rnd.choice(["full", "causal", "causal", "window"])
+        causal = mode == "causal"
+        wl, wr = (rnd.randint(0, 300), rnd.randint(0, 300)) if mode == "window" else (-1, -1)
+        softcap = rnd.choice([0.0, 0.0, 15.0])
+        use_alibi = rnd.random() < 0.25
+        dt = rnd.choice([torch.bfloat16, torch.float16])
+        g = torch.Generator(device="cuda").manual_seed(9000 + seed)
+        scale = d ** -0.5
+        alibi = (torch.rand(h, device="cuda", generator=g) * 0.3).float() if use_alibi else None
+        if packed:
+            n = rnd.randint(1, 6)
+            lq = [rnd.choice([0, 1, rnd.randint(2, 600)]) for _ in range(n)]
+            lk = lq if rnd.random() < 0.5 else [rnd.choice([0, 1, rnd.randint(2, 800)]) for _ in range(n)]
+            if sum(lq) == 0:
+                lq[0] = 50
+            if sum(lk) == 0:
+                lk = list(lk)
+                lk[0] = 60
+            cuq = torch.tensor([0] + list(torch.tensor(lq).cumsum(0)), dtype=torch.int32, device="cuda")
+            cuk = torch.tensor([0] + list(torch.tensor(lk).cumsum(0)), dtype=torch.int32, device="cuda")
+            q = torch.randn(sum(lq), h, d, device="cuda", generator=g).to(dt)
+            k = torch.randn(sum(lk), hkv, d, device="cuda", generator=g).to(dt)
+            v = torch.randn(sum(lk), hkv, d, device="cuda", generator=g).to(dt)
+            tag = f"seed {seed}: packed lq {lq} lk {lk} h{h}/{hkv} d{d} {mode} ({wl},{wr}) softcap {softcap} alibi {use_alibi} {dt}"
+        else:
+            b = rnd.randint(1, 3)
+            sq, sk = rnd.randint(1, 700), rnd.randint(1, 900)
+            q = torch.randn(b, sq, h, d, device="cuda", generator=g).to(dt)
+            k = torch.randn(b, sk, hkv, d, device="cuda", generator=g).to(dt)
+            v = torch.randn(b, sk, hkv, d, device="cuda", generator=g).to(dt)
+            tag = f"seed {seed}: dense b{b} sq{sq} sk{sk} h{h}/{hkv} d{d} {mode} ({wl},{wr}) softcap {softcap} alibi {use_alibi} {dt}"
+        do = torch.randn(q.shape, device="cuda", generator=g).to(dt)
+
+        def call():
+            if packed:
+                out, lse, _, _ = ext.varlen_fwd(q, k, v, None, cuq, cuk, None, None, None, alibi, max(lq), max(lk), 0.0, scale,
+                                                False, causal, wl, wr, softcap, False, None)
+            else:
+                out, lse, _, _ = ext.fwd(q, k, v, None, alibi, 0.0, scale, causal, wl, wr, softcap, False, None)
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            if packed:
+                ext.varlen_bwd(do, q, k, v, out, lse, dq, dk, dv, cuq, cuk, alibi, max(lq), max(lk), 0.0, scale, False, causal,
+                               wl, wr, softcap, False, None, None)
+            else:
+                ext.bwd(do, q, k, v, out, lse, dq, dk, dv, alibi, 0.0, scale, causal, wl, wr, softcap, False, None, None)
+            return out, lse, dq, dk, dv
+
+        (o1, l1, dq1, dk1, dv1), b1 = _run(0, call)
+        (o2, l2, dq2, dk2, dv2), b2 = _run(1, call)
+        assert b2 == "generic_mma_bwd", b2
+        assert b1.startswith("sm100_tcgen05_bwd") == (d <= 128), (tag, b1)
+        assert capi.lib.fa_debug_get(2) == 0, tag
+        msgs = []
+        for name, t1, t2 in (("out", o1, o2), ("dq", dq1, dq2), ("dk", dk1, dk2), ("dv", dv1, dv2)):
+            if torch.isnan(t1.float()).any():
+                msgs.append(name + " has nan")
+            try:
+                _close(t1, t2, name)
+            except AssertionError as e:
+                msgs.append(str(e))
+        fin = torch.isfinite(l2)
+        if not torch.equal(torch.isfinite(l1), fin):
+            msgs.append("lse finiteness differs")
+        elif fin.any() and (l1[fin] - l2[fin]).abs().max().item() > 1e-4 * max(1.0, l2[fin].abs().max().item()):
+            msgs.append("lse differs")
+        if msgs:
+            bad.append(tag + ": " + "; ".join(msgs))
+    assert not bad, "\n".join(bad)
