@@ -158,7 +158,8 @@ __global__ void __launch_bounds__(608, 1) bwd_dkdv_sm100_kernel(const __grid_con
             if (r < krows) {
                 const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-                for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(row)[c] = z;
+                for (int c = 0; c < D / 8; ++c)
+                if (c * 8 < a.d) reinterpret_cast<uint4*>(row)[c] = z;      // the call's head dim, not the kernel's padded one
             }
         }
         return;
@@ -459,7 +460,8 @@ __global__ void __launch_bounds__(608, 1) bwd_dq_sm100_kernel(const __grid_const
             const uint4 z = make_uint4(0, 0, 0, 0);
             T* row = dqb + (int64_t)tid * a.dq_ss;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(row)[c] = z;
+            for (int c = 0; c < D / 8; ++c)
+                if (c * 8 < a.d) reinterpret_cast<uint4*>(row)[c] = z;      // the call's head dim, not the kernel's padded one
         }
         return;
     }
@@ -712,7 +714,8 @@ __global__ void __launch_bounds__(192, 1) bwd_dq_from_ds_sm100_kernel(const __gr
             const uint4 z = make_uint4(0, 0, 0, 0);
             T* row = dqb + (int64_t)tid * a.dq_ss;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(row)[c] = z;
+            for (int c = 0; c < D / 8; ++c)
+                if (c * 8 < a.d) reinterpret_cast<uint4*>(row)[c] = z;      // the call's head dim, not the kernel's padded one
         }
         return;
     }

@@ -284,3 +284,60 @@ def test_alibi_backward_without_the_ds_workspace():
             capi.lib.fa_debug_set(7, 1)
     for name, x, y in zip(("dq", "dk", "dv"), res[0], res[1]):
         assert (x.float() - y.float()).abs().max().item() <= 2.0 ** -7 * max(1.0, x.float().abs().max().item()), name
+
+
+@pytest.mark.parametrize("packed", [True, False])
+def test_zero_fill_of_padded_head_dims_stays_inside_the_rows(packed):
+    """Head dim 8 runs on the kernels for 64.  Blocks that no key (or no query) reaches are filled with zeros: the
+    fill must write the call's 8 columns, not the kernel's 64 (it once ran 112 bytes past the last row, into whatever
+    the allocator had put behind dq).  dq, dk and dv are views into buffers with sentinel rows on both sides; packed
+    case: sequences without keys and without queries; dense case: causal with more queries than keys."""
+    from flash_attn_npu import flash_attn_npu as ext
+    import fa_b200_capi as capi
+    g = torch.Generator().manual_seed(336)
+    h, hkv, d, dt = 6, 3, 8, torch.float16
+    scale = d ** -0.5
+    if packed:
+        lq, lk = [1, 1, 1, 1, 444, 0], [1, 0, 281, 612, 0, 1]
+        cq = [0] + torch.tensor(lq).cumsum(0).tolist()
+        ck = [0] + torch.tensor(lk).cumsum(0).tolist()
+        q = torch.randn(sum(lq), h, d, generator=g).to(dt)
+        k = torch.randn(sum(lk), hkv, d, generator=g).to(dt)
+        v = torch.randn(sum(lk), hkv, d, generator=g).to(dt)
+    else:
+        q = torch.randn(2, 300, h, d, generator=g).to(dt)
+        k = torch.randn(2, 40, hkv, d, generator=g).to(dt)
+        v = torch.randn(2, 40, hkv, d, generator=g).to(dt)
+    do = torch.randn(q.shape, generator=g).to(dt)
+    if packed:
+        _, rl = orc.attention_varlen_fwd(q.float(), k.float(), v.float(), cq, ck, scale, True, data_type=torch.float32)
+        ref = orc.attention_varlen_bwd(q.float(), k.float(), v.float(), do.float(), rl, cq, ck, scale, True)
+    else:
+        _, rl = orc.attention_fwd(q.float(), k.float(), v.float(), scale, True, data_type=torch.float32)
+        ref = orc.attention_bwd(q.float(), k.float(), v.float(), do.float(), rl, scale, True)
+
+    def guarded(t):          # a view of t's shape with four sentinel rows before and behind it
+        flat = torch.full((t.numel() + 8 * t.shape[-1] * t.shape[-2],), 777.0, dtype=dt, device="cuda")
+        off = 4 * t.shape[-1] * t.shape[-2]
+        return flat, flat[off:off + t.numel()].view(t.shape)
+
+    qg, kg, vg, dog = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    bufs = [guarded(t) for t in (q, k, v)]
+    dq, dk, dv = (b[1] for b in bufs)
+    if packed:
+        cuq = torch.tensor(cq, dtype=torch.int32, device="cuda")
+        cuk = torch.tensor(ck, dtype=torch.int32, device="cuda")
+        out, lse, _, _ = ext.varlen_fwd(qg, kg, vg, None, cuq, cuk, None, None, None, None, max(lq), max(lk), 0.0, scale, False,
+                                        True, -1, -1, 0.0, False, None)
+        ext.varlen_bwd(dog, qg, kg, vg, out, lse, dq, dk, dv, cuq, cuk, None, max(lq), max(lk), 0.0, scale, False, True,
+                       -1, -1, 0.0, False, None, None)
+    else:
+        out, lse, _, _ = ext.fwd(qg, kg, vg, None, None, 0.0, scale, True, -1, -1, 0.0, False, None)
+        ext.bwd(dog, qg, kg, vg, out, lse, dq, dk, dv, None, 0.0, scale, True, -1, -1, 0.0, False, None, None)
+    torch.cuda.synchronize()
+    assert capi.last_kernel().startswith("sm100_tcgen05_bwd")
+    for name, (flat, view), r in zip(("dq", "dk", "dv"), bufs, ref):
+        off = (flat.numel() - view.numel()) // 2
+        assert (flat[:off] == 777.0).all() and (flat[off + view.numel():] == 777.0).all(), name + ": sentinel rows overwritten"
+        err = (view.cpu().float() - r.float()).abs().max().item()
+        assert err <= 2e-3 * max(1.0, r.abs().max().item()), (name, err)
