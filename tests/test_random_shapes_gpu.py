@@ -21,6 +21,19 @@ def _run(policy, fn):
         capi.lib.fa_set_kernel_policy(0)
 
 
+def _guarded(like):
+    """A tensor of `like`'s shape that lies between sentinel elements (about four rows on each side): a kernel that
+    writes past a row or past the tensor shows up as a changed sentinel instead of as a corrupted neighbour."""
+    pad = 4 * like.shape[-1] * like.shape[-2]
+    flat = torch.full((like.numel() + 2 * pad,), 777.0, dtype=like.dtype, device=like.device)
+    return flat, flat[pad:pad + like.numel()].view(like.shape)
+
+
+def _sentinels_intact(flat, view):
+    pad = (flat.numel() - view.numel()) // 2
+    return bool((flat[:pad] == 777.0).all() and (flat[pad + view.numel():] == 777.0).all())
+
+
 def _close(a, b, what):
     a, b = a.float(), b.float()
     scale = max(1.0, b.abs().max().item())
@@ -224,10 +237,14 @@ def test_kvcache_calls_random(block):
         if c is None:
             continue
 
+        guards = []
+
         def call():
             k2, v2 = c["kc"].clone(), c["vc"].clone()
+            flat, out_ = _guarded(c["q"])
+            guards.append((flat, out_))
             out, lse = ext.fwd_kvcache(c["q"], k2, v2, c["kn"], c["vn"], c["lens"], c["cos"], c["sin"], None, None, c["table"],
-                                       c["alibi"], None, c["scale"], c["causal"], c["wl"], c["wr"], c["softcap"],
+                                       c["alibi"], out_, c["scale"], c["causal"], c["wl"], c["wr"], c["softcap"],
                                        c["interleaved"], c["nsplit"])
             return out, lse, k2, v2
 
@@ -237,6 +254,8 @@ def test_kvcache_calls_random(block):
         assert not n2.startswith(("sm100", "decode")), n2
         assert capi.lib.fa_debug_get(2) == 0, c["tag"]
         msgs = []
+        if not all(_sentinels_intact(f, o) for f, o in guards):
+            msgs.append("a kernel wrote outside the output tensor")
         if not torch.equal(k1, k2) or not torch.equal(v1, v2):
             msgs.append("cache differs")
         a, r = o1.float(), o2.float()
@@ -303,13 +322,17 @@ def test_dense_and_packed_calls_any_head_dim_random(block):
             tag = f"seed {seed}: dense b{b} sq{sq} sk{sk} h{h}/{hkv} d{d} {mode} ({wl},{wr}) softcap {softcap} alibi {use_alibi} {dt}"
         do = torch.randn(q.shape, device="cuda", generator=g).to(dt)
 
+        guards = []
+
         def call():
+            g4 = [_guarded(t) for t in (q, q, k, v)]
+            guards.extend(g4)
+            out_, dq, dk, dv = (x[1] for x in g4)
             if packed:
-                out, lse, _, _ = ext.varlen_fwd(q, k, v, None, cuq, cuk, None, None, None, alibi, max(lq), max(lk), 0.0, scale,
+                out, lse, _, _ = ext.varlen_fwd(q, k, v, out_, cuq, cuk, None, None, None, alibi, max(lq), max(lk), 0.0, scale,
                                                 False, causal, wl, wr, softcap, False, None)
             else:
-                out, lse, _, _ = ext.fwd(q, k, v, None, alibi, 0.0, scale, causal, wl, wr, softcap, False, None)
-            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+                out, lse, _, _ = ext.fwd(q, k, v, out_, alibi, 0.0, scale, causal, wl, wr, softcap, False, None)
             if packed:
                 ext.varlen_bwd(do, q, k, v, out, lse, dq, dk, dv, cuq, cuk, alibi, max(lq), max(lk), 0.0, scale, False, causal,
                                wl, wr, softcap, False, None, None)
@@ -323,6 +346,8 @@ def test_dense_and_packed_calls_any_head_dim_random(block):
         assert b1.startswith("sm100_tcgen05_bwd") == (d <= 128), (tag, b1)
         assert capi.lib.fa_debug_get(2) == 0, tag
         msgs = []
+        if not all(_sentinels_intact(f, o) for f, o in guards):
+            msgs.append("a kernel wrote outside an output tensor")
         for name, t1, t2 in (("out", o1, o2), ("dq", dq1, dq2), ("dk", dk1, dk2), ("dv", dv1, dv2)):
             if torch.isnan(t1.float()).any():
                 msgs.append(name + " has nan")
