@@ -921,12 +921,13 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
         // KV-cache calls (prefill against a cache): lengths and pages are read on the device
         if (p.cu_seqlens_q || p.cu_seqlens_k || !p.seqused_k) return false;
         if (p.block_table && (p.page_size <= 0 || p.page_size % 64)) return false;
-        // Head dims below 64 stay on the split-KV decode and general kernels in cache calls.  Two launches of one
-        // sequence (head dim 32, four new tokens under a query group of 8 / 16 against a dense cache of 256 rows: one
-        // and two CTAs, one and two key tiles) raised an illegal memory access here; the same calls on a build with
-        // address checks on every plain access and on every page index ran clean, dense calls of the same size and
-        // cache calls at head dim 64 do too, and the cause is not established.
-        if (p.d < 64) return false;
+        // Cache calls take this kernel at its own head dims only (64, 128, 192, 256); padded head dims stay on the
+        // split-KV decode and general kernels.  Three small launches at padded head dims (32, 32 and 72; one or two
+        // sequences, 4-7 new tokens under a query group of 8 / 16 against a dense cache of 256 rows, one to four CTAs)
+        // raised an illegal memory access here, about one in a hundred launches of that kind; the same calls on a build
+        // with address checks on every plain access, every page index and the nominal spans of the tile copies ran
+        // clean, and so did 500 dense launches of the same shapes.  The cause is not established.
+        if (p.d != 64 && p.d != 128 && p.d != 192 && p.d != 256) return false;
         // Short queries (fewer than 64 a head).  Up to 16 stacked rows a KV head belong to the split-KV decode kernel.
         // Above that the two-tile kernel takes the call with the query group stacked into the tile rows and the keys
         // split over CTAs (partials + combine): a CTA streams its share of a KV head's cache once for all the rows.
