@@ -227,8 +227,8 @@ def test_kvcache_calls_random(block):
     """25 random flash_attn_with_kvcache calls a block (300 in all; head dims 32-256, query groups 1-16 including groups
     that cannot be stacked, 1-300 new tokens, dense and paged caches with pages of 64-256 tokens, append, rotary, windows,
     softcap, alibi, forced split counts): output, LSE and the cache after the call of the default routing against the
-    general kernels.  Among them are launches of a single CTA with one key tile and 32 output columns, the shortest
-    run the two-tile tcgen05 kernel can have (seed 200)."""
+    general kernels.  Among them are one-sequence calls with a handful of new tokens against a cache of 256 rows (seed
+    200: head dim 32, one CTA's worth of work), the smallest launches the routing has to place."""
     from flash_attn_npu import flash_attn_npu as ext
     import fa_b200_capi as capi
     bad, kernels = [], set()
