@@ -298,10 +298,13 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                     // Rows of a cache past the sequence hold whatever was there before (possibly NaN patterns): their
                     // probabilities are exact zeros, but 0 x NaN is NaN, so the V rows are cleared before the MMA.
                     // A row is 128 bytes in every 64-column sub-tile whatever the swizzle.
+                    // Only rows the tile copy fetched are touched: rows past the capacity of a dense cache were
+                    // zero-filled by the copy itself, and generic stores are kept off bytes a copy has filled.
                     const int first = max(0, sk - (t_lo + j) * 128);
+                    const int last = a.block_table ? 128 : min(128, a.sk - (t_lo + j) * 128);
 #pragma unroll
                     for (int sub = 0; sub < NSUB; ++sub)
-                        for (int idx = first * 8 + lane; idx < 128 * 8; idx += 32)      // 16-byte chunks of rows first .. 127
+                        for (int idx = first * 8 + lane; idx < last * 8; idx += 32)     // 16-byte chunks of rows first .. last - 1
                             *reinterpret_cast<uint4*>(sgen + L::oV + st * L::kKV + sub * L::kSub + idx * 16) = make_uint4(0, 0, 0, 0);
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -685,9 +688,10 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel_wide(const __grid_con
             if (a.seqused_k && (t_lo + j) * 128 + 128 > sk) {
                 // stale cache rows past the sequence may hold NaN patterns: 0 x NaN is NaN, so the V rows are cleared
                 const int first = max(0, sk - (t_lo + j) * 128);
+                const int last = a.block_table ? 128 : min(128, a.sk - (t_lo + j) * 128);     // rows the copy fetched
 #pragma unroll
                 for (int sub = 0; sub < NSUB; ++sub)
-                    for (int idx = first * 8 + lane; idx < 128 * 8; idx += 32)
+                    for (int idx = first * 8 + lane; idx < last * 8; idx += 32)
                         *reinterpret_cast<uint4*>(sgen + L::oV + sub * L::kSub + idx * 16) = make_uint4(0, 0, 0, 0);
                 fence_proxy_async_smem();
                 __syncwarp();

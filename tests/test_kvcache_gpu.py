@@ -580,3 +580,35 @@ def test_oversized_cache_seqlens_are_truncated_and_append_nothing(paged):
         f_o, f_l = orc.attention_fwd(q[i:i + 1].float(), ki.float(), vi.float(), d ** -0.5, True, data_type=torch.float32)
         assert_within(f"out[{i}]", out[i:i + 1].cpu(), lp_o, f_o)
         assert_lse(lse[i:i + 1], f_l)
+
+
+@pytest.mark.parametrize("sq,h,hkv,kernel", [(1, 8, 2, "decode_splitkv_tma"), (4, 16, 2, "sm100_tcgen05_2q"), (70, 4, 2, "sm100_tcgen05_2q")])
+def test_dense_cache_whose_capacity_is_not_a_multiple_of_the_tile(sq, h, hkv, kernel):
+    """A dense cache of 333 rows: the last 128-key tile (32-key tile in the decode kernel) reaches past the capacity, the
+    tile copy zero-fills those rows, and the rows between a sequence's length and the capacity hold NaN.  Sequences that
+    end in the last tile, at the capacity itself and one row before it."""
+    import flash_attn_npu as m
+    import fa_b200_capi as capi
+    gen = torch.Generator().manual_seed(333 + sq)
+    b, cap, d, dt = 3, 333, 128, torch.bfloat16
+    lens = [333, 332, 270]
+    q = torch.randn(b, sq, h, d, generator=gen).to(dt)
+    kc = torch.randn(b, cap, hkv, d, generator=gen).to(dt)
+    vc = torch.randn(b, cap, hkv, d, generator=gen).to(dt)
+    for i, L in enumerate(lens):
+        kc[i, L:] = float("nan")
+        vc[i, L:] = float("nan")
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    scale = d ** -0.5
+    rk, rv = torch.nan_to_num(kc.clone()), torch.nan_to_num(vc.clone())
+    lp_o, _ = orc.kvcache_fwd(q, rk.clone(), rv.clone(), lens_t, scale, causal=True)
+    f_o, f_l = orc.kvcache_fwd(q.float(), rk.float(), rv.float(), lens_t, scale, causal=True)
+    for ns in (0, 1):
+        out, lse = m.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=lens_t.cuda(), softmax_scale=scale,
+                                             causal=True, num_splits=ns, return_softmax_lse=True)
+        torch.cuda.synchronize()
+        assert capi.last_kernel() == kernel
+        assert capi.lib.fa_debug_get(2) == 0
+        assert torch.isfinite(out).all()
+        assert_within("out", out.cpu(), lp_o, f_o)
+        assert_lse(lse, f_l)
