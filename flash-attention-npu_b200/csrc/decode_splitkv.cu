@@ -470,8 +470,7 @@ __global__ void __launch_bounds__(WIDE ? 160 : 128) decode_tma_kernel(const __gr
         const uint32_t sKs = sKw + stage * TILE_BYTES, sVs = sVw + stage * TILE_BYTES;
         const int n0 = t_begin + it * TILE;
         if (n0 + TILE > sk) {                                 // rows past the sequence end hold stale cache bytes
-            // (rows past the capacity of a dense cache were zero-filled by the copy itself: generic stores are kept off
-            // bytes a copy has filled)
+            // (rows past the capacity of a dense cache were zero-filled by the copy itself)
             unsigned char* vgen = gen_base + (sVs - sbase);
             const int fetched = btab ? TILE : min(TILE, p.sk - n0);
             for (int idx = lane; idx < TILE * (HD / 8); idx += 32) {

@@ -298,8 +298,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
                     // Rows of a cache past the sequence hold whatever was there before (possibly NaN patterns): their
                     // probabilities are exact zeros, but 0 x NaN is NaN, so the V rows are cleared before the MMA.
                     // A row is 128 bytes in every 64-column sub-tile whatever the swizzle.
-                    // Only rows the tile copy fetched are touched: rows past the capacity of a dense cache were
-                    // zero-filled by the copy itself, and generic stores are kept off bytes a copy has filled.
+                    // Only rows the tile copy fetched need it: rows past the capacity of a dense cache were zero-filled
+                    // by the copy itself.
                     const int first = max(0, sk - (t_lo + j) * 128);
                     const int last = a.block_table ? 128 : min(128, a.sk - (t_lo + j) * 128);
 #pragma unroll
@@ -335,9 +335,8 @@ __global__ void __launch_bounds__(384, 1) fwd_sm100_kernel2(const __grid_constan
             }
             // The release of the last K/V stage has no waiter, and with one query tile in use it is issued after the
             // commit the epilogue waits for.  An arrive that the tensor core performs after the CTA has left would land
-            // in shared memory the CTA no longer owns (an illegal access when nothing else is resident: seen with a
-            // one-CTA launch, one key tile and 32 output columns, the shortest epilogue there is).  Commits complete in
-            // issue order, so the warp waits for a last one of its own before it leaves.
+            // in shared memory the CTA no longer owns.  Commits complete in issue order, so the warp waits for a last
+            // one of its own before it leaves.
             if (ok) {
                 umma_commit_w(bar(C_DRAIN));
                 ok = mbar_wait(bar(C_DRAIN), 0, abort_flag, err, 13);
