@@ -588,10 +588,11 @@ static int launch_decode_tma_t(const DecodeArgs& a, cudaStream_t st) {
     const bool wide = p.sq * (p.hq / p.hkv) > 16;
     DecodeTmaArgs ta;
     ta.d = a;
-    // rows: tokens of a page (paged) or of the cache (dense); the outermost extent is not known to the
-    // parameter block, every index the kernel uses comes from the block table / batch index
+    // rows: tokens of a page (paged) or of the cache (dense); the outermost extent is the number of pages / cache
+    // entries when the caller passed it, else an upper limit; every index the kernel uses comes from the block table /
+    // batch index
     const int64_t rows = p.block_table ? p.page_size : p.sk;
-    const int outer = 1 << 24;
+    const int outer = (p.kv_entries > 0 && p.kv_entries < (1 << 24)) ? (int)p.kv_entries : 1 << 24;
     if (int e = make_tile_map(&ta.tk, p.dtype, p.k.ptr, p.d, p.hkv, rows, outer, p.k.stride_h, p.k.stride_s, p.k.stride_b, TILE)) return e;
     if (int e = make_tile_map(&ta.tv, p.dtype, p.v.ptr, p.dv, p.hkv, rows, outer, p.v.stride_h, p.v.stride_s, p.v.stride_b, TILE)) return e;
     if (wide) {

@@ -33,7 +33,7 @@ class FwdParams(C.Structure):
         ("num_splits", C.c_int32), ("kv_begin", C.c_int32), ("kv_end", C.c_int32), ("partials_only", C.c_int32),
         ("o_partial", C.c_void_p), ("lse_partial", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("sched_meta", C.c_void_p), ("stream", C.c_void_p),
+        ("sched_meta", C.c_void_p), ("kv_entries", C.c_int64), ("stream", C.c_void_p),
     ]
 
 

@@ -213,6 +213,7 @@ def kvcache_forward(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_s
         p.lse_stride_b, p.lse_stride_h, p.lse_stride_s = lse.stride(0), lse.stride(1), lse.stride(2)
     p.lse = lse.data_ptr()
     p.k, p.v = tensor4(kcache), tensor4(vcache)
+    p.kv_entries = min(kcache.shape[0], vcache.shape[0])
     s_new = 0
     if k_ is not None:
         if v_ is None:

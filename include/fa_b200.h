@@ -105,6 +105,11 @@ typedef struct {
                                     * per split from it; a blob built for another batch
                                     * size, split count or for other lengths is ignored
                                     * on the device (the host's uniform plan runs).     */
+    int64_t kv_entries;            /* cache calls: how many pages (paged cache) or cache
+                                    * entries (dense cache) lie behind k.ptr / v.ptr, i.e. the
+                                    * first dimension of the cache tensors; 0 = not known.
+                                    * The tile copies of the cache are then bounded by the
+                                    * cache itself instead of by an upper limit of 2^24.  */
     void*   stream;                /* cudaStream_t                                     */
 } fa_fwd_params;
 

@@ -363,3 +363,78 @@ def test_dense_and_packed_calls_any_head_dim_random(block):
         if msgs:
             bad.append(tag + ": " + "; ".join(msgs))
     assert not bad, "\n".join(bad)
+
+
+@pytest.mark.parametrize("block", range(8))
+def test_small_cache_launches_random(block):
+    """25 small flash_attn_with_kvcache launches a block (200 in all): one or two sequences, one to sixteen new tokens,
+    dense caches whose capacity is not a multiple of the key tile (200, 300, 333, 1000 rows) or paged ones, lengths that
+    end in the last tile, at the capacity and one row before it.  These are launches of one to a few CTAs with one to
+    eight key tiles on the tcgen05 forward and on the decode kernel; default routing against the general kernels."""
+    from flash_attn_npu import flash_attn_npu as ext
+    import fa_b200_capi as capi
+    bad = []
+    for seed in range(block * 25, block * 25 + 25):
+        rnd = random.Random(seed)
+        d = rnd.choice([64, 64, 128, 128])
+        hkv = rnd.choice([1, 1, 2])
+        grp = rnd.choice([2, 4, 8, 16])
+        h = hkv * grp
+        b = rnd.choice([1, 1, 2])
+        sq = rnd.choice([2, 3, 4, 4, 7, 8, 16])
+        if rnd.random() < 0.3:
+            sq = 1
+        elif sq * grp <= 16:
+            sq = 17 // grp + 1
+        paged = rnd.random() < 0.4
+        page = rnd.choice([64, 128, 256])
+        cap = rnd.choice([256, 200, 300, 333, 512, 1000])
+        lens = [rnd.randint(sq, cap) for _ in range(b)]
+        if rnd.random() < 0.5:
+            lens[0] = rnd.choice([86, 100, 128, min(249, cap), cap, cap - 1, max(sq, cap - 60)])
+        causal = rnd.random() < 0.6
+        nsplit = rnd.choice([0, 1, 1])
+        dt = rnd.choice([torch.bfloat16, torch.bfloat16, torch.float16])
+        g = torch.Generator(device="cuda").manual_seed(88000 + seed)
+        q = torch.randn(b, sq, h, d, device="cuda", generator=g).to(dt)
+        if paged:
+            cap = (cap + page - 1) // page * page
+            nb = cap // page
+            pool = nb * b + 2
+            table = torch.randperm(pool, device="cuda", generator=g).int()[: nb * b].reshape(b, nb).contiguous()
+            kc = torch.randn(pool, page, hkv, d, device="cuda", generator=g).to(dt)
+            vc = torch.randn(pool, page, hkv, d, device="cuda", generator=g).to(dt)
+        else:
+            table = None
+            kc = torch.randn(b, cap, hkv, d, device="cuda", generator=g).to(dt)
+            vc = torch.randn(b, cap, hkv, d, device="cuda", generator=g).to(dt)
+        lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        tag = f"seed {seed}: b{b} sq{sq} h{h}/{hkv} d{d} capacity {cap} paged {paged} page {page} lens {lens} causal {causal} num_splits {nsplit} {dt}"
+        guards = []
+
+        def call():
+            flat, out_ = _guarded(q)
+            guards.append((flat, out_))
+            out, lse = ext.fwd_kvcache(q, kc, vc, None, None, lens_t, None, None, None, None, table, None, out_, d ** -0.5, causal,
+                                       -1, -1, 0.0, False, nsplit)
+            return out, lse
+
+        (o1, l1), n1 = _run(0, call)
+        (o2, l2), n2 = _run(1, call)
+        assert n1 in ("sm100_tcgen05_2q", "decode_splitkv_tma"), (tag, n1)
+        assert capi.lib.fa_debug_get(2) == 0, tag
+        msgs = []
+        if not all(_sentinels_intact(f, o) for f, o in guards):
+            msgs.append("a kernel wrote outside the output tensor")
+        try:
+            _close(o1, o2, "out")
+        except AssertionError as e:
+            msgs.append(str(e))
+        fin = torch.isfinite(l2)
+        if not torch.equal(torch.isfinite(l1), fin):
+            msgs.append("lse finiteness differs")
+        elif fin.any() and (l1[fin] - l2[fin]).abs().max().item() > 1e-4 * max(1.0, l2[fin].abs().max().item()):
+            msgs.append("lse differs")
+        if msgs:
+            bad.append(tag + f" [{n1}]: " + "; ".join(msgs))
+    assert not bad, "\n".join(bad)
