@@ -132,6 +132,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k_, leftpad_k_
         if block_table_.dtype != torch.int32 or block_table_.stride(-1) != 1:
             raise RuntimeError("block_table must be int32 with contiguous last dimension")
         p.block_table, p.block_table_stride, p.page_size = block_table_.data_ptr(), block_table_.stride(0), k.shape[1]
+        p.kv_entries = min(k.shape[0], v.shape[0])
         p.seqused_k = ptr(seqused_k_)
         p.num_splits = 0
     else:

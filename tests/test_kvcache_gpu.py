@@ -349,6 +349,7 @@ def test_scheduler_metadata_is_consumed_by_the_decode():
     out_c, lse_c = torch.empty_like(qg), torch.empty(b, h, 1, device="cuda")
     p = FwdParams()
     p.q, p.k, p.v, p.o = tensor4(qg), tensor4(kg), tensor4(vg), tensor4(out_c)
+    p.kv_entries = kg.shape[0]
     p.lse, p.lse_stride_b, p.lse_stride_h, p.lse_stride_s = lse_c.data_ptr(), lse_c.stride(0), lse_c.stride(1), lse_c.stride(2)
     p.block_table, p.block_table_stride, p.page_size, p.seqused_k = tg.data_ptr(), tg.stride(0), page, lg.data_ptr()
     p.b, p.sq, p.sk, p.hq, p.hkv, p.d, p.dv = b, 1, cap, h, hkv, d, d

@@ -19,6 +19,7 @@ def build_params(q, kc, vc, table, lens, out, lse, num_splits):
     b, sq, hq, d = q.shape
     p = FwdParams()
     p.q, p.k, p.v, p.o = tensor4(q), tensor4(kc), tensor4(vc), tensor4(out)
+    p.kv_entries = kc.shape[0]
     p.lse = lse.data_ptr()
     p.lse_stride_b, p.lse_stride_h, p.lse_stride_s = lse.stride(0), lse.stride(1), lse.stride(2)
     p.block_table, p.block_table_stride, p.page_size = table.data_ptr(), table.stride(0), kc.shape[1]
