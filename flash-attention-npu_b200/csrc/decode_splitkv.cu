@@ -575,6 +575,7 @@ __global__ void __launch_bounds__(WIDE ? 160 : 128) decode_tma_kernel(const __gr
 
 static bool decode_tma_ok(const fa_fwd_params& p) {
     if (p.d != p.dv || (p.d != 64 && p.d != 128 && p.d != 256)) return false;
+    if (p.kv_entries <= 0) return false;           // the tile maps need the cache's own outermost extent (see fa_fwd_params)
     const int tile = p.d > 128 ? 16 : 32;
     if (p.block_table && (p.page_size % tile) != 0) return false;
     if (p.k.stride_h <= 0 || p.k.stride_s <= 0 || p.k.stride_b <= 0 || p.v.stride_h <= 0 || p.v.stride_s <= 0 || p.v.stride_b <= 0) return false;
@@ -589,10 +590,9 @@ static int launch_decode_tma_t(const DecodeArgs& a, cudaStream_t st) {
     DecodeTmaArgs ta;
     ta.d = a;
     // rows: tokens of a page (paged) or of the cache (dense); the outermost extent is the number of pages / cache
-    // entries when the caller passed it, else an upper limit; every index the kernel uses comes from the block table /
-    // batch index
+    // entries; every index the kernel uses comes from the block table / batch index
     const int64_t rows = p.block_table ? p.page_size : p.sk;
-    const int outer = (p.kv_entries > 0 && p.kv_entries < (1 << 24)) ? (int)p.kv_entries : 1 << 24;
+    const int outer = (int)(p.kv_entries < (1 << 24) ? p.kv_entries : 1 << 24);      // > 0: checked by the support predicate
     if (int e = make_tile_map(&ta.tk, p.dtype, p.k.ptr, p.d, p.hkv, rows, outer, p.k.stride_h, p.k.stride_s, p.k.stride_b, TILE)) return e;
     if (int e = make_tile_map(&ta.tv, p.dtype, p.v.ptr, p.dv, p.hkv, rows, outer, p.v.stride_h, p.v.stride_s, p.v.stride_b, TILE)) return e;
     if (wide) {

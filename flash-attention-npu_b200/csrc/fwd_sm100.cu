@@ -924,6 +924,10 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
         // KV-cache calls (prefill against a cache): lengths and pages are read on the device
         if (p.cu_seqlens_q || p.cu_seqlens_k || !p.seqused_k) return false;
         if (p.block_table && (p.page_size <= 0 || p.page_size % 64)) return false;
+        // The tile maps of a cache must end with the cache (a copy touches the addresses of clipped box elements that lie
+        // inside the declared tensor): without the number of pages / cache entries the call stays on kernels with plain,
+        // guarded loads.
+        if (p.kv_entries <= 0) return false;
         // Cache calls take this kernel at its own head dims only (64, 128, 192, 256); padded head dims stay on the
         // split-KV decode and general kernels.  (A box that reaches past a row's columns touches the following row, which
         // for the last row of a cache is only harmless when the tile map ends with the cache: see kv_entries below.  The
@@ -1027,10 +1031,10 @@ int launch_fwd_sm100(const fa_fwd_params& p, int nsplit, int keys_per_split, flo
     if (int e = make_tile_map(&a.tq, p.dtype, p.q.ptr, p.d, p.hq, q_rows, nb, p.q.stride_h, p.q.stride_s, bstride(p.q, q_rows), 128 / a.gq, a.gq)) return e;
     const bool cache = p.block_table || p.seqused_k || p.cache_batch_idx;
     if (cache) {
-        // rows of one page / cache entry; the outermost extent is the number of pages or cache entries when the caller
-        // passed it, else only an upper limit (the page table and cache_batch_idx are valid by contract)
+        // rows of one page / cache entry; the outermost extent is the number of pages or cache entries (the page table
+        // and cache_batch_idx are valid by contract)
         const int64_t rows = p.block_table ? p.page_size : p.sk;
-        const int outer = (p.kv_entries > 0 && p.kv_entries < (1 << 24)) ? (int)p.kv_entries : 1 << 24;
+        const int outer = (int)(p.kv_entries < (1 << 24) ? p.kv_entries : 1 << 24);      // > 0: checked by the support predicate
         if (p.block_table && p.page_size % 128) a.kv_box = 64;
         if (int e = make_tile_map(&a.tk, p.dtype, p.k.ptr, p.d, p.hkv, rows, outer, p.k.stride_h, p.k.stride_s, p.k.stride_b, a.kv_box)) return e;
         if (int e = make_tile_map(&a.tv, p.dtype, p.v.ptr, p.d, p.hkv, rows, outer, p.v.stride_h, p.v.stride_s, p.v.stride_b, a.kv_box)) return e;

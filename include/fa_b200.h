@@ -108,8 +108,9 @@ typedef struct {
     int64_t kv_entries;            /* cache calls: how many pages (paged cache) or cache
                                     * entries (dense cache) lie behind k.ptr / v.ptr, i.e. the
                                     * first dimension of the cache tensors; 0 = not known.
-                                    * The tile copies of the cache are then bounded by the
-                                    * cache itself instead of by an upper limit of 2^24.  */
+                                    * The tile copies (TMA) of the cache are bounded by it;
+                                    * without it cache calls run on the kernels that use
+                                    * plain guarded loads (slower, same results).          */
     void*   stream;                /* cudaStream_t                                     */
 } fa_fwd_params;
 
