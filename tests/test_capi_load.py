@@ -72,3 +72,24 @@ def test_split_planner_is_host_only():
     p.num_splits = 4
     assert capi.lib.fa_fwd_num_splits(p) == 4
     assert capi.lib.fa_scheduler_metadata_ints(16) == 8 + 8 * 16
+
+
+def _header_fields(name):
+    """Field names of `typedef struct { ... } name;` in the header, in order."""
+    text = open(os.path.join(ROOT, "include", "fa_b200.h")).read()
+    chunk = [c for c in text.split("typedef struct") if re.search(r"\}\s*%s\s*;" % name, c)][0]
+    body = chunk[chunk.index("{") + 1:chunk.index("} " + name)]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for stmt in body.split(";"):
+        stmt = stmt.strip()
+        if not stmt:
+            continue
+        stmt = re.sub(r"^(const\s+)?\w+(\s+const)?[\s\*]*", "", stmt, count=1)       # drop the type
+        names += [re.sub(r"[\s\*]|\[.*\]", "", part) for part in stmt.split(",")]
+    return names
+
+
+def test_ctypes_structs_follow_the_header_field_by_field():
+    for name, cls in (("fa_fwd_params", capi.FwdParams), ("fa_bwd_params", capi.BwdParams)):
+        assert _header_fields(name) == [f[0] for f in cls._fields_], name
