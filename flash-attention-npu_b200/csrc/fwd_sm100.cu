@@ -930,7 +930,7 @@ bool fwd_sm100_supported(const fa_fwd_params& p) {
         if (p.kv_entries <= 0) return false;
         // Cache calls take this kernel at its own head dims only (64, 128, 192, 256); padded head dims stay on the
         // split-KV decode and general kernels.  (A box that reaches past a row's columns touches the following row, which
-        // for the last row of a cache is only harmless when the tile map ends with the cache: see kv_entries below.  The
+        // for the last row of a cache is only harmless when the tile map ends with the cache: see kv_entries above.  The
         // restriction was put in before that was understood and has not been measured without it since.)
         if (p.d != 64 && p.d != 128 && p.d != 192 && p.d != 256) return false;
         // Short queries (fewer than 64 a head).  Up to 16 stacked rows a KV head belong to the split-KV decode kernel.
